@@ -1,0 +1,128 @@
+/*
+ * C ABI of the B200 FP8 gate/up-projection + SwiGLU library (libgateup.so).
+ *
+ *   output[M, N] (bf16) = SiLU(X . Wg^T) * (X . Wu^T)
+ *
+ * X is e4m3 [M, K] with fp32 scales [M, K/128]; Wg / Wu are e4m3 [N, K] with
+ * fp32 scales [N/128, K/128]; all row-major and contiguous (output may have a
+ * row pitch larger than N).  These are the tensors the reference entry point
+ * takes, in its order:
+ *   kernels/179_fp8_mlp_gate_up_projection/kernel.py:398-407            (Python `run`)
+ *   kernels/179_fp8_mlp_gate_up_projection/variants/cuda_cpp_v4/binding.cpp:18-25 (pybind `run`)
+ *
+ * Every pointer is a device pointer on the current device, 16-byte aligned.
+ * No entry point allocates or frees device memory; scratch is passed in by the
+ * caller.  All launches go to the stream that is passed in.  Functions return 0
+ * on success or a negative GU_E* code; nothing throws.
+ */
+#ifndef GATEUP_H_
+#define GATEUP_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define GU_VERSION 1
+
+/* error codes */
+#define GU_OK 0
+#define GU_EINVAL_NULL (-1)      /* a required pointer is null                         */
+#define GU_EINVAL_SHAPE (-2)     /* M < 1, or K or N not a positive multiple of 128    */
+#define GU_EINVAL_ALIGN (-3)     /* a pointer or the output pitch is not 16-B aligned  */
+#define GU_EINVAL_PLAN (-4)      /* unknown plan id, or the plan cannot run this shape */
+#define GU_EWORKSPACE (-5)       /* workspace missing or smaller than required         */
+#define GU_ECUDA (-6)            /* a CUDA runtime / driver call failed                */
+#define GU_EDEVICE (-7)          /* not a compute-capability-10.x device               */
+#define GU_ETIMEOUT (-8)         /* a bounded device-side wait gave up (gu_last_status) */
+
+/* plans */
+#define GU_PLAN_AUTO 0    /* shape heuristic (gu_select_plan)                                      */
+#define GU_PLAN_TILE 1    /* persistent 128 x (128 gate + 128 up) tiles; any M                      */
+#define GU_PLAN_STREAM 2  /* weight-streaming, tokens on the MMA N side, stream-K over (N-block, K-block); M <= 64 */
+
+/*
+ * One call's operands.  Replaces the seven tensors of the reference `run`
+ * (kernel.py:398-407) plus what its host glue derives from them: M, K, N
+ * (kernel.py:354,419) and the launch stream (kernel.py:212-213, passed to
+ * gu_run separately).
+ */
+typedef struct gu_problem {
+  const void* x;            /* e4m3 [M, K]                 */
+  const float* scale_x;     /* f32  [M, K/128]             */
+  const void* gate_w;       /* e4m3 [N, K]                 */
+  const float* scale_gate;  /* f32  [N/128, K/128]         */
+  const void* up_w;         /* e4m3 [N, K]                 */
+  const float* scale_up;    /* f32  [N/128, K/128]         */
+  void* output;             /* bf16 [M, ld_output], columns [0, N) written */
+  int64_t m, k, n;
+  int64_t ld_output;        /* row pitch of output in elements (>= N, multiple of 8) */
+  void* workspace;          /* gu_workspace_bytes() bytes, prepared once by gu_workspace_init; may be null when 0 */
+  size_t workspace_bytes;
+  int32_t plan;             /* GU_PLAN_*                   */
+  int32_t reserved;
+} gu_problem;
+
+/* Library version (GU_VERSION). */
+int gu_version(void);
+
+/* Static message for a GU_E* code. */
+const char* gu_error_string(int code);
+
+/*
+ * Tile / split policy.  Stands where the reference has `_select_config`
+ * (kernel.py:232-249) and the even/odd-M dispatch of `launch_fp8_mlp_gate_up`
+ * (variants/cuda_cpp_v4/kernel.cu:297-311).  Returns GU_PLAN_TILE or
+ * GU_PLAN_STREAM for a valid shape, or a negative code.
+ */
+int gu_select_plan(int64_t m, int64_t k, int64_t n);
+
+/*
+ * Scratch bytes a plan needs for this shape (0 for GU_PLAN_TILE).  The
+ * reference allocates its scratch inside the call (kernel.py:226-229,
+ * cuda_cpp_v4/kernel.cu:221-230, 290-296); here the caller owns it.
+ */
+size_t gu_workspace_bytes(int64_t m, int64_t k, int64_t n, int plan);
+
+/*
+ * Prepare freshly allocated scratch (zeroes the hand-off flags; enqueued on
+ * `stream`).  Needed once per allocation, not per call: each call stamps the
+ * flags with a new epoch.  Calls that share one workspace must not overlap on
+ * the GPU.
+ */
+int gu_workspace_init(void* workspace, size_t bytes, void* stream);
+
+/*
+ * Launch the fused op on `stream` (a cudaStream_t).  Replaces the whole body
+ * of the reference `run`: two GEMM launches and the SwiGLU launch
+ * (kernel.py:487-503), or `launch_fp8_mlp_gate_up` (cuda_cpp_v4/kernel.cu:271-341).
+ * Asynchronous; returns after the launch with 0 or a negative code.
+ */
+int gu_run(const gu_problem* problem, void* stream);
+
+/*
+ * Same op with concatenated weights W[2N, K] (gate rows first) and scales
+ * [2N/128, K/128]; slices and forwards to gu_run.
+ */
+int gu_run_concat(const void* x, const float* scale_x, const void* w2n, const float* scale_w2n,
+                  void* output, int64_t m, int64_t k, int64_t n, int64_t ld_output,
+                  void* workspace, size_t workspace_bytes, int plan, void* stream);
+
+/*
+ * Device-side status of the current device: 0, or GU_ETIMEOUT with `detail`
+ * = (wait id << 24 | block index) of the first wait that gave up.  Synchronises
+ * the device; meant for tests and debugging, never for the timed path.  The
+ * reference has no counterpart (its cluster wait spins without bound,
+ * variants/cute_fused_v1/blockwise_gemm_fused.py:85-91).  `clear` != 0 resets it.
+ */
+int gu_last_status(int* detail, int clear);
+
+/* Kernel launches issued by this library in this process so far. */
+int64_t gu_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GATEUP_H_ */

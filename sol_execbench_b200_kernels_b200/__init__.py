@@ -1,0 +1,28 @@
+"""B200-native FP8 gate/up projection with fused SwiGLU.
+
+    from sol_execbench_b200_kernels_b200 import run
+    run(x, scale_x, gate_proj_weight, scale_gate, up_proj_weight, scale_up, output)
+
+`run` keeps the reference submission's entry-point signature
+(kernels/179_fp8_mlp_gate_up_projection/kernel.py:398-407).  The arithmetic is
+hand-written sm_100a CUDA in libgateup.so (C ABI in include/gateup.h); build it
+with `python -m sol_execbench_b200_kernels_b200.build`.  Importing the compute
+entry points without the built library raises: there is no fallback path.
+"""
+from . import workloads  # noqa: F401  (pure torch, no native code)
+from .sharded import (assemble_gathered, gather_columns, run_sharded, shard_bounds,  # noqa: F401
+                      shard_concat_weights, shard_weights)
+
+_NATIVE = ("run", "run_concat", "run_with_plan", "select_plan", "last_status", "launch_count")
+
+
+def __getattr__(name):
+    # the native entry points load libgateup.so on first use and raise if it is missing
+    if name in _NATIVE:
+        from . import kernel
+        return getattr(kernel, name)
+    raise AttributeError(name)
+
+
+__all__ = list(_NATIVE) + ["workloads", "run_sharded", "shard_bounds", "shard_weights", "shard_concat_weights",
+                           "gather_columns", "assemble_gathered"]

@@ -1,0 +1,338 @@
+// Host side of libgateup.so: argument checks, TMA descriptor encoding, the
+// shape heuristic and the extern "C" entry points declared in include/gateup.h.
+// Takes over what the reference does in its pybind `run` and
+// `launch_fp8_mlp_gate_up` (variants/cuda_cpp_v4/binding.cpp:18-81,
+// variants/cuda_cpp_v4/kernel.cu:185-233, 271-341), for any (M, K, N) with
+// K and N multiples of 128.
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <unordered_map>
+
+#include "../../include/gateup.h"
+#include "gateup_stream.cuh"
+#include "gateup_tile.cuh"
+
+namespace gu {
+namespace {
+
+// ---------------------------------------------------------------------------
+// driver entry point for tensor-map encoding (no link-time libcuda dependency,
+// so the library also loads on a machine without a driver)
+// ---------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess) {
+      p = nullptr;
+    }
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+struct MapKey {
+  const void* ptr;
+  uint64_t cols, rows, pitch_bytes;
+  uint32_t box_cols, box_rows, dtype;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && cols == o.cols && rows == o.rows && pitch_bytes == o.pitch_bytes &&
+           box_cols == o.box_cols && box_rows == o.box_rows && dtype == o.dtype;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    uint64_t h = reinterpret_cast<uint64_t>(k.ptr) * 0x9e3779b97f4a7c15ull;
+    h ^= (k.cols + 0x632be59bd9b4e019ull) * 0xff51afd7ed558ccdull;
+    h ^= (k.rows << 17) ^ (k.pitch_bytes << 3) ^ (uint64_t(k.box_rows) << 40) ^ (uint64_t(k.box_cols) << 52) ^ k.dtype;
+    return static_cast<size_t>(h ^ (h >> 29));
+  }
+};
+
+std::mutex g_mutex;
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;  // encoded descriptors, keyed by what they describe
+
+// Row-major 2-D tensor [rows, cols] with a row pitch, box [box_rows, box_cols],
+// 128-byte swizzle (box_cols * element size must be 128 bytes).
+int get_map(CUtensorMap* out, CUtensorMapDataType dtype, uint32_t elem_bytes, const void* ptr, uint64_t cols,
+            uint64_t rows, uint64_t pitch_bytes, uint32_t box_cols, uint32_t box_rows) {
+  MapKey key{ptr, cols, rows, pitch_bytes, box_cols, box_rows, static_cast<uint32_t>(dtype)};
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    auto it = g_maps.find(key);
+    if (it != g_maps.end()) {
+      *out = it->second;
+      return GU_OK;
+    }
+  }
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return GU_ECUDA;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {pitch_bytes};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  (void)elem_bytes;
+  CUresult r = fn(out, dtype, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return GU_ECUDA;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (g_maps.size() > 4096) g_maps.clear();
+  g_maps.emplace(key, *out);
+  return GU_OK;
+}
+
+struct DeviceInfo {
+  bool ready = false;
+  int sm_count = 0;
+  int cc_major = 0;
+  int max_smem_optin = 0;
+  bool attrs_set = false;
+};
+DeviceInfo g_dev[64];
+
+int device_info(DeviceInfo** out) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return GU_ECUDA;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  DeviceInfo& d = g_dev[dev];
+  if (!d.ready) {
+    if (cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return GU_ECUDA;
+    if (cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return GU_ECUDA;
+    if (cudaDeviceGetAttribute(&d.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess)
+      return GU_ECUDA;
+    d.ready = true;
+  }
+  if (d.cc_major != 10) return GU_EDEVICE;
+  if (!d.attrs_set) {
+    const int smem = d.max_smem_optin;
+    if (cudaFuncSetAttribute(gateup_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
+        cudaFuncSetAttribute(gateup_stream_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
+            cudaSuccess ||
+        cudaFuncSetAttribute(gateup_stream_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
+            cudaSuccess ||
+        cudaFuncSetAttribute(gateup_stream_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
+            cudaSuccess) {
+      cudaGetLastError();
+      return GU_ECUDA;
+    }
+    d.attrs_set = true;
+  }
+  *out = &d;
+  return GU_OK;
+}
+
+std::atomic<unsigned int> g_epoch{0};
+std::atomic<long long> g_launches{0};
+
+constexpr int kSmemBudget = 227 * 1024;
+
+inline int stream_mpad(int64_t m) { return m <= 16 ? 16 : (m <= 32 ? 32 : 64); }
+
+// Ring depth of the streaming kernel: as deep as shared memory allows, 0 if fewer than 3 stages fit.
+int stream_stages(int mpad, int64_t kb) {
+  const int64_t stage = 2 * kOperandTileBytes + int64_t(mpad) * 128;
+  const int64_t fixed = 512 + kb * mpad * 4 + 1024;
+  int64_t s = (kSmemBudget - fixed) / stage;
+  if (s > kStreamMaxStages) s = kStreamMaxStages;
+  return s >= 3 ? static_cast<int>(s) : 0;
+}
+
+bool shape_ok(int64_t m, int64_t k, int64_t n) {
+  return m >= 1 && k >= 128 && n >= 128 && (k % 128) == 0 && (n % 128) == 0 && m < (1ll << 31) &&
+         k < (1ll << 31) && n < (1ll << 31);
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int check_problem(const gu_problem* pr) {
+  if (!pr) return GU_EINVAL_NULL;
+  if (!pr->x || !pr->scale_x || !pr->gate_w || !pr->scale_gate || !pr->up_w || !pr->scale_up || !pr->output)
+    return GU_EINVAL_NULL;
+  if (!shape_ok(pr->m, pr->k, pr->n)) return GU_EINVAL_SHAPE;
+  if (pr->ld_output < pr->n) return GU_EINVAL_SHAPE;
+  if (!aligned16(pr->x) || !aligned16(pr->gate_w) || !aligned16(pr->up_w) || !aligned16(pr->output) ||
+      (reinterpret_cast<uintptr_t>(pr->scale_x) & 3u) || (reinterpret_cast<uintptr_t>(pr->scale_gate) & 3u) ||
+      (reinterpret_cast<uintptr_t>(pr->scale_up) & 3u) || (pr->ld_output % 8) != 0)
+    return GU_EINVAL_ALIGN;
+  return GU_OK;
+}
+
+int launch_tile(const gu_problem* pr, const DeviceInfo& dev, cudaStream_t stream) {
+  const int64_t m = pr->m, k = pr->k, n = pr->n;
+  CUtensorMap tm_x, tm_g, tm_u, tm_o;
+  int rc;
+  if ((rc = get_map(&tm_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, pr->x, k, m, k, 128, 128)) != GU_OK) return rc;
+  if ((rc = get_map(&tm_g, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, pr->gate_w, k, n, k, 128, 128)) != GU_OK) return rc;
+  if ((rc = get_map(&tm_u, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, pr->up_w, k, n, k, 128, 128)) != GU_OK) return rc;
+  if ((rc = get_map(&tm_o, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, pr->output, n, m, pr->ld_output * 2, 64, 128)) !=
+      GU_OK)
+    return rc;
+
+  TileParams p;
+  p.scale_x = pr->scale_x;
+  p.scale_gate = pr->scale_gate;
+  p.scale_up = pr->scale_up;
+  p.m = static_cast<int>(m);
+  p.kb = static_cast<int>(k / 128);
+  p.num_m_blocks = static_cast<int>((m + kTileM - 1) / kTileM);
+  p.num_n_blocks = static_cast<int>(n / kTileN);
+  const int64_t tiles = int64_t(p.num_m_blocks) * p.num_n_blocks;
+  if (tiles >= (1ll << 31)) return GU_EINVAL_SHAPE;
+  p.num_tiles = static_cast<int>(tiles);
+  // raster group: as many M blocks as keep the group's X tiles (128 x K bytes each) within ~24 MiB of L2
+  int64_t gm = (24ll << 20) / (128 * k);
+  if (gm < 1) gm = 1;
+  if (gm > p.num_m_blocks) gm = p.num_m_blocks;
+  p.group_m = static_cast<int>(gm);
+
+  const int grid = p.num_tiles < dev.sm_count ? p.num_tiles : dev.sm_count;
+  gateup_tile_kernel<<<grid, kTileThreads, kTileSmemBytes, stream>>>(tm_x, tm_g, tm_u, tm_o, p);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError() == cudaSuccess ? GU_OK : GU_ECUDA;
+}
+
+template <int MPAD>
+int launch_stream_t(const gu_problem* pr, const DeviceInfo& dev, cudaStream_t stream, int stages) {
+  const int64_t m = pr->m, k = pr->k, n = pr->n;
+  CUtensorMap tm_x, tm_g, tm_u;
+  int rc;
+  if ((rc = get_map(&tm_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, pr->x, k, m, k, 128, MPAD)) != GU_OK) return rc;
+  if ((rc = get_map(&tm_g, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, pr->gate_w, k, n, k, 128, 128)) != GU_OK) return rc;
+  if ((rc = get_map(&tm_u, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, pr->up_w, k, n, k, 128, 128)) != GU_OK) return rc;
+
+  StreamParams p;
+  p.scale_x = pr->scale_x;
+  p.scale_gate = pr->scale_gate;
+  p.scale_up = pr->scale_up;
+  p.out = static_cast<__nv_bfloat16*>(pr->output);
+  p.ld_out = pr->ld_output;
+  p.m = static_cast<int>(m);
+  p.kb = static_cast<int>(k / 128);
+  p.nb = static_cast<int>(n / 128);
+  p.stages = stages;
+  p.flags = static_cast<unsigned int*>(pr->workspace);
+  p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(pr->workspace) + kStreamFlagBytes);
+  unsigned int e = g_epoch.fetch_add(1, std::memory_order_relaxed) + 1;
+  if (e == 0) e = g_epoch.fetch_add(1, std::memory_order_relaxed) + 1;
+  p.epoch = e;
+
+  const int64_t units = int64_t(p.nb) * p.kb;
+  int64_t grid = dev.sm_count < kStreamMaxGrid ? dev.sm_count : kStreamMaxGrid;
+  if (units < grid) grid = units;
+  const uint32_t smem = StreamCfg<MPAD>::smem_bytes(stages, p.kb);
+  gateup_stream_kernel<MPAD><<<static_cast<int>(grid), kStreamThreads, smem, stream>>>(tm_x, tm_g, tm_u, p);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError() == cudaSuccess ? GU_OK : GU_ECUDA;
+}
+
+}  // namespace
+}  // namespace gu
+
+extern "C" {
+
+int gu_version(void) { return GU_VERSION; }
+
+const char* gu_error_string(int code) {
+  switch (code) {
+    case GU_OK: return "ok";
+    case GU_EINVAL_NULL: return "a required pointer is null";
+    case GU_EINVAL_SHAPE: return "unsupported shape: need M >= 1, K and N positive multiples of 128, ld_output >= N";
+    case GU_EINVAL_ALIGN: return "pointers must be 16-byte aligned and ld_output a multiple of 8";
+    case GU_EINVAL_PLAN: return "unknown plan, or the plan cannot run this shape";
+    case GU_EWORKSPACE: return "workspace missing or too small (see gu_workspace_bytes)";
+    case GU_ECUDA: return "a CUDA call failed";
+    case GU_EDEVICE: return "the current device is not compute capability 10.x";
+    case GU_ETIMEOUT: return "a bounded device-side wait gave up";
+    default: return "unknown error";
+  }
+}
+
+int gu_select_plan(int64_t m, int64_t k, int64_t n) {
+  if (!gu::shape_ok(m, k, n)) return GU_EINVAL_SHAPE;
+  if (m <= 64 && gu::stream_stages(gu::stream_mpad(m), k / 128) > 0) return GU_PLAN_STREAM;
+  return GU_PLAN_TILE;
+}
+
+size_t gu_workspace_bytes(int64_t m, int64_t k, int64_t n, int plan) {
+  if (!gu::shape_ok(m, k, n)) return 0;
+  if (plan == GU_PLAN_AUTO) plan = gu_select_plan(m, k, n);
+  if (plan != GU_PLAN_STREAM || m > 64) return 0;
+  return gu::kStreamFlagBytes + size_t(gu::kStreamMaxGrid) * 2 * gu::stream_mpad(m) * 128 * sizeof(float);
+}
+
+int gu_workspace_init(void* workspace, size_t bytes, void* stream) {
+  if (!workspace || bytes == 0) return GU_OK;
+  const size_t n = bytes < gu::kStreamFlagBytes ? bytes : gu::kStreamFlagBytes;
+  return cudaMemsetAsync(workspace, 0, n, static_cast<cudaStream_t>(stream)) == cudaSuccess ? GU_OK : GU_ECUDA;
+}
+
+int gu_run(const gu_problem* pr, void* stream_v) {
+  int rc = gu::check_problem(pr);
+  if (rc != GU_OK) return rc;
+  int plan = pr->plan;
+  if (plan == GU_PLAN_AUTO) plan = gu_select_plan(pr->m, pr->k, pr->n);
+  if (plan != GU_PLAN_TILE && plan != GU_PLAN_STREAM) return GU_EINVAL_PLAN;
+  gu::DeviceInfo* dev = nullptr;
+  if ((rc = gu::device_info(&dev)) != GU_OK) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  if (plan == GU_PLAN_TILE) return gu::launch_tile(pr, *dev, stream);
+
+  if (pr->m > 64) return GU_EINVAL_PLAN;
+  const int mpad = gu::stream_mpad(pr->m);
+  const int stages = gu::stream_stages(mpad, pr->k / 128);
+  if (stages == 0) return GU_EINVAL_PLAN;
+  const size_t need = gu_workspace_bytes(pr->m, pr->k, pr->n, GU_PLAN_STREAM);
+  if (!pr->workspace || pr->workspace_bytes < need || !gu::aligned16(pr->workspace)) return GU_EWORKSPACE;
+  switch (mpad) {
+    case 16: return gu::launch_stream_t<16>(pr, *dev, stream, stages);
+    case 32: return gu::launch_stream_t<32>(pr, *dev, stream, stages);
+    default: return gu::launch_stream_t<64>(pr, *dev, stream, stages);
+  }
+}
+
+int gu_run_concat(const void* x, const float* scale_x, const void* w2n, const float* scale_w2n, void* output,
+                  int64_t m, int64_t k, int64_t n, int64_t ld_output, void* workspace, size_t workspace_bytes,
+                  int plan, void* stream) {
+  if (!w2n || !scale_w2n) return GU_EINVAL_NULL;
+  if (!gu::shape_ok(m, k, n)) return GU_EINVAL_SHAPE;
+  gu_problem pr;
+  std::memset(&pr, 0, sizeof(pr));
+  pr.x = x;
+  pr.scale_x = scale_x;
+  pr.gate_w = w2n;
+  pr.scale_gate = scale_w2n;
+  pr.up_w = static_cast<const uint8_t*>(w2n) + size_t(n) * size_t(k);
+  pr.scale_up = scale_w2n + size_t(n / 128) * size_t(k / 128);
+  pr.output = output;
+  pr.m = m;
+  pr.k = k;
+  pr.n = n;
+  pr.ld_output = ld_output;
+  pr.workspace = workspace;
+  pr.workspace_bytes = workspace_bytes;
+  pr.plan = plan;
+  return gu_run(&pr, stream);
+}
+
+int gu_last_status(int* detail, int clear) {
+  unsigned int host[4] = {0, 0, 0, 0};
+  if (cudaDeviceSynchronize() != cudaSuccess) return GU_ECUDA;
+  if (cudaMemcpyFromSymbol(host, gu::g_status, sizeof(host)) != cudaSuccess) return GU_ECUDA;
+  if (detail) *detail = static_cast<int>(host[1]);
+  if (clear && host[0] != 0) {
+    unsigned int zero[4] = {0, 0, 0, 0};
+    if (cudaMemcpyToSymbol(gu::g_status, zero, sizeof(zero)) != cudaSuccess) return GU_ECUDA;
+  }
+  return host[0] == 0 ? GU_OK : GU_ETIMEOUT;
+}
+
+int64_t gu_launch_count(void) { return gu::g_launches.load(std::memory_order_relaxed); }
+
+}  // extern "C"

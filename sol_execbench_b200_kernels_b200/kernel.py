@@ -1,0 +1,153 @@
+"""Drop-in entry point for the FP8 gate/up projection with fused SwiGLU.
+
+``run`` has the signature, tensor layouts, destination-passing style and stream
+behaviour of the reference submission's entry point
+(kernels/179_fp8_mlp_gate_up_projection/kernel.py:398-407 and
+solution.json:14,20): seven positional tensors, the last one written in place,
+launched on torch's current CUDA stream.  Where the reference launches two
+block-scaled GEMMs and an elementwise SwiGLU kernel (kernel.py:487-503), this
+makes one call into libgateup.so, which launches one fused sm_100a kernel.
+
+PyTorch is used for device memory, streams and nothing else.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from . import _cabi
+from ._cabi import PLAN_AUTO, PLAN_STREAM, PLAN_TILE, GuProblem
+
+BLOCK = 128
+_PLANS = {"auto": PLAN_AUTO, "tile": PLAN_TILE, "stream": PLAN_STREAM}
+
+# Scratch for the stream-K hand-off, one buffer per (device, stream): it is
+# written and consumed inside a single call and carries no result across calls.
+_WORKSPACES: Dict[Tuple[int, int], torch.Tensor] = {}
+
+
+def select_plan(m: int, k: int, n: int) -> str:
+    """Name of the kernel the heuristic picks for a shape ('tile' or 'stream').
+
+    Counterpart of the reference's `_select_config` (kernel.py:232-249), which has
+    no small-M branch; here M <= 64 streams the weights with stream-K.
+    """
+    code = _cabi.lib.gu_select_plan(m, k, n)
+    _cabi.check(min(code, 0))
+    return _cabi.PLAN_NAMES[code]
+
+
+def _validate(x, scale_x, gate_w, scale_gate, up_w, scale_up, output) -> Tuple[int, int, int]:
+    """Same checks as the reference's `_debug_validate` / pybind `run`
+    (kernel.py:345-395, variants/cuda_cpp_v4/binding.cpp:26-72), for any K, N
+    multiple of 128 and any M >= 1; always on."""
+    if x.dim() != 2 or gate_w.dim() != 2 or up_w.dim() != 2 or output.dim() != 2:
+        raise ValueError("x, gate_proj_weight, up_proj_weight and output must be 2-D")
+    m, k = x.shape
+    n = gate_w.shape[0]
+    if m < 1 or k % BLOCK or n % BLOCK or k < BLOCK or n < BLOCK:
+        raise ValueError(f"Unsupported contract shape M={m}, K={k}, N={n}: need M >= 1 and K, N multiples of {BLOCK}")
+    kb, nb = k // BLOCK, n // BLOCK
+    expected = {
+        "x": (x, (m, k), torch.float8_e4m3fn),
+        "scale_x": (scale_x, (m, kb), torch.float32),
+        "gate_proj_weight": (gate_w, (n, k), torch.float8_e4m3fn),
+        "scale_gate": (scale_gate, (nb, kb), torch.float32),
+        "up_proj_weight": (up_w, (n, k), torch.float8_e4m3fn),
+        "scale_up": (scale_up, (nb, kb), torch.float32),
+        "output": (output, (m, n), torch.bfloat16),
+    }
+    for name, (t, shape, dtype) in expected.items():
+        if tuple(t.shape) != shape or t.dtype != dtype:
+            raise ValueError(f"{name}: expected shape={shape}, dtype={dtype}; "
+                             f"got shape={tuple(t.shape)}, dtype={t.dtype}")
+        if not t.is_cuda:
+            raise ValueError(f"{name} must be a CUDA tensor (this package has no CPU path)")
+        if t.device != x.device:
+            raise ValueError(f"{name} is on {t.device}, x is on {x.device}")
+        if name != "output" and not t.is_contiguous():
+            raise ValueError(f"{name} must be contiguous")
+    # output may be a column slice of a wider row-major buffer (sharded writes)
+    if output.stride(1) != 1 or output.stride(0) < n:
+        raise ValueError("output must be row-major with unit column stride")
+    return m, k, n
+
+
+def _workspace(device: torch.device, stream_ptr: int, nbytes: int) -> Optional[torch.Tensor]:
+    if nbytes == 0:
+        return None
+    key = (device.index if device.index is not None else torch.cuda.current_device(), stream_ptr)
+    ws = _WORKSPACES.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        _cabi.check(_cabi.lib.gu_workspace_init(ws.data_ptr(), nbytes, stream_ptr))
+        _WORKSPACES[key] = ws
+    return ws
+
+
+def _launch(x, scale_x, gate_w, scale_gate, up_w, scale_up, output, plan: str) -> None:
+    m, k, n = _validate(x, scale_x, gate_w, scale_gate, up_w, scale_up, output)
+    plan_id = _PLANS[plan]
+    with torch.cuda.device(x.device):
+        stream_ptr = torch.cuda.current_stream(x.device).cuda_stream
+        nbytes = _cabi.lib.gu_workspace_bytes(m, k, n, plan_id)
+        ws = _workspace(x.device, stream_ptr, nbytes)
+        pr = GuProblem(
+            x.data_ptr(), scale_x.data_ptr(), gate_w.data_ptr(), scale_gate.data_ptr(),
+            up_w.data_ptr(), scale_up.data_ptr(), output.data_ptr(),
+            m, k, n, output.stride(0),
+            ws.data_ptr() if ws is not None else None, nbytes, plan_id, 0)
+        code = _cabi.lib.gu_run(ctypes.byref(pr), stream_ptr)
+    if code != _cabi.GU_OK:
+        if code in (_cabi.GU_EINVAL_NULL, _cabi.GU_EINVAL_SHAPE, _cabi.GU_EINVAL_ALIGN, _cabi.GU_EINVAL_PLAN):
+            raise ValueError(f"libgateup: {_cabi.error_string(code)} (code {code})")
+        raise _cabi.GateUpError(code, _cabi.error_string(code))
+
+
+@torch.no_grad()
+def run(x: torch.Tensor, scale_x: torch.Tensor, gate_proj_weight: torch.Tensor, scale_gate: torch.Tensor,
+        up_proj_weight: torch.Tensor, scale_up: torch.Tensor, output: torch.Tensor) -> None:
+    """output[M, N] (bf16) = SiLU(x @ gate^T) * (x @ up^T) with block-scaled e4m3 operands.
+
+    Same arguments as the reference `run` (kernel.py:398-407).  Raises ValueError
+    for a shape, dtype, device or layout outside the contract.
+    """
+    _launch(x, scale_x, gate_proj_weight, scale_gate, up_proj_weight, scale_up, output, "auto")
+
+
+@torch.no_grad()
+def run_with_plan(x, scale_x, gate_proj_weight, scale_gate, up_proj_weight, scale_up, output, plan: str) -> None:
+    """`run` with the kernel forced ('tile', 'stream' or 'auto'); used by the M-sweep study and the tests."""
+    if plan not in _PLANS:
+        raise ValueError(f"unknown plan {plan!r}")
+    _launch(x, scale_x, gate_proj_weight, scale_gate, up_proj_weight, scale_up, output, plan)
+
+
+@torch.no_grad()
+def run_concat(x: torch.Tensor, scale_x: torch.Tensor, w: torch.Tensor, scale_w: torch.Tensor,
+               output: torch.Tensor) -> None:
+    """Same op with concatenated weights W[2N, K] (gate rows first) and scales [2N/128, K/128].
+
+    Row-major halves are contiguous views, so this slices and forwards to `run`.
+    """
+    if w.dim() != 2 or w.shape[0] % (2 * BLOCK):
+        raise ValueError("w must be [2N, K] with N a multiple of 128")
+    n = w.shape[0] // 2
+    nb = n // BLOCK
+    if scale_w.dim() != 2 or scale_w.shape[0] != 2 * nb:
+        raise ValueError(f"scale_w: expected {2 * nb} rows, got {tuple(scale_w.shape)}")
+    run(x, scale_x, w[:n], scale_w[:nb], w[n:], scale_w[nb:], output)
+
+
+def last_status(clear: bool = True) -> Tuple[int, int]:
+    """(code, detail) of the device-side status word; synchronises the device."""
+    detail = ctypes.c_int(0)
+    code = _cabi.lib.gu_last_status(ctypes.byref(detail), 1 if clear else 0)
+    return code, detail.value
+
+
+def launch_count() -> int:
+    """Kernel launches made by libgateup.so in this process."""
+    return int(_cabi.lib.gu_launch_count())

@@ -1,0 +1,91 @@
+"""Column-parallel sharding of the intermediate dimension N across the GPUs of one box.
+
+Output column n depends only on gate row n and up row n, so rank r of R owns
+the row range [r*N/R, (r+1)*N/R) of both weight matrices and of both scale
+grids, x and scale_x are replicated, and each rank produces output[:, its
+columns] with no reduction and no data-path collective.  The reference is
+single-GPU only; this is the multi-GPU layer added on top of its entry point.
+
+An all-gather over NCCL (NVLink / NVSwitch) runs only when a contiguous [M, N]
+result is asked for.  NCCL gathers contiguous buffers, so ranks exchange their
+[M, N/R] slices into a rank-major [R, M, N/R] buffer that is then permuted into
+row-major [M, N] locally.
+
+One process per GPU; `group=None` means the default process group.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+BLOCK = 128
+
+
+def shard_bounds(n: int, rank: int, world: int) -> Tuple[int, int]:
+    """[start, stop) of the output columns rank `rank` owns; shards are whole 128-column scale blocks."""
+    if n % BLOCK:
+        raise ValueError(f"N={n} is not a multiple of {BLOCK}")
+    nb = n // BLOCK
+    if world < 1 or not 0 <= rank < world:
+        raise ValueError(f"bad rank/world {rank}/{world}")
+    if nb % world:
+        raise ValueError(f"N/128 = {nb} column blocks do not divide over {world} ranks")
+    per = nb // world
+    return rank * per * BLOCK, (rank + 1) * per * BLOCK
+
+
+def shard_weights(gate_w: torch.Tensor, scale_gate: torch.Tensor, up_w: torch.Tensor, scale_up: torch.Tensor,
+                  rank: int, world: int):
+    """This rank's row ranges of the four weight-side tensors (contiguous views, no copy)."""
+    n = gate_w.shape[0]
+    lo, hi = shard_bounds(n, rank, world)
+    blo, bhi = lo // BLOCK, hi // BLOCK
+    return gate_w[lo:hi], scale_gate[blo:bhi], up_w[lo:hi], scale_up[blo:bhi]
+
+
+def shard_concat_weights(w: torch.Tensor, scale_w: torch.Tensor, rank: int, world: int):
+    """Same for concatenated W[2N, K]: the shard is two row ranges, returned as (gate, sg, up, su) views."""
+    n = w.shape[0] // 2
+    nb = n // BLOCK
+    return shard_weights(w[:n], scale_w[:nb], w[n:], scale_w[nb:], rank, world)
+
+
+def assemble_gathered(gathered: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Rank-major [R, M, N/R] -> row-major [M, N]."""
+    r, m, ns = gathered.shape
+    if out is None:
+        out = torch.empty(m, r * ns, dtype=gathered.dtype, device=gathered.device)
+    out.view(m, r, ns).copy_(gathered.transpose(0, 1))
+    return out
+
+
+def gather_columns(local: torch.Tensor, group=None, out: Optional[torch.Tensor] = None,
+                   scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """All-gather every rank's [M, N/R] slice and return the contiguous [M, N] result."""
+    world = dist.get_world_size(group)
+    m, ns = local.shape
+    if scratch is None:
+        scratch = torch.empty(world, m, ns, dtype=local.dtype, device=local.device)
+    dist.all_gather_into_tensor(scratch.view(world * m, ns), local.contiguous(), group=group)
+    return assemble_gathered(scratch, out)
+
+
+@torch.no_grad()
+def run_sharded(x: torch.Tensor, scale_x: torch.Tensor, gate_shard: torch.Tensor, scale_gate_shard: torch.Tensor,
+                up_shard: torch.Tensor, scale_up_shard: torch.Tensor, output_shard: torch.Tensor,
+                group=None, gather: bool = False, gathered_out: Optional[torch.Tensor] = None,
+                scratch: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """One rank's part of the column-parallel op.
+
+    `*_shard` are this rank's slices (see `shard_weights`), `output_shard` is bf16
+    [M, N/R].  With `gather=True` returns the contiguous [M, N] tensor (NCCL
+    all-gather + local permute); otherwise returns None and nothing is exchanged.
+    """
+    from .kernel import run  # needs the CUDA library; kept out of the index helpers above
+
+    run(x, scale_x, gate_shard, scale_gate_shard, up_shard, scale_up_shard, output_shard)
+    if not gather:
+        return None
+    return gather_columns(output_shard, group=group, out=gathered_out, scratch=scratch)
