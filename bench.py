@@ -1,0 +1,381 @@
+#!/usr/bin/env python
+"""Benchmark of the FP8 gate/up + SwiGLU hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME] [--gather]
+
+A step is one pass of the fused op over one synthetic workload (seeded
+N(0,1) activations, N(0,0.02) weights, e4m3 block quantisation).
+
+  N = 1   workload "prefill_8b"  (M=4096, K=4096, N=14336; tensor-bound), plus the
+          decode shape (M=16, K=8192, N=28672; HBM-bound) reported under "also".
+  N > 1   workload "prefill_sharded" (M=16384, K=7168, N=18432) with the intermediate
+          dimension column-sharded over the ranks (torchrun, one process per GPU);
+          no data-path collective unless --gather asks for the contiguous output.
+
+Prints ONE JSON line on rank 0.  `--impl reference` times the CPU restatement of
+the reference's definition (dequantise, fp32 matmul, SwiGLU) on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+METRIC = "FP8 gate/up+SwiGLU TFLOP/s & HBM GB/s vs roofline at 1/2/4/8 B200"
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+L2_FLUSH_BYTES = 256 << 20  # written between timed iterations; B200 L2 is 126 MB
+
+# Measured DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum from the ncu
+# captures summarised under profiles/), keyed by workload; None until a capture exists.
+NCU_TRAFFIC_BYTES = {}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        p["_source"] = "measured"
+        return p
+    p = dict(FALLBACK_PEAKS)
+    p["_source"] = "fallback"
+    return p
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.samples = []
+        self._stop = threading.Event()
+        self._thread = None
+
+    def _loop(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(
+                    ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits"],
+                    capture_output=True, text=True, timeout=5).stdout.strip()
+                if out:
+                    self.samples.append([c.strip() for c in out.splitlines()[0].split(",")])
+            except Exception:
+                pass
+            self._stop.wait(0.05)
+
+    def __enter__(self):
+        self._thread = threading.Thread(target=self._loop, daemon=True)
+        self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        self._thread.join(timeout=10)
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            try:
+                sm.append(float(s[1]))
+                mx.append(float(s[2]))
+            except (ValueError, IndexError):
+                continue
+            for name, val in zip(names, s[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------------------
+# GPU arm
+# --------------------------------------------------------------------------------------
+def time_device_steps(fn, steps: int, warmup: int, flush: torch.Tensor, barrier=None):
+    """Per-step CUDA-event timing on the current stream, L2 flushed before every step."""
+    for _ in range(warmup):
+        flush.zero_()
+        fn()
+    torch.cuda.synchronize()
+    if barrier is not None:
+        barrier()
+    torch.cuda.synchronize()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    stops = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    for i in range(steps):
+        flush.zero_()
+        starts[i].record()
+        fn()
+        stops[i].record()
+    torch.cuda.synchronize()
+    if barrier is not None:
+        barrier()
+    torch.cuda.synchronize()
+    per = [s.elapsed_time(e) for s, e in zip(starts, stops)]
+    return sum(per), per
+
+
+def roofline_for(m, k, n, ms, peaks, W):
+    flops = W.algorithmic_flops(m, k, n)
+    nbytes = W.algorithmic_bytes(m, k, n)
+    fp8_peak = 2.0 * peaks["bf16_tflops"]       # dense FP8 = 2x the measured dense bf16 burst rate
+    t_tensor = flops / (fp8_peak * 1e12)
+    t_hbm = nbytes / (peaks["hbm_gbs"] * 1e9)
+    src = "of measured" if peaks["_source"] == "measured" else "of fallback"
+    if t_tensor >= t_hbm:
+        achieved = flops / (ms * 1e-3) / 1e12
+        return {"bound": "tensor", "achieved": round(achieved, 2), "peak": round(fp8_peak, 1), "unit": "TFLOP/s",
+                "frac": round(achieved / fp8_peak, 4), "traffic": None,
+                "peak_source": f"2 x bf16_tflops burst, {src}", "algorithmic_flops": flops}
+    achieved = nbytes / (ms * 1e-3) / 1e9
+    return {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+            "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": None,
+            "peak_source": f"hbm_gbs, {src}", "algorithmic_bytes": nbytes}
+
+
+def cpu_baseline(inp_cpu, oracle, max_flops: float = 2.0e12):
+    """Oracle (dequant, fp32 matmul, SwiGLU) on the host cores over a bounded row sample of the workload."""
+    m, k, n = inp_cpu.shape
+    rows = int(min(m, max(64, max_flops // (4 * k * n))))
+    oracle.gateup_dequant(*inp_cpu.rows(torch.arange(min(m, 16))).args())  # untimed warm pass (thread pool, pages)
+    sub = inp_cpu if rows == m else inp_cpu.rows(torch.arange(rows))
+    timings = {}
+    oracle.gateup_dequant(*sub.args(), timings=timings)
+    flops = 4.0 * rows * k * n
+    return {
+        "value": round(flops / timings["total_s"] / 1e12, 4), "unit": "TFLOP/s",
+        "cores": torch.get_num_threads(), "host_cpus": os.cpu_count(), "kind": "port",
+        "sample": f"rows 0..{rows - 1} of M={m} (K={k}, N={n}), one timed pass, weights dequantised inside the pass",
+        "seconds": round(timings["total_s"], 3),
+        "phases_s": {p: round(timings[p], 3) for p in ("dequant_s", "matmul_s", "swiglu_s")},
+    }
+
+
+def run_ours(args):
+    import torch.distributed as dist
+
+    import sol_execbench_b200_kernels_b200 as pkg
+    from sol_execbench_b200_kernels_b200 import workloads as W
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; this library has no CPU path (use --impl reference for the CPU baseline)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    n_gpus = world
+    peaks = load_peaks()
+
+    workload = args.workload or ("prefill_8b" if n_gpus == 1 else "prefill_sharded")
+    m, k, n = W.SHAPES[workload]
+    # every rank draws the same seeded workload on its GPU and keeps its own column shard
+    full = W.make_inputs(m, k, n, seed=0, device=dev)
+    if n_gpus > 1:
+        gw, sg, uw, su = pkg.shard_weights(full.gate_proj_weight, full.scale_gate, full.up_proj_weight,
+                                           full.scale_up, rank, world)
+        gw, sg, uw, su = (t.clone() for t in (gw, sg, uw, su))
+        local = W.GateUpInputs(full.x, full.scale_x, gw, sg, uw, su)
+        del full
+        torch.cuda.empty_cache()
+    else:
+        local = full
+    n_local = local.gate_proj_weight.shape[0]
+    out = torch.empty(m, n_local, dtype=torch.bfloat16, device=dev)
+    flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
+    gathered = torch.empty(m, n, dtype=torch.bfloat16, device=dev) if (args.gather and n_gpus > 1) else None
+    scratch = torch.empty(world, m, n_local, dtype=torch.bfloat16, device=dev) if gathered is not None else None
+
+    def step():
+        pkg.run_sharded(*local.args(), out, gather=gathered is not None, gathered_out=gathered, scratch=scratch) \
+            if n_gpus > 1 else pkg.run(*local.args(), out)
+
+    barrier = (lambda: dist.barrier()) if n_gpus > 1 else None
+    launches0 = pkg.launch_count()
+    with ClockSampler(local_rank) as clocks:
+        total_ms, per = time_device_steps(step, args.steps, args.warmup, flush, barrier)
+        # keep the GPU busy long enough for a few clock samples when the steps are very short
+        t_end = time.perf_counter() + max(0.0, 0.4 - total_ms * 1e-3)
+        while time.perf_counter() < t_end:
+            step()
+        torch.cuda.synchronize()
+    launches_timed = args.steps  # one fused kernel per step (pkg.launch_count() confirms below)
+    assert pkg.launch_count() - launches0 >= args.steps + args.warmup
+    code, detail = pkg.last_status()
+    if code != 0:
+        raise SystemExit(f"bench.py: device status {code} detail {detail:#x}")
+
+    t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
+    if n_gpus > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms = float(t.item())
+    ms_per_step = total_ms / args.steps
+    flops_job = W.algorithmic_flops(m, k, n)
+    value = flops_job / (ms_per_step * 1e-3) / 1e12
+
+    # ---- end to end through the public entry point: pinned host activations in, host result out ----
+    x_host = local.x.cpu().view(torch.uint8).pin_memory()
+    sx_host = local.scale_x.cpu().pin_memory()
+    out_host = torch.empty(m, n_local, dtype=torch.bfloat16).pin_memory()
+    x_dev = torch.empty_like(local.x)
+    sx_dev = torch.empty_like(local.scale_x)
+
+    def e2e_step():
+        x_dev.view(torch.uint8).copy_(x_host, non_blocking=True)
+        sx_dev.copy_(sx_host, non_blocking=True)
+        pkg.run(x_dev, sx_dev, local.gate_proj_weight, local.scale_gate, local.up_proj_weight, local.scale_up, out)
+        out_host.copy_(out, non_blocking=True)
+
+    for _ in range(max(1, args.warmup // 2)):
+        e2e_step()
+    torch.cuda.synchronize()
+    if barrier:
+        barrier()
+    e2e_steps = max(3, min(args.steps, 10))
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    te = torch.tensor([e2e_s], dtype=torch.float64, device=dev)
+    if n_gpus > 1:
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+    e2e_s = float(te.item())
+    h2d = x_host.numel() + sx_host.numel() * 4
+    d2h = out_host.numel() * 2
+    e2e = {"value": round(flops_job / (e2e_s / e2e_steps) / 1e12, 3), "unit": "TFLOP/s",
+           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+           "note": "weights resident in HBM; x and scale_x copied from pinned host memory and the bf16 output "
+                   "copied back to pinned host memory every step, wall clock"}
+
+    result = None
+    if rank == 0:
+        roof = roofline_for(m, k, n_local, ms_per_step, peaks, W)
+        roof["traffic"] = NCU_TRAFFIC_BYTES.get(workload)
+        result = {
+            "metric": METRIC, "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": n_gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 5),
+            "higher_is_better": True, "scaling": "strong" if n_gpus > 1 or workload == "prefill_sharded" else "weak",
+            "vs_baseline": None, "dtype": "fp8_e4m3 x fp8_e4m3 -> f32 accumulate -> bf16", "data": "synthetic",
+            "config": {"workload": f"{workload}: M={m} K={k} N={n}", "sharding": f"N column-sharded over {n_gpus}" if n_gpus > 1 else "none",
+                       "per_rank_n": n_local, "plan": pkg.select_plan(m, k, n_local),
+                       "gather": bool(gathered is not None),
+                       "l2": f"flushed between timed steps by writing a {L2_FLUSH_BYTES >> 20} MiB buffer"},
+            "roofline": roof, "e2e": e2e, "gpu_launches": launches_timed,
+            "clocks": clocks.summary(),
+        }
+
+    # ---- decode shape (HBM-bound) and CPU baseline: rank 0, single-GPU runs only ----
+    if n_gpus == 1 and not args.workload:
+        dm, dk, dn = W.SHAPES["decode_70b"]
+        del local, out, x_dev, sx_dev
+        torch.cuda.empty_cache()
+        dec = W.make_inputs(dm, dk, dn, seed=0, device=dev)
+        dout = torch.empty(dm, dn, dtype=torch.bfloat16, device=dev)
+        dsteps = max(args.steps, 20)
+        dms, _ = time_device_steps(lambda: pkg.run(*dec.args(), dout), dsteps, max(args.warmup, 3), flush)
+        droof = roofline_for(dm, dk, dn, dms / dsteps, peaks, W)
+        droof["traffic"] = NCU_TRAFFIC_BYTES.get("decode_70b")
+        result["also"] = [{
+            "workload": f"decode_70b: M={dm} K={dk} N={dn}", "plan": pkg.select_plan(dm, dk, dn),
+            "ms_per_step": round(dms / dsteps, 5), "steps": dsteps,
+            "tflops": round(W.algorithmic_flops(dm, dk, dn) / (dms / dsteps * 1e-3) / 1e12, 2),
+            "roofline": droof}]
+        del dec, dout
+        torch.cuda.empty_cache()
+        sm_, sk_, sn_ = W.SHAPES["prefill_sharded"]
+        big = W.make_inputs(sm_, sk_, sn_, seed=0, device=dev)
+        bout = torch.empty(sm_, sn_, dtype=torch.bfloat16, device=dev)
+        bsteps = 5
+        bms, _ = time_device_steps(lambda: pkg.run(*big.args(), bout), bsteps, 3, flush)
+        result["also"].append({
+            "workload": f"prefill_sharded on one GPU: M={sm_} K={sk_} N={sn_}", "plan": pkg.select_plan(sm_, sk_, sn_),
+            "ms_per_step": round(bms / bsteps, 5), "steps": bsteps,
+            "tflops": round(W.algorithmic_flops(sm_, sk_, sn_) / (bms / bsteps * 1e-3) / 1e12, 2),
+            "roofline": roofline_for(sm_, sk_, sn_, bms / bsteps, peaks, W)})
+        del big, bout
+        torch.cuda.empty_cache()
+        from oracle import gateup_oracle as oracle  # CPU baseline leg: the only use of the checker here
+
+        cpu_inp = W.make_inputs(m, k, n, seed=0, device="cpu")
+        result["cpu_baseline"] = cpu_baseline(cpu_inp, oracle)
+    if rank == 0:
+        print(json.dumps(result), flush=True)
+    if n_gpus > 1:
+        dist.destroy_process_group()
+
+
+# --------------------------------------------------------------------------------------
+# reference arm: the CPU definition (dequantise, fp32 matmul, SwiGLU) on the host cores
+# --------------------------------------------------------------------------------------
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if rank != 0:
+        return
+    from oracle import gateup_oracle as oracle
+    from sol_execbench_b200_kernels_b200 import workloads as W
+
+    n_gpus = max(world, args.gpus)
+    workload = args.workload or ("prefill_8b" if n_gpus == 1 else "prefill_sharded")
+    m, k, n = W.SHAPES[workload]
+    # bounded sample: a row block of the workload, sized so warmup + steps stay within minutes
+    rows = min(m, 1024)
+    inp = W.make_inputs(rows, k, n, seed=0, device="cpu")
+    for _ in range(args.warmup):
+        oracle.gateup_dequant(*inp.args())
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        oracle.gateup_dequant(*inp.args())
+    dt = (time.perf_counter() - t0) / args.steps
+    value = 4.0 * rows * k * n / dt / 1e12
+    sample = (f"{rows} token rows of {workload} (M={m}, K={k}, N={n}) per step; weights dequantised inside every "
+              f"step as the CPU definition does; throughput is per-row-proportional for the matmul part")
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": round(value, 4), "unit": "TFLOP/s", "n_gpus": n_gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True,
+        "scaling": "strong" if n_gpus > 1 else "weak", "vs_baseline": None, "dtype": "f32 (dequantised e4m3)",
+        "data": "synthetic", "config": {"workload": f"{workload}: M={m} K={k} N={n}", "sample_rows": rows},
+        "cpu_baseline": {"value": round(value, 4), "unit": "TFLOP/s", "cores": torch.get_num_threads(),
+                         "host_cpus": os.cpu_count(), "kind": "port", "sample": sample},
+        "e2e": {"value": round(value, 4), "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--workload", default=None, help="override: one of workloads.SHAPES")
+    ap.add_argument("--gather", action="store_true", help="N>1: also all-gather the contiguous [M, N] output")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -63,6 +63,7 @@ def _validate(x, scale_x, gate_w, scale_gate, up_w, scale_up, output) -> Tuple[i
         if tuple(t.shape) != shape or t.dtype != dtype:
             raise ValueError(f"{name}: expected shape={shape}, dtype={dtype}; "
                              f"got shape={tuple(t.shape)}, dtype={t.dtype}")
+    for name, (t, shape, dtype) in expected.items():
         if not t.is_cuda:
             raise ValueError(f"{name} must be a CUDA tensor (this package has no CPU path)")
         if t.device != x.device:

@@ -1,0 +1,123 @@
+"""Host-side checks that need no GPU: the library loads, exports what include/gateup.h
+declares, validates arguments before touching CUDA, and the Python entry point refuses CPU tensors."""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "gateup.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(gu_[a-z_]+)\s*\(", text)))
+
+
+def test_header_symbols_all_exported(gateup_lib):
+    declared = _declared_symbols()
+    assert "gu_run" in declared and len(declared) >= 9
+    for name in declared:
+        assert hasattr(gateup_lib.lib, name), f"{name} declared in gateup.h but not exported"
+    assert sorted(gateup_lib.EXPORTS) == declared
+
+
+def test_version_and_error_strings(gateup_lib):
+    assert gateup_lib.lib.gu_version() == 1
+    for code in range(0, -9, -1):
+        msg = gateup_lib.error_string(code)
+        assert msg and msg != "unknown error"
+    assert gateup_lib.error_string(-99) == "unknown error"
+
+
+def test_struct_layout_matches_header(gateup_lib):
+    # 7 pointers, 4 int64, pointer, size_t, 2 int32 -> 8-byte fields throughout
+    assert ctypes.sizeof(gateup_lib.GuProblem) == 7 * 8 + 4 * 8 + 8 + 8 + 8
+
+
+@pytest.mark.parametrize("shape,plan", [
+    ((16, 8192, 28672), "stream"), ((1, 4096, 14336), "stream"), ((64, 4096, 14336), "stream"),
+    ((65, 4096, 14336), "tile"), ((128, 2048, 5632), "tile"), ((4096, 4096, 14336), "tile"),
+    ((16384, 7168, 18432), "tile"),
+])
+def test_plan_heuristic(gateup_lib, shape, plan):
+    code = gateup_lib.lib.gu_select_plan(*shape)
+    assert gateup_lib.PLAN_NAMES[code] == plan
+
+
+@pytest.mark.parametrize("shape", [(0, 128, 128), (4, 100, 128), (4, 128, 200), (4, 0, 128), (-1, 128, 128)])
+def test_plan_rejects_bad_shapes(gateup_lib, shape):
+    assert gateup_lib.lib.gu_select_plan(*shape) == gateup_lib.GU_EINVAL_SHAPE
+    assert gateup_lib.lib.gu_workspace_bytes(*shape, 0) == 0
+
+
+def test_workspace_sizes(gateup_lib):
+    lib = gateup_lib.lib
+    assert lib.gu_workspace_bytes(4096, 4096, 14336, gateup_lib.PLAN_AUTO) == 0
+    assert lib.gu_workspace_bytes(4096, 4096, 14336, gateup_lib.PLAN_TILE) == 0
+    w16 = lib.gu_workspace_bytes(16, 8192, 28672, gateup_lib.PLAN_AUTO)
+    w64 = lib.gu_workspace_bytes(64, 8192, 28672, gateup_lib.PLAN_STREAM)
+    assert w16 == 4096 + 256 * 2 * 16 * 128 * 4
+    assert w64 == 4096 + 256 * 2 * 64 * 128 * 4
+
+
+def _problem(gateup_lib, **over):
+    base = dict(x=0x1000, scale_x=0x2000, gate_w=0x3000, scale_gate=0x4000, up_w=0x5000, scale_up=0x6000,
+                output=0x7000, m=128, k=128, n=128, ld_output=128, workspace=None, workspace_bytes=0,
+                plan=gateup_lib.PLAN_TILE, reserved=0)
+    base.update(over)
+    return gateup_lib.GuProblem(**base)
+
+
+def test_argument_validation_precedes_any_cuda_call(gateup_lib):
+    lib = gateup_lib.lib
+    assert lib.gu_run(None, None) == gateup_lib.GU_EINVAL_NULL
+    for field in ("x", "scale_x", "gate_w", "scale_gate", "up_w", "scale_up", "output"):
+        pr = _problem(gateup_lib, **{field: None})
+        assert lib.gu_run(ctypes.byref(pr), None) == gateup_lib.GU_EINVAL_NULL, field
+    assert lib.gu_run(ctypes.byref(_problem(gateup_lib, k=130)), None) == gateup_lib.GU_EINVAL_SHAPE
+    assert lib.gu_run(ctypes.byref(_problem(gateup_lib, n=64)), None) == gateup_lib.GU_EINVAL_SHAPE
+    assert lib.gu_run(ctypes.byref(_problem(gateup_lib, m=0)), None) == gateup_lib.GU_EINVAL_SHAPE
+    assert lib.gu_run(ctypes.byref(_problem(gateup_lib, ld_output=64)), None) == gateup_lib.GU_EINVAL_SHAPE
+    assert lib.gu_run(ctypes.byref(_problem(gateup_lib, x=0x1001)), None) == gateup_lib.GU_EINVAL_ALIGN
+    assert lib.gu_run(ctypes.byref(_problem(gateup_lib, ld_output=132)), None) == gateup_lib.GU_EINVAL_ALIGN
+    assert lib.gu_run(ctypes.byref(_problem(gateup_lib, plan=7)), None) == gateup_lib.GU_EINVAL_PLAN
+    assert lib.gu_run_concat(0x1000, 0x2000, None, 0x4000, 0x7000, 128, 128, 128, 128, None, 0, 0, None) \
+        == gateup_lib.GU_EINVAL_NULL
+
+
+@pytest.mark.skipif(torch.cuda.is_available(), reason="CPU-only check")
+def test_valid_problem_without_a_gpu_fails_loudly(gateup_lib):
+    # nothing to fall back to: a well-formed call on a machine without a device is an error, not a CPU result
+    code = gateup_lib.lib.gu_run(ctypes.byref(_problem(gateup_lib)), None)
+    assert code in (gateup_lib.GU_ECUDA, gateup_lib.GU_EDEVICE)
+
+
+def test_python_entry_point_refuses_cpu_tensors(gateup_lib):
+    import sol_execbench_b200_kernels_b200 as pkg
+    from sol_execbench_b200_kernels_b200 import workloads as W
+
+    inp = W.make_inputs(4, 128, 128, seed=0)
+    out = torch.empty(4, 128, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="CUDA"):
+        pkg.run(*inp.args(), out)
+
+
+def test_python_entry_point_shape_and_dtype_errors(gateup_lib):
+    import sol_execbench_b200_kernels_b200 as pkg
+    from sol_execbench_b200_kernels_b200 import workloads as W
+
+    inp = W.make_inputs(4, 128, 128, seed=0)
+    out = torch.empty(4, 128, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="output"):
+        pkg.run(*inp.args(), out.float())
+    with pytest.raises(ValueError, match="scale_x"):
+        pkg.run(inp.x, inp.scale_x[:, :0], *inp.args()[2:], out)
+    with pytest.raises(ValueError, match="Unsupported contract shape"):
+        pkg.run(inp.x[:, :100], *inp.args()[1:], out)
+    with pytest.raises(ValueError):
+        pkg.run_concat(inp.x, inp.scale_x, torch.empty(100, 128, dtype=torch.float8_e4m3fn), inp.scale_gate, out)
+    with pytest.raises(ValueError, match="unknown plan"):
+        pkg.run_with_plan(*inp.args(), out, "fastest")

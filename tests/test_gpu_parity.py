@@ -1,0 +1,280 @@
+"""GPU parity tests: the CUDA path, called through the Python entry point and the C ABI,
+against the CPU oracle on the same seeded inputs.
+
+Tolerances (on bf16 outputs, as the path's contract states them):
+    max-abs error <= 2e-2  and  relative-L2 error <= 1e-2
+against the oracle in the kernels' own accumulation order (`gateup_blockwise`).  Against the
+dequantise-then-matmul oracle (`gateup_dequant`) the same relative-L2 bound holds, and max-abs
+holds for every element except isolated bf16 rounding flips: where |ref| >= 4 one bf16 ulp is
+0.03125 > 2e-2, so two correct fp32 sums that differ in the last bit can land one or two ulps
+apart.  Those are bounded by `MAX_FLIP_ULPS` and `MAX_FLIP_FRACTION` below.
+"""
+import ctypes
+
+import pytest
+import torch
+
+from oracle import gateup_oracle as O
+from sol_execbench_b200_kernels_b200 import workloads as W
+
+pytestmark = pytest.mark.gpu
+
+ATOL = 2e-2
+REL_L2 = 1e-2
+MAX_FLIP_ULPS = 4.0
+MAX_FLIP_FRACTION = 2e-5
+
+
+@pytest.fixture(scope="module")
+def pkg():
+    import sol_execbench_b200_kernels_b200 as p
+
+    assert torch.cuda.is_available()
+    p.last_status(clear=True)
+    return p
+
+
+def _run(pkg, inp, plan="auto", out=None):
+    dev = torch.device("cuda:0")
+    g = inp.to(dev)
+    m, _, n = inp.shape
+    if out is None:
+        out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=dev)
+    pkg.run_with_plan(*g.args(), out, plan)
+    torch.cuda.synchronize()
+    code, detail = pkg.last_status()
+    assert code == 0, f"device status {code}, detail {detail:#x}"
+    return out
+
+
+def _check(out, inp, label=""):
+    blk = O.gateup_blockwise(*inp.args())
+    st = O.error_stats(out, blk)
+    assert st["finite"] and not st["all_zero"], (label, st)
+    assert st["max_abs"] <= ATOL and st["rel_l2"] <= REL_L2, (label, "vs blockwise", st)
+    deq = O.gateup_dequant(*inp.args())
+    sd = O.error_stats(out, deq)
+    assert sd["rel_l2"] <= REL_L2, (label, "vs dequant", sd)
+    if sd["max_abs"] > ATOL:
+        # only isolated bf16 flips at magnitudes where one ulp exceeds the tolerance
+        assert sd["min_abs_ref_over"] >= 2.0 and sd["max_ulp"] <= MAX_FLIP_ULPS, (label, sd)
+        assert sd["frac_over_atol"] <= MAX_FLIP_FRACTION, (label, sd)
+    return st, sd
+
+
+TILE_SHAPES = [(128, 128, 128), (128, 2048, 5632), (256, 1024, 512), (100, 384, 256), (129, 256, 384),
+               (300, 512, 384), (65, 640, 256), (1024, 3584, 1024), (640, 896, 2304)]
+STREAM_SHAPES = [(1, 128, 128), (1, 512, 384), (7, 2048, 5632), (16, 256, 256), (16, 1024, 1024), (17, 640, 384),
+                 (32, 1024, 512), (33, 512, 256), (48, 4096, 1792), (64, 1024, 1280), (16, 8192, 2048),
+                 (8, 384, 18944)]
+
+
+@pytest.mark.parametrize("shape", TILE_SHAPES)
+def test_tile_kernel_parity(pkg, shape):
+    inp = W.make_inputs(*shape, seed=1)
+    _check(_run(pkg, inp, "tile"), inp, f"tile {shape}")
+
+
+@pytest.mark.parametrize("shape", STREAM_SHAPES)
+def test_stream_kernel_parity(pkg, shape):
+    inp = W.make_inputs(*shape, seed=2)
+    _check(_run(pkg, inp, "stream"), inp, f"stream {shape}")
+
+
+@pytest.mark.parametrize("shape", [(1, 512, 384), (16, 1024, 1024), (64, 1024, 1280), (48, 4096, 1792)])
+def test_both_kernels_agree_bit_for_bit_on_small_m(pkg, shape):
+    # same block order, same fp32 FMA chain (stream-K splits fall on K-block boundaries and add in order)
+    inp = W.make_inputs(*shape, seed=3)
+    a = _run(pkg, inp, "tile")
+    b = _run(pkg, inp, "stream")
+    st = O.error_stats(a, b)
+    assert st["max_abs"] <= ATOL and st["rel_l2"] <= 1e-4, st
+
+
+def test_small_config_through_public_run(pkg):
+    m, k, n = W.SHAPES["small"]
+    inp = W.make_inputs(m, k, n, seed=0)
+    dev = torch.device("cuda:0")
+    g = inp.to(dev)
+    out = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+    before = pkg.launch_count()
+    assert pkg.run(*g.args(), out) is None
+    torch.cuda.synchronize()
+    assert pkg.launch_count() == before + 1          # one fused kernel, where the reference launches three
+    _check(out, inp, "small config")
+
+
+def test_deterministic(pkg):
+    for shape, plan in (((300, 512, 384), "tile"), ((16, 8192, 2048), "stream"), ((7, 2048, 5632), "stream")):
+        inp = W.make_inputs(*shape, seed=4)
+        a = _run(pkg, inp, plan).clone()
+        for _ in range(3):
+            assert torch.equal(a, _run(pkg, inp, plan))
+
+
+def test_output_padding_untouched_and_pitched_output(pkg):
+    # output as a column slice of a wider buffer: only [M, N] may be written
+    for shape, plan in (((100, 384, 256), "tile"), ((7, 512, 256), "stream")):
+        m, k, n = shape
+        inp = W.make_inputs(*shape, seed=5)
+        dev = torch.device("cuda:0")
+        wide = torch.full((m + 2, n + 256), 7.0, dtype=torch.bfloat16, device=dev)
+        view = wide[1:m + 1, 128:128 + n]
+        _run(pkg, inp, plan, out=view)
+        _check(view, inp, f"pitched {shape}")
+        mask = torch.ones_like(wide, dtype=torch.bool)
+        mask[1:m + 1, 128:128 + n] = False
+        assert (wide[mask] == 7.0).all()
+
+
+def test_run_concat_matches_run(pkg):
+    inp = W.make_inputs(40, 512, 384, seed=6)
+    dev = torch.device("cuda:0")
+    g = inp.to(dev)
+    w = torch.cat([g.gate_proj_weight.view(torch.uint8), g.up_proj_weight.view(torch.uint8)]).view(torch.float8_e4m3fn)
+    sw = torch.cat([g.scale_gate, g.scale_up])
+    a = torch.empty(40, 384, dtype=torch.bfloat16, device=dev)
+    b = torch.empty_like(a)
+    pkg.run(*g.args(), a)
+    pkg.run_concat(g.x, g.scale_x, w, sw, b)
+    torch.cuda.synchronize()
+    assert torch.equal(a, b)
+
+
+def test_c_abi_direct_call(pkg):
+    """gu_run / gu_run_concat with raw pointers, no Python wrapper in between."""
+    from sol_execbench_b200_kernels_b200 import _cabi
+
+    inp = W.make_inputs(16, 512, 512, seed=7)
+    dev = torch.device("cuda:0")
+    g = inp.to(dev)
+    out = torch.empty(16, 512, dtype=torch.bfloat16, device=dev)
+    nbytes = _cabi.lib.gu_workspace_bytes(16, 512, 512, _cabi.PLAN_STREAM)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    stream = torch.cuda.current_stream().cuda_stream
+    assert _cabi.lib.gu_workspace_init(ws.data_ptr(), nbytes, stream) == 0
+    pr = _cabi.GuProblem(g.x.data_ptr(), g.scale_x.data_ptr(), g.gate_proj_weight.data_ptr(), g.scale_gate.data_ptr(),
+                         g.up_proj_weight.data_ptr(), g.scale_up.data_ptr(), out.data_ptr(), 16, 512, 512, 512,
+                         ws.data_ptr(), nbytes, _cabi.PLAN_STREAM, 0)
+    assert _cabi.lib.gu_run(ctypes.byref(pr), stream) == 0
+    torch.cuda.synchronize()
+    _check(out, inp, "c abi stream")
+    # stream plan without scratch, or with M too large, is refused before any launch
+    pr.workspace = None
+    assert _cabi.lib.gu_run(ctypes.byref(pr), stream) == _cabi.GU_EWORKSPACE
+    pr.m = 65
+    assert _cabi.lib.gu_run(ctypes.byref(pr), stream) == _cabi.GU_EINVAL_PLAN
+    # concatenated weights through the C ABI
+    w = torch.cat([g.gate_proj_weight.view(torch.uint8), g.up_proj_weight.view(torch.uint8)])
+    sw = torch.cat([g.scale_gate, g.scale_up])
+    out2 = torch.empty_like(out)
+    assert _cabi.lib.gu_run_concat(g.x.data_ptr(), g.scale_x.data_ptr(), w.data_ptr(), sw.data_ptr(), out2.data_ptr(),
+                                   16, 512, 512, 512, ws.data_ptr(), nbytes, _cabi.PLAN_TILE, stream) == 0
+    torch.cuda.synchronize()
+    assert O.error_stats(out2, out)["max_abs"] <= ATOL
+
+
+def test_gpu_argument_errors(pkg):
+    inp = W.make_inputs(8, 256, 256, seed=8).to("cuda:0")
+    out = torch.empty(8, 256, dtype=torch.bfloat16, device="cuda:0")
+    with pytest.raises(ValueError, match="contiguous"):
+        pkg.run(inp.x, inp.scale_x, inp.gate_proj_weight.t().contiguous().t(), *inp.args()[3:], out)
+    with pytest.raises(ValueError, match="row-major"):
+        pkg.run(*inp.args(), torch.empty(256, 8, dtype=torch.bfloat16, device="cuda:0").t())
+    big = W.make_inputs(65, 256, 256, seed=8).to("cuda:0")
+    with pytest.raises(ValueError, match="plan"):   # the streaming kernel takes at most 64 tokens
+        pkg.run_with_plan(*big.args(), torch.empty(65, 256, dtype=torch.bfloat16, device="cuda:0"), "stream")
+
+
+# ---------------------------------------------------------------------------------------------
+# size-independent properties
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("shape,plan", [((200, 512, 384), "tile"), ((24, 1024, 768), "stream")])
+def test_power_of_two_scaling_of_up_is_exact(pkg, shape, plan):
+    # scale_up * 4 multiplies every up accumulator, its bf16 rounding and the product by exactly 4
+    inp = W.make_inputs(*shape, seed=9)
+    a = _run(pkg, inp, plan).float()
+    inp4 = W.GateUpInputs(inp.x, inp.scale_x, inp.gate_proj_weight, inp.scale_gate, inp.up_proj_weight, inp.scale_up * 4)
+    b = _run(pkg, inp4, plan).float()
+    assert torch.equal(b, a * 4)
+
+
+@pytest.mark.parametrize("shape,plan", [((260, 384, 256), "tile"), ((40, 640, 512), "stream")])
+def test_row_permutation_and_column_block_permutation(pkg, shape, plan):
+    inp = W.make_inputs(*shape, seed=10)
+    base = _run(pkg, inp, plan)
+    perm = torch.randperm(shape[0], generator=torch.Generator().manual_seed(0))
+    assert torch.equal(_run(pkg, inp.rows(perm), plan), base[perm.cuda()])
+    nb = shape[2] // 128
+    bperm = torch.randperm(nb, generator=torch.Generator().manual_seed(1))
+    cols = (bperm[:, None] * 128 + torch.arange(128)[None]).reshape(-1).cuda()
+    assert torch.equal(_run(pkg, inp.column_blocks(bperm), plan), base[:, cols])
+
+
+def test_zero_gate_gives_zero_and_saturated_inputs_stay_finite(pkg):
+    inp = W.make_inputs(128, 256, 256, seed=11)
+    zero_gate = W.GateUpInputs(inp.x, inp.scale_x, torch.zeros_like(inp.gate_proj_weight.view(torch.uint8)).view(torch.float8_e4m3fn),
+                               inp.scale_gate, inp.up_proj_weight, inp.scale_up)
+    assert (_run(pkg, zero_gate, "tile").float() == 0).all()
+    big = W.make_inputs(128, 256, 256, seed=11, x_std=50.0, w_std=5.0)
+    out = _run(pkg, big, "tile")
+    assert torch.isfinite(out.float()).all()
+    _check(out, big, "large magnitudes")
+
+
+# ---------------------------------------------------------------------------------------------
+# full-size configurations: generated on the GPU, checked on sampled rows x column blocks, which
+# the oracle evaluates exactly because rows and column blocks are independent
+# ---------------------------------------------------------------------------------------------
+def _sampled_check(pkg, name, shape, rows, blocks, plan="auto", seed=0):
+    m, k, n = shape
+    dev = torch.device("cuda:0")
+    inp = W.make_inputs(m, k, n, seed=seed, device=dev)
+    out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=dev)
+    pkg.run_with_plan(*inp.args(), out, plan)
+    torch.cuda.synchronize()
+    code, detail = pkg.last_status()
+    assert code == 0, (name, code, hex(detail))
+    assert torch.isfinite(out.float()).all(), name
+    ridx = torch.tensor(rows, device=dev)
+    bidx = torch.tensor(blocks, device=dev)
+    sub = inp.rows(ridx).column_blocks(bidx).to("cpu")
+    cols = (bidx[:, None] * 128 + torch.arange(128, device=dev)[None]).reshape(-1)
+    got = out[ridx][:, cols].cpu()
+    _check(got, sub, name)
+    # idempotence: a second call overwrites the destination with identical bits
+    again = torch.empty_like(out)
+    pkg.run_with_plan(*inp.args(), again, plan)
+    torch.cuda.synchronize()
+    assert torch.equal(out, again), name
+    del inp, out, again
+    torch.cuda.empty_cache()
+
+
+def test_full_size_prefill_8b(pkg):
+    m, k, n = W.SHAPES["prefill_8b"]
+    rows = list(range(0, m, 157)) + [127, 128, m - 1]
+    _sampled_check(pkg, "prefill_8b", (m, k, n), rows, [0, 1, 55, 110, n // 128 - 1])
+
+
+def test_full_size_decode_70b(pkg):
+    m, k, n = W.SHAPES["decode_70b"]
+    _sampled_check(pkg, "decode_70b", (m, k, n), list(range(m)), [0, 1, 2, 3, 100, 101, 150, 222, n // 128 - 1])
+
+
+def test_full_size_prefill_sharded_shape_on_one_gpu(pkg):
+    m, k, n = W.SHAPES["prefill_sharded"]
+    rows = list(range(5, m, 1021)) + [m - 1]
+    _sampled_check(pkg, "prefill_sharded", (m, k, n), rows, [0, 71, n // 128 - 1])
+
+
+def test_reference_native_shape(pkg):
+    m, k, n = W.SHAPES["reference_native"]
+    _sampled_check(pkg, "reference_native", (m, k, n), list(range(0, m, 67)), [0, 73, 147])
+
+
+@pytest.mark.parametrize("m", W.SWEEP_M)
+def test_m_sweep_shapes(pkg, m):
+    k, n = W.SWEEP_KN
+    rows = sorted(set([0, m - 1] + list(range(0, m, max(1, m // 24)))))
+    _sampled_check(pkg, f"sweep M={m}", (m, k, n), rows, [0, 56, n // 128 - 1])

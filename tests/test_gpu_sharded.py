@@ -1,0 +1,75 @@
+"""Column-parallel sharding on GPUs: shards written into column slices of one buffer must
+reproduce the unsharded result bit for bit; with two or more GPUs the NCCL path is run as
+one process per GPU."""
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from sol_execbench_b200_kernels_b200 import workloads as W
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.mark.parametrize("shape,world", [((256, 512, 1024), 2), ((256, 512, 1024), 4), ((16, 1024, 2048), 8),
+                                         ((1000, 1024, 2304), 2)])
+def test_shards_on_one_gpu_reproduce_unsharded_output(shape, world):
+    import sol_execbench_b200_kernels_b200 as pkg
+
+    m, k, n = shape
+    dev = torch.device("cuda:0")
+    inp = W.make_inputs(m, k, n, seed=12, device=dev)
+    ref = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+    pkg.run(*inp.args(), ref)
+    full = torch.zeros(m, n, dtype=torch.bfloat16, device=dev)
+    for r in range(world):
+        lo, hi = pkg.shard_bounds(n, r, world)
+        gw, sg, uw, su = pkg.shard_weights(inp.gate_proj_weight, inp.scale_gate, inp.up_proj_weight, inp.scale_up, r, world)
+        assert pkg.run_sharded(inp.x, inp.scale_x, gw, sg, uw, su, full[:, lo:hi]) is None
+    torch.cuda.synchronize()
+    assert pkg.last_status()[0] == 0
+    assert torch.equal(full, ref)
+
+
+_RANK_SCRIPT = r"""
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["GU_ROOT"])
+import sol_execbench_b200_kernels_b200 as pkg
+from sol_execbench_b200_kernels_b200 import workloads as W
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dev = torch.device("cuda", rank)
+dist.init_process_group("nccl", device_id=dev)
+m, k, n = 512, 1024, 2048
+inp = W.make_inputs(m, k, n, seed=13, device=dev)
+gw, sg, uw, su = pkg.shard_weights(inp.gate_proj_weight, inp.scale_gate, inp.up_proj_weight, inp.scale_up, rank, world)
+local = torch.empty(m, n // world, dtype=torch.bfloat16, device=dev)
+full = pkg.run_sharded(inp.x, inp.scale_x, gw, sg, uw, su, local, gather=True)
+ref = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+pkg.run(*inp.args(), ref)
+torch.cuda.synchronize()
+assert pkg.last_status()[0] == 0
+assert torch.equal(full, ref), f"rank {rank}: gathered result differs"
+dist.barrier()
+dist.destroy_process_group()
+print(f"rank {rank} ok")
+"""
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_nccl_all_gather_of_shards():
+    world = min(torch.cuda.device_count(), 4)
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    env = dict(os.environ, GU_ROOT=ROOT, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), WORLD_SIZE=str(world),
+               NCCL_NVLS_ENABLE="0")
+    procs = [subprocess.Popen([sys.executable, "-c", _RANK_SCRIPT], env=dict(env, RANK=str(r), LOCAL_RANK=str(r)),
+                              stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(world)]
+    for p in procs:
+        out, _ = p.communicate(timeout=300)
+        assert p.returncode == 0, out

@@ -1,0 +1,125 @@
+"""CPU checks of the oracle itself: the two restatements against each other, against an
+independent scalar evaluation, and against the committed golden fixtures."""
+import glob
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import gateup_oracle as O
+from sol_execbench_b200_kernels_b200 import workloads as W
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def test_quantizers_scale_and_range():
+    torch.manual_seed(3)
+    x = torch.randn(5, 256)
+    q, s = W.quantize_activation_1x128(x)
+    assert q.dtype == torch.float8_e4m3fn and s.shape == (5, 2)
+    assert torch.allclose(s, x.reshape(5, 2, 128).abs().amax(-1) / 448.0)
+    assert torch.isfinite(q.float()).all() and q.float().abs().max() <= 448
+    # the largest element of every block lands exactly on +-448
+    assert (q.float().reshape(5, 2, 128).abs().amax(-1) == 448).all()
+    w = torch.randn(256, 384) * 0.02
+    qw, sw = W.quantize_weight_128x128(w)
+    assert sw.shape == (2, 3)
+    deq = O.dequantize(qw, sw, 128)
+    assert (deq - w).abs().max() <= sw.max() * 32  # half an e4m3 ulp at the top binade is 16 quanta
+
+
+def test_quantizer_zero_block_is_finite():
+    x = torch.zeros(2, 128)
+    q, s = W.quantize_activation_1x128(x)
+    assert torch.isfinite(s).all() and (q.float() == 0).all()
+
+
+def test_quantizer_rejects_ragged_k():
+    with pytest.raises(ValueError):
+        W.quantize_activation_1x128(torch.zeros(2, 100))
+    with pytest.raises(ValueError):
+        W.quantize_weight_128x128(torch.zeros(100, 128))
+
+
+def _scalar_oracle(inp):
+    """Independent float64 evaluation, element by element in numpy (tiny shapes only)."""
+    x = inp.x.float().double().numpy()
+    sx = inp.scale_x.double().numpy()
+    res = []
+    for w, s in ((inp.gate_proj_weight, inp.scale_gate), (inp.up_proj_weight, inp.scale_up)):
+        wd = w.float().double().numpy()
+        sd = s.double().numpy()
+        m, k = x.shape
+        n = wd.shape[0]
+        acc = np.zeros((m, n))
+        for j in range(k // 128):
+            part = x[:, j * 128:(j + 1) * 128] @ wd[:, j * 128:(j + 1) * 128].T
+            acc += part * sx[:, j:j + 1] * np.repeat(sd[:, j], 128)[None, :]
+        res.append(torch.from_numpy(acc).float())
+    return O.swiglu_bf16(res[0], res[1])
+
+
+@pytest.mark.parametrize("shape", [(3, 128, 128), (17, 384, 256), (128, 512, 384)])
+def test_restatements_agree(shape):
+    inp = W.make_inputs(*shape, seed=11)
+    a = O.gateup_dequant(*inp.args())
+    b = O.gateup_blockwise(*inp.args())
+    c = _scalar_oracle(inp)
+    for lhs, rhs in ((a, c), (b, c), (a, b)):
+        st = O.error_stats(lhs, rhs)
+        assert st["finite"] and st["rel_l2"] <= 1e-3 and st["max_abs"] <= 2e-2, st
+
+
+def test_small_config_oracles_within_north_star_tolerance():
+    m, k, n = W.SHAPES["small"]
+    inp = W.make_inputs(m, k, n, seed=0)
+    a = O.gateup_dequant(*inp.args())
+    b = O.gateup_blockwise(*inp.args())
+    st = O.error_stats(a, b)
+    assert st["max_abs"] <= 2e-2 and st["rel_l2"] <= 1e-2, st
+    assert a.dtype == torch.bfloat16 and tuple(a.shape) == (m, n)
+
+
+def test_swiglu_rounding_boundaries():
+    g = torch.tensor([[1.00390625, -3.0, 20.0, -100.0]])   # 1.00390625 is not a bf16 value
+    u = torch.tensor([[2.0, 0.5, 1.0, 1.0]])
+    out = O.swiglu_bf16(g, u)
+    gb = g.to(torch.bfloat16).float()
+    act = (gb * torch.sigmoid(gb)).to(torch.bfloat16)
+    assert torch.equal(out, (act.float() * u.to(torch.bfloat16).float()).to(torch.bfloat16))
+    assert out[0, 3] == 0
+
+
+def test_row_and_column_restriction_are_exact():
+    inp = W.make_inputs(40, 256, 384, seed=5)
+    full = O.gateup_blockwise(*inp.args())
+    rows = torch.tensor([3, 17, 39])
+    assert torch.equal(O.gateup_blockwise(*inp.rows(rows).args()), full[rows])
+    blocks = torch.tensor([2, 0])
+    cols = (blocks[:, None] * 128 + torch.arange(128)[None]).reshape(-1)
+    assert torch.equal(O.gateup_blockwise(*inp.column_blocks(blocks).args()), full[:, cols])
+
+
+def _fixtures():
+    return sorted(glob.glob(os.path.join(GOLDEN, "*.json")))
+
+
+@pytest.mark.parametrize("meta_path", _fixtures() or [None])
+def test_golden_fixtures(meta_path):
+    """Outputs of the reference submission's own GPU kernel on seeded inputs, regenerated here from the seed."""
+    if meta_path is None:
+        pytest.skip("no golden fixtures committed yet")
+    with open(meta_path) as f:
+        meta = json.load(f)
+    data = torch.load(meta_path[:-5] + ".pt", weights_only=True)
+    m, k, n = meta["shape"]
+    inp = W.make_inputs(m, k, n, seed=meta["seed"])
+    rows, cols = data["rows"], data["cols"]
+    sub = inp.rows(rows)
+    for name, fn in (("blockwise", O.gateup_blockwise), ("dequant", O.gateup_dequant)):
+        got = fn(*sub.args())[:, cols]
+        st = O.error_stats(got, data["out"])
+        assert st["rel_l2"] <= 1e-2, (name, st)
+        assert st["frac_over_atol"] <= 1e-4, (name, st)

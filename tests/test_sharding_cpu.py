@@ -1,0 +1,99 @@
+"""Column-parallel sharding: index arithmetic and the gather layout, exercised with
+world_size-2 (and 4) gloo ranks on CPU.  The per-rank arithmetic is done by the oracle here;
+the GPU tests cover the kernels."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import gateup_oracle as O
+from sol_execbench_b200_kernels_b200 import workloads as W
+from sol_execbench_b200_kernels_b200.sharded import (assemble_gathered, gather_columns, shard_bounds,
+                                                      shard_concat_weights, shard_weights)
+
+
+def test_shard_bounds_cover_and_tile():
+    n = 18432
+    for world in (1, 2, 4, 8):
+        edges = [shard_bounds(n, r, world) for r in range(world)]
+        assert edges[0][0] == 0 and edges[-1][1] == n
+        for (a0, a1), (b0, b1) in zip(edges, edges[1:]):
+            assert a1 == b0
+        assert all((hi - lo) % 128 == 0 and hi - lo == n // world for lo, hi in edges)
+
+
+def test_shard_bounds_errors():
+    with pytest.raises(ValueError):
+        shard_bounds(128 * 3, 0, 2)        # 3 column blocks over 2 ranks
+    with pytest.raises(ValueError):
+        shard_bounds(1000, 0, 2)           # not a multiple of 128
+    with pytest.raises(ValueError):
+        shard_bounds(256, 2, 2)            # rank out of range
+    with pytest.raises(ValueError):
+        shard_bounds(256, 0, 0)
+
+
+def test_shards_are_views_and_match_concat_form():
+    inp = W.make_inputs(8, 256, 512, seed=4)
+    w = torch.cat([inp.gate_proj_weight.view(torch.uint8), inp.up_proj_weight.view(torch.uint8)]).view(torch.float8_e4m3fn)
+    sw = torch.cat([inp.scale_gate, inp.scale_up])
+    for r in range(2):
+        a = shard_weights(inp.gate_proj_weight, inp.scale_gate, inp.up_proj_weight, inp.scale_up, r, 2)
+        b = shard_concat_weights(w, sw, r, 2)
+        assert a[0].data_ptr() == inp.gate_proj_weight[r * 256:].data_ptr() and a[0].is_contiguous()
+        for ta, tb in zip(a, b):
+            assert torch.equal(ta.view(torch.uint8) if ta.dtype == torch.float8_e4m3fn else ta,
+                               tb.view(torch.uint8) if tb.dtype == torch.float8_e4m3fn else tb)
+
+
+def test_assemble_gathered_layout():
+    r, m, ns = 4, 5, 6
+    full = torch.arange(m * r * ns, dtype=torch.float32).reshape(m, r * ns)
+    gathered = torch.stack([full[:, i * ns:(i + 1) * ns] for i in range(r)])
+    assert torch.equal(assemble_gathered(gathered), full)
+    out = torch.empty(m, r * ns)
+    assert assemble_gathered(gathered, out) is out and torch.equal(out, full)
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _rank_main(rank, world, port, shape, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        torch.set_num_threads(2)
+        inp = W.make_inputs(*shape, seed=9)
+        gw, sg, uw, su = shard_weights(inp.gate_proj_weight, inp.scale_gate, inp.up_proj_weight, inp.scale_up,
+                                       rank, world)
+        local = O.gateup_blockwise(inp.x, inp.scale_x, gw, sg, uw, su)
+        full = gather_columns(local)
+        if rank == 0:
+            ref = O.gateup_blockwise(*inp.args())
+            q.put(bool(torch.equal(full, ref)))
+        # every rank ends up with the same contiguous result
+        check = full.clone().float()
+        dist.all_reduce(check, op=dist.ReduceOp.MAX)
+        assert torch.equal(check, full.float())
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_sharded_gather_matches_unsharded_gloo(world):
+    ctx = mp.get_context("spawn")
+    q = ctx.SimpleQueue()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, (24, 256, 1024), q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    assert q.get() is True
