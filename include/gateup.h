@@ -12,7 +12,7 @@
  *
  * Every pointer is a device pointer on the current device, 16-byte aligned.
  * No entry point allocates or frees device memory; scratch is passed in by the
- * caller.  All launches go to the stream that is passed in.  Functions return 0
+ * caller (gu_run_decode_static carries its own).  All launches go to the stream that is passed in.  Functions return 0
  * on success or a negative GU_E* code; nothing throws.
  */
 #ifndef GATEUP_H_
@@ -37,6 +37,7 @@ extern "C" {
 #define GU_ECUDA (-6)            /* a CUDA runtime / driver call failed                */
 #define GU_EDEVICE (-7)          /* not a compute-capability-10.x device               */
 #define GU_ETIMEOUT (-8)         /* a bounded device-side wait gave up (gu_last_status) */
+#define GU_ESTATIC_LIMIT (-9)    /* gu_run_decode_static: more tokens than its built-in scratch holds */
 
 /* plans */
 #define GU_PLAN_AUTO 0    /* shape heuristic (gu_select_plan)                                      */
@@ -118,6 +119,35 @@ int gu_run_concat(const void* x, const float* scale_x, const void* w2n, const fl
  * variants/cute_fused_v1/blockwise_gemm_fused.py:85-91).  `clear` != 0 resets it.
  */
 int gu_last_status(int* detail, int clear);
+
+/*
+ * Decode-sized variant of gu_run for callers that cannot hand the library any
+ * scratch memory because they are not allowed to allocate on the device: a
+ * plugin inside a serving runtime that claims all of HBM for its own arena at
+ * start-up and forbids cudaMalloc afterwards, or a latency-critical decode loop
+ * that cannot afford the device-wide synchronisation a cudaMalloc / cudaFree
+ * implies.  It runs the weight-streaming (stream-K) kernel with its hand-off
+ * scratch in an array compiled into the library (4 MiB + 4 KiB on every GPU
+ * that loads the library, held until the process exits) and calls no
+ * cudaMalloc, cudaFree or other allocating routine.  The caller still passes
+ * inputs and output; `workspace`, `workspace_bytes` and `plan` are ignored.
+ *
+ *   - At most 16 tokens (M <= 16).  A larger M returns GU_ESTATIC_LIMIT and
+ *     launches nothing.
+ *   - The first call on each device looks up the array's device address and
+ *     sets the kernel's shared-memory attribute.  Make that call with the
+ *     device current, and before any stream capture begins.
+ *   - Every call this process makes on a device uses the same array, and the
+ *     array keeps what the previous call left in it.  Nothing has to be
+ *     cleared between calls (each call stamps its hand-off flags with an epoch
+ *     no earlier call used), but two calls in flight on the GPU at the same
+ *     time — two streams, or two host threads — race on it and give wrong
+ *     results.  Keep these calls on one stream.
+ *
+ * This entry point has no counterpart in the reference, which allocates its
+ * scratch inside every call.
+ */
+int gu_run_decode_static(const gu_problem* problem, void* stream);
 
 /* Kernel launches issued by this library in this process so far. */
 int64_t gu_launch_count(void);

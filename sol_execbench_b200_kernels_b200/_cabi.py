@@ -19,13 +19,14 @@ GU_EWORKSPACE = -5
 GU_ECUDA = -6
 GU_EDEVICE = -7
 GU_ETIMEOUT = -8
+GU_ESTATIC_LIMIT = -9
 
 PLAN_AUTO, PLAN_TILE, PLAN_STREAM = 0, 1, 2
 PLAN_NAMES = {PLAN_AUTO: "auto", PLAN_TILE: "tile", PLAN_STREAM: "stream"}
 
 EXPORTS = (
     "gu_version", "gu_error_string", "gu_select_plan", "gu_workspace_bytes", "gu_workspace_init",
-    "gu_run", "gu_run_concat", "gu_last_status", "gu_launch_count",
+    "gu_run", "gu_run_concat", "gu_last_status", "gu_launch_count", "gu_run_decode_static",
 )
 
 
@@ -68,6 +69,8 @@ def _load() -> ctypes.CDLL:
     lib.gu_run_concat.restype = c_int
     lib.gu_run_concat.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                   c_int64, c_void_p, c_size_t, c_int, c_void_p]
+    lib.gu_run_decode_static.restype = c_int
+    lib.gu_run_decode_static.argtypes = [POINTER(GuProblem), c_void_p]
     lib.gu_last_status.restype = c_int
     lib.gu_last_status.argtypes = [POINTER(c_int), c_int]
     lib.gu_launch_count.restype = c_int64

@@ -232,6 +232,61 @@ int launch_stream_t(const gu_problem* pr, const DeviceInfo& dev, cudaStream_t st
   return cudaGetLastError() == cudaSuccess ? GU_OK : GU_ECUDA;
 }
 
+
+// ---------------------------------------------------------------------------
+// Built-in scratch for gu_run_decode_static.
+//
+// Some hosts of this library may not allocate device memory at all: a serving
+// runtime that claims all of HBM for its own arena at start-up and forbids
+// cudaMalloc afterwards, or a decode loop that cannot afford the device-wide
+// synchronisation an allocation implies.  For them the stream-K hand-off scratch
+// of the decode kernel lives in this file-scope array instead of in a
+// caller-supplied workspace.  It is sized for at most kStaticMaxTokens tokens
+// (4 KiB of flags + 256 ranges x 2 x 16 x 128 fp32 = 4 MiB + 4 KiB), and every
+// GPU that loads the library carries it until the process exits.
+//
+// In host code the array's name is only a stand-in for the symbol; the device
+// address is obtained with cudaGetSymbolAddress, once per device, with that
+// device current (static_scratch_ptr below), and passed to the kernel.
+// ---------------------------------------------------------------------------
+constexpr int kStaticMaxTokens = 16;
+constexpr size_t kStaticScratchBytes =
+    kStreamFlagBytes + size_t(kStreamMaxGrid) * 2 * kStaticMaxTokens * 128 * sizeof(float);
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+void* g_static_ptr[64] = {nullptr};
+
+int static_scratch_ptr(void** out) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return GU_ECUDA;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (!g_static_ptr[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || !p) {
+      cudaGetLastError();
+      return GU_ECUDA;
+    }
+    g_static_ptr[dev] = p;
+  }
+  *out = g_static_ptr[dev];
+  return GU_OK;
+}
+
+// Descriptor encoding straight into caller storage: no cache entry, so no host allocation either.
+int encode_map_uncached(CUtensorMap* out, const void* ptr, uint64_t cols, uint64_t rows, uint64_t pitch_bytes,
+                        uint32_t box_cols, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return GU_ECUDA;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {pitch_bytes};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? GU_OK : GU_ECUDA;
+}
+
 }  // namespace
 }  // namespace gu
 
@@ -250,6 +305,7 @@ const char* gu_error_string(int code) {
     case GU_ECUDA: return "a CUDA call failed";
     case GU_EDEVICE: return "the current device is not compute capability 10.x";
     case GU_ETIMEOUT: return "a bounded device-side wait gave up";
+    case GU_ESTATIC_LIMIT: return "gu_run_decode_static: at most 16 tokens fit the built-in scratch";
     default: return "unknown error";
   }
 }
@@ -319,6 +375,53 @@ int gu_run_concat(const void* x, const float* scale_x, const void* w2n, const fl
   pr.workspace_bytes = workspace_bytes;
   pr.plan = plan;
   return gu_run(&pr, stream);
+}
+
+int gu_run_decode_static(const gu_problem* pr, void* stream_v) {
+  int rc = gu::check_problem(pr);
+  if (rc != GU_OK) return rc;
+  if (pr->m > gu::kStaticMaxTokens) return GU_ESTATIC_LIMIT;
+  const int stages = gu::stream_stages(16, pr->k / 128);
+  if (stages == 0) return GU_EINVAL_PLAN;
+  gu::DeviceInfo* dev = nullptr;
+  if ((rc = gu::device_info(&dev)) != GU_OK) return rc;   // first call per device: function attributes
+  void* scratch = nullptr;
+  if ((rc = gu::static_scratch_ptr(&scratch)) != GU_OK) return rc;  // first call per device: symbol address
+
+  const int64_t m = pr->m, k = pr->k, n = pr->n;
+  CUtensorMap tm_x, tm_g, tm_u;
+  if ((rc = gu::encode_map_uncached(&tm_x, pr->x, k, m, k, 128, 16)) != GU_OK) return rc;
+  if ((rc = gu::encode_map_uncached(&tm_g, pr->gate_w, k, n, k, 128, 128)) != GU_OK) return rc;
+  if ((rc = gu::encode_map_uncached(&tm_u, pr->up_w, k, n, k, 128, 128)) != GU_OK) return rc;
+
+  gu::StreamParams p;
+  p.scale_x = pr->scale_x;
+  p.scale_gate = pr->scale_gate;
+  p.scale_up = pr->scale_up;
+  p.out = static_cast<__nv_bfloat16*>(pr->output);
+  p.ld_out = pr->ld_output;
+  p.m = static_cast<int>(m);
+  p.kb = static_cast<int>(k / 128);
+  p.nb = static_cast<int>(n / 128);
+  p.stages = stages;
+  // The array keeps whatever the previous call left in it.  Nothing has to be cleared: a flag only
+  // counts when it equals this call's epoch, a value no earlier call has written (the array starts
+  // zeroed at module load and 0 is never an epoch), and partial slots are fully rewritten before
+  // their flag is stamped.
+  p.flags = static_cast<unsigned int*>(scratch);
+  p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) + gu::kStreamFlagBytes);
+  unsigned int e = gu::g_epoch.fetch_add(1, std::memory_order_relaxed) + 1;
+  if (e == 0) e = gu::g_epoch.fetch_add(1, std::memory_order_relaxed) + 1;
+  p.epoch = e;
+
+  const int64_t units = int64_t(p.nb) * p.kb;
+  int64_t grid = dev->sm_count < gu::kStreamMaxGrid ? dev->sm_count : gu::kStreamMaxGrid;
+  if (units < grid) grid = units;
+  const uint32_t smem = gu::StreamCfg<16>::smem_bytes(stages, p.kb);
+  gu::gateup_stream_kernel<16><<<static_cast<int>(grid), gu::kStreamThreads, smem,
+                                 static_cast<cudaStream_t>(stream_v)>>>(tm_x, tm_g, tm_u, p);
+  gu::g_launches.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError() == cudaSuccess ? GU_OK : GU_ECUDA;
 }
 
 int gu_last_status(int* detail, int clear) {
