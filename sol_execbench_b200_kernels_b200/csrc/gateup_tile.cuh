@@ -5,6 +5,8 @@
 // gate and up weight tiles (three plain TMA boxes, 48 KiB), and a single
 // tcgen05.mma sequence with N = 256 leaves the gate partial in TMEM columns
 // [0,128) and the up partial in [128,256) of a double-buffered accumulator.
+// (One N = 256 instruction stream, not two of N = 128: the MMA is limited by
+// shared-memory operand reads, and the narrower form reads the X tile twice.)
 // Eight consumer warps read each partial out of TMEM, apply
 // scale_x[m, kb] * scale_w[n/128, kb] and add it to fp32 running sums they keep
 // in registers (block order ascending, as the reference's promotion loop does:
@@ -118,7 +120,7 @@ gateup_tile_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   WaitCtx ctx{abort_gen, false};
 
   if (warp < 4) {
-    reg_dealloc<40>();
+    reg_dealloc<64>();
     if (warp == 0 && lane == 0) {
       // ------------------------------ TMA producer ------------------------------
       int stage = 0;
@@ -169,37 +171,45 @@ gateup_tile_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
       }
     }
   } else {
-    reg_alloc<232>();
+    reg_alloc<216>();
     // ------------------------------- consumers --------------------------------
     const int quarter = warp & 3;          // TMEM lane quarter this warp may read
     const int half = (warp - 4) >> 2;      // which 64 output columns
     const int row = quarter * 32 + lane;   // token row inside the tile
-    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + half * 64;
     const uint32_t out_half = out_stage + half * kTileOutHalfBytes;
+    const uint32_t my_acc_full = bar_acc_full;
+    const uint32_t my_acc_empty = bar_acc_empty;
     const bool store_leader = ((threadIdx.x - 128) & 127) == 0;
     int acc = 0;
     uint32_t acc_phase = 0;
 
-    for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
-      int mb, nb;
-      tile_coords(p, tile, mb, nb);
+    int tile = blockIdx.x;
+    int mb = 0, nb = 0;
+    const float *sx_row = p.scale_x, *sg_row = p.scale_gate, *su_row = p.scale_up;
+    float sx0 = 0.f, sg0 = 0.f, su0 = 0.f, sx1 = 0.f, sg1 = 0.f, su1 = 0.f;
+    // first two K blocks' scales of a tile (fetched before the previous tile's epilogue)
+    auto start_tile = [&](int t) {
+      tile_coords(p, t, mb, nb);
       const int m_global = min(mb * kTileM + row, p.m - 1);
-      const float* sx_row = p.scale_x + static_cast<size_t>(m_global) * p.kb;
-      const float* sg_row = p.scale_gate + static_cast<size_t>(nb) * p.kb;
-      const float* su_row = p.scale_up + static_cast<size_t>(nb) * p.kb;
+      sx_row = p.scale_x + static_cast<size_t>(m_global) * p.kb;
+      sg_row = p.scale_gate + static_cast<size_t>(nb) * p.kb;
+      su_row = p.scale_up + static_cast<size_t>(nb) * p.kb;
+      sx0 = __ldg(sx_row); sg0 = __ldg(sg_row); su0 = __ldg(su_row);
+      if (p.kb > 1) { sx1 = __ldg(sx_row + 1); sg1 = __ldg(sg_row + 1); su1 = __ldg(su_row + 1); }
+    };
+    if (tile < p.num_tiles) start_tile(tile);
 
+    while (tile < p.num_tiles) {
       float2 g[32], u[32];  // 64 gate + 64 up running sums
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
         g[i] = make_float2(0.f, 0.f);
         u[i] = make_float2(0.f, 0.f);
       }
-      // scales are fetched two K blocks ahead of their use
-      float sx0 = __ldg(sx_row), sg0 = __ldg(sg_row), su0 = __ldg(su_row);
-      float sx1 = 0.f, sg1 = 0.f, su1 = 0.f;
-      if (p.kb > 1) { sx1 = __ldg(sx_row + 1); sg1 = __ldg(sg_row + 1); su1 = __ldg(su_row + 1); }
 
       for (int j = 0; j < p.kb; ++j) {
+        // scales are fetched two K blocks ahead of their use
         float sx2 = 0.f, sg2 = 0.f, su2 = 0.f;
         if (j + 2 < p.kb) { sx2 = __ldg(sx_row + j + 2); sg2 = __ldg(sg_row + j + 2); su2 = __ldg(su_row + j + 2); }
         const float sgx = sx0 * sg0;
@@ -207,11 +217,11 @@ gateup_tile_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
         const float2 sg2v = make_float2(sgx, sgx);
         const float2 su2v = make_float2(sux, sux);
 
-        const bool ok = mbar_wait(ctx, bar_acc_full + 8 * acc, acc_phase, kWaitTileAccFull);
+        const bool ok = mbar_wait(ctx, my_acc_full + 8 * acc, acc_phase, kWaitTileAccFull);
         tc_fence_after();
+        float v[64];
         if (ok) {
-          const uint32_t t = lane_addr + acc * (2 * kTileN) + half * 64;
-          float v[64];
+          const uint32_t t = lane_addr + acc * (2 * kTileN);
           tmem_ld32(t, v);
           tmem_ld32(t + 32, v + 32);
           tmem_ld_wait_pin<64>(v);
@@ -220,17 +230,26 @@ gateup_tile_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
           tmem_ld32(t + kTileN, v);
           tmem_ld32(t + kTileN + 32, v + 32);
           tmem_ld_wait_pin<64>(v);
+        } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) u[i] = __ffma2_rn(make_float2(v[2 * i], v[2 * i + 1]), su2v, u[i]);
+          for (int i = 0; i < 64; ++i) v[i] = 0.f;
         }
+        // the partial is in registers: hand the TMEM stage back before the last FMAs
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar_acc_empty + 8 * acc);
+        if (lane == 0) mbar_arrive(my_acc_empty + 8 * acc);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) u[i] = __ffma2_rn(make_float2(v[2 * i], v[2 * i + 1]), su2v, u[i]);
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
         sx0 = sx1; sg0 = sg1; su0 = su1;
         sx1 = sx2; sg1 = sg2; su1 = su2;
       }
+
+      // next tile's coordinates and first scales, so their latency hides under the epilogue
+      const int cur_mb = mb, cur_nb = nb;
+      const int next = tile + gridDim.x;
+      if (next < p.num_tiles) start_tile(next);
 
       // -------- epilogue: SwiGLU in registers, swizzled staging tile, TMA store --------
       if (store_leader) tma_store_wait_read0();  // previous tile's store has finished reading the staging tile
@@ -240,19 +259,20 @@ gateup_tile_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
 #pragma unroll
         for (int c = 0; c < 8; ++c) {  // 8 chunks of 8 bf16 = 16 bytes
           uint4 q;
-          q.x = pack_bf16x2(swiglu_bf16(g[4 * c + 0].x, u[4 * c + 0].x), swiglu_bf16(g[4 * c + 0].y, u[4 * c + 0].y));
-          q.y = pack_bf16x2(swiglu_bf16(g[4 * c + 1].x, u[4 * c + 1].x), swiglu_bf16(g[4 * c + 1].y, u[4 * c + 1].y));
-          q.z = pack_bf16x2(swiglu_bf16(g[4 * c + 2].x, u[4 * c + 2].x), swiglu_bf16(g[4 * c + 2].y, u[4 * c + 2].y));
-          q.w = pack_bf16x2(swiglu_bf16(g[4 * c + 3].x, u[4 * c + 3].x), swiglu_bf16(g[4 * c + 3].y, u[4 * c + 3].y));
+          q.x = swiglu_bf16x2(g[4 * c + 0], u[4 * c + 0]);
+          q.y = swiglu_bf16x2(g[4 * c + 1], u[4 * c + 1]);
+          q.z = swiglu_bf16x2(g[4 * c + 2], u[4 * c + 2]);
+          q.w = swiglu_bf16x2(g[4 * c + 3], u[4 * c + 3]);
           *reinterpret_cast<uint4*>(out_row + ((c ^ (row & 7)) << 4)) = q;
         }
       }
       fence_proxy_async_smem();
       named_bar_sync(1 + half, 128);
       if (store_leader && !ctx.aborted) {
-        tma_store_2d(&tm_out, out_half, nb * kTileN + half * 64, mb * kTileM);
+        tma_store_2d(&tm_out, out_half, cur_nb * kTileN + half * 64, cur_mb * kTileM);
         tma_store_commit();
       }
+      tile = next;
     }
     if (store_leader) tma_store_wait_all0();
   }

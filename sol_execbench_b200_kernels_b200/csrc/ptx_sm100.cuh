@@ -273,4 +273,20 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// Same three rounding boundaries for two adjacent columns at once, with every
+// bf16 rounding done by the packed two-value conversion (half the conversion
+// instructions) and the widening back to fp32 by shifts.  Returns the two bf16
+// outputs packed (.x in the low half).
+__device__ __forceinline__ uint32_t swiglu_bf16x2(float2 gate_acc, float2 up_acc) {
+  const uint32_t gp = pack_bf16x2(gate_acc.x, gate_acc.y);
+  const uint32_t up = pack_bf16x2(up_acc.x, up_acc.y);
+  const float g0 = __uint_as_float(gp << 16), g1 = __uint_as_float(gp & 0xffff0000u);
+  const float u0 = __uint_as_float(up << 16), u1 = __uint_as_float(up & 0xffff0000u);
+  const float a0 = __fdividef(g0, 1.0f + __expf(-g0));
+  const float a1 = __fdividef(g1, 1.0f + __expf(-g1));
+  const uint32_t ap = pack_bf16x2(a0, a1);
+  const float r0 = __uint_as_float(ap << 16), r1 = __uint_as_float(ap & 0xffff0000u);
+  return pack_bf16x2(r0 * u0, r1 * u1);
+}
+
 }  // namespace gu
