@@ -33,7 +33,15 @@ import torch  # noqa: E402
 
 METRIC = "FP8 gate/up+SwiGLU TFLOP/s & HBM GB/s vs roofline at 1/2/4/8 B200"
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
-L2_FLUSH_BYTES = 256 << 20  # written between timed iterations; B200 L2 is 126 MB
+L2_FLUSH_BYTES = 256 << 20  # written, then read back, between timed iterations; B200 L2 is 126 MB
+
+
+def flush_l2(buf: torch.Tensor) -> None:
+    """Evicts the workload from L2: writes a buffer larger than L2, then reads it back so the lines it
+    leaves behind are clean (dirty lines would be written back during the timed kernel and charge it
+    with DRAM traffic that is not its own)."""
+    buf.zero_()
+    buf.sum()
 
 # Measured DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum from the ncu
 # captures summarised under profiles/), keyed by workload; None until a capture exists.
@@ -110,7 +118,7 @@ class ClockSampler:
 def time_device_steps(fn, steps: int, warmup: int, flush: torch.Tensor, barrier=None):
     """Per-step CUDA-event timing on the current stream, L2 flushed before every step."""
     for _ in range(warmup):
-        flush.zero_()
+        flush_l2(flush)
         fn()
     torch.cuda.synchronize()
     if barrier is not None:
@@ -119,7 +127,7 @@ def time_device_steps(fn, steps: int, warmup: int, flush: torch.Tensor, barrier=
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
     stops = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
     for i in range(steps):
-        flush.zero_()
+        flush_l2(flush)
         starts[i].record()
         fn()
         stops[i].record()
@@ -200,7 +208,7 @@ def run_ours(args):
         local = full
     n_local = local.gate_proj_weight.shape[0]
     out = torch.empty(m, n_local, dtype=torch.bfloat16, device=dev)
-    flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
+    flush = torch.empty(L2_FLUSH_BYTES // 4, dtype=torch.int32, device=dev)
     gathered = torch.empty(m, n, dtype=torch.bfloat16, device=dev) if (args.gather and n_gpus > 1) else None
     scratch = torch.empty(world, m, n_local, dtype=torch.bfloat16, device=dev) if gathered is not None else None
 
@@ -278,7 +286,7 @@ def run_ours(args):
             "config": {"workload": f"{workload}: M={m} K={k} N={n}", "sharding": f"N column-sharded over {n_gpus}" if n_gpus > 1 else "none",
                        "per_rank_n": n_local, "plan": pkg.select_plan(m, k, n_local),
                        "gather": bool(gathered is not None),
-                       "l2": f"flushed between timed steps by writing a {L2_FLUSH_BYTES >> 20} MiB buffer"},
+                       "l2": f"flushed before every timed step by writing, then reading back, a {L2_FLUSH_BYTES >> 20} MiB buffer"},
             "roofline": roof, "e2e": e2e, "gpu_launches": launches_timed,
             "clocks": clocks.summary(),
         }
