@@ -41,8 +41,10 @@ extern "C" {
 
 /* plans */
 #define GU_PLAN_AUTO 0    /* shape heuristic (gu_select_plan)                                      */
-#define GU_PLAN_TILE 1    /* persistent 128 x (128 gate + 128 up) tiles; any M                      */
+#define GU_PLAN_TILE 1    /* persistent 128 x (128 gate + 128 up) tiles; any M; schedule by tile count */
 #define GU_PLAN_STREAM 2  /* weight-streaming, tokens on the MMA N side, stream-K over (N-block, K-block); M <= 64 */
+#define GU_PLAN_TILE_DP 3 /* tile kernel, data-parallel schedule forced (whole tiles per CTA, no scratch)    */
+#define GU_PLAN_TILE_SK 4 /* tile kernel, stream-K schedule forced (needs scratch)                           */
 
 /*
  * One call's operands.  Replaces the seven tensors of the reference `run`
@@ -81,7 +83,7 @@ const char* gu_error_string(int code);
 int gu_select_plan(int64_t m, int64_t k, int64_t n);
 
 /*
- * Scratch bytes a plan needs for this shape (0 for GU_PLAN_TILE).  The
+ * Scratch bytes a plan needs for this shape (0 when it needs none).  The
  * reference allocates its scratch inside the call (kernel.py:226-229,
  * cuda_cpp_v4/kernel.cu:221-230, 290-296); here the caller owns it.
  */

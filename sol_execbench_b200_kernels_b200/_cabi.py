@@ -21,8 +21,9 @@ GU_EDEVICE = -7
 GU_ETIMEOUT = -8
 GU_ESTATIC_LIMIT = -9
 
-PLAN_AUTO, PLAN_TILE, PLAN_STREAM = 0, 1, 2
-PLAN_NAMES = {PLAN_AUTO: "auto", PLAN_TILE: "tile", PLAN_STREAM: "stream"}
+PLAN_AUTO, PLAN_TILE, PLAN_STREAM, PLAN_TILE_DP, PLAN_TILE_SK = 0, 1, 2, 3, 4
+PLAN_NAMES = {PLAN_AUTO: "auto", PLAN_TILE: "tile", PLAN_STREAM: "stream", PLAN_TILE_DP: "tile_dp",
+              PLAN_TILE_SK: "tile_sk"}
 
 EXPORTS = (
     "gu_version", "gu_error_string", "gu_select_plan", "gu_workspace_bytes", "gu_workspace_init",

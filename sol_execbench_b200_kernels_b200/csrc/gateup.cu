@@ -112,7 +112,10 @@ int device_info(DeviceInfo** out) {
   if (d.cc_major != 10) return GU_EDEVICE;
   if (!d.attrs_set) {
     const int smem = d.max_smem_optin;
-    if (cudaFuncSetAttribute(gateup_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
+    if (cudaFuncSetAttribute(gateup_tile_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
+            cudaSuccess ||
+        cudaFuncSetAttribute(gateup_tile_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
+            cudaSuccess ||
         cudaFuncSetAttribute(gateup_stream_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
             cudaSuccess ||
         cudaFuncSetAttribute(gateup_stream_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
@@ -129,6 +132,13 @@ int device_info(DeviceInfo** out) {
 }
 
 std::atomic<unsigned int> g_epoch{0};
+
+// A stamp no earlier call of this process has used for its hand-off flags; never 0.
+unsigned int next_epoch() {
+  unsigned int e = g_epoch.fetch_add(1, std::memory_order_relaxed) + 1;
+  if (e == 0) e = g_epoch.fetch_add(1, std::memory_order_relaxed) + 1;
+  return e;
+}
 std::atomic<long long> g_launches{0};
 
 constexpr int kSmemBudget = 227 * 1024;
@@ -143,6 +153,25 @@ int stream_stages(int mpad, int64_t kb) {
   if (s > kStreamMaxStages) s = kStreamMaxStages;
   return s >= 3 ? static_cast<int>(s) : 0;
 }
+
+// SM count of the current device, or the B200's 148 when no device can be asked (sizing queries on a CPU box).
+int sm_count_or_default() {
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess &&
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && sms > 0)
+    return sms;
+  cudaGetLastError();
+  return 148;
+}
+
+// Tile kernel schedule.  The stream-K schedule (whole rounds data-parallel, the last one to two rounds' worth of
+// tiles cut into equal unit ranges) balances awkward tile counts, but measured on B200 its hand-off cost
+// (publish, gather, a second launch) cancels the gain at every size tried: 128 x 4096 x 14336 takes 38.9 us
+// against 30.7 us data-parallel, 512 rows 89.1 against 86.0, 1024 rows 148.5 against 145.4.  So the heuristic
+// keeps the data-parallel schedule; GU_PLAN_TILE_SK still selects stream-K explicitly.
+bool tile_prefers_stream_k(int64_t, int64_t, int64_t, int) { return false; }
+
+size_t tile_stream_k_bytes() { return kTileFlagBytes + size_t(kTileMaxGrid) * kTilePartialFloats * sizeof(float); }
 
 bool shape_ok(int64_t m, int64_t k, int64_t n) {
   return m >= 1 && k >= 128 && n >= 128 && (k % 128) == 0 && (n % 128) == 0 && m < (1ll << 31) &&
@@ -164,7 +193,7 @@ int check_problem(const gu_problem* pr) {
   return GU_OK;
 }
 
-int launch_tile(const gu_problem* pr, const DeviceInfo& dev, cudaStream_t stream) {
+int launch_tile(const gu_problem* pr, const DeviceInfo& dev, cudaStream_t stream, bool stream_k) {
   const int64_t m = pr->m, k = pr->k, n = pr->n;
   CUtensorMap tm_x, tm_g, tm_u, tm_o;
   int rc;
@@ -184,7 +213,7 @@ int launch_tile(const gu_problem* pr, const DeviceInfo& dev, cudaStream_t stream
   p.num_m_blocks = static_cast<int>((m + kTileM - 1) / kTileM);
   p.num_n_blocks = static_cast<int>(n / kTileN);
   const int64_t tiles = int64_t(p.num_m_blocks) * p.num_n_blocks;
-  if (tiles >= (1ll << 31)) return GU_EINVAL_SHAPE;
+  if (tiles * (k / 128) >= (1ll << 31)) return GU_EINVAL_SHAPE;  // the schedules count (tile, K block) units in 32 bits
   p.num_tiles = static_cast<int>(tiles);
   // raster group: as many M blocks as keep the group's X tiles (128 x K bytes each) within ~24 MiB of L2
   int64_t gm = (24ll << 20) / (128 * k);
@@ -192,10 +221,40 @@ int launch_tile(const gu_problem* pr, const DeviceInfo& dev, cudaStream_t stream
   if (gm > p.num_m_blocks) gm = p.num_m_blocks;
   p.group_m = static_cast<int>(gm);
 
-  const int grid = p.num_tiles < dev.sm_count ? p.num_tiles : dev.sm_count;
-  gateup_tile_kernel<<<grid, kTileThreads, kTileSmemBytes, stream>>>(tm_x, tm_g, tm_u, tm_o, p);
-  g_launches.fetch_add(1, std::memory_order_relaxed);
-  return cudaGetLastError() == cudaSuccess ? GU_OK : GU_ECUDA;
+  p.flags = nullptr;
+  p.partials = nullptr;
+  p.epoch = 0;
+  p.tile_begin = 0;
+  const int total_tiles = p.num_tiles;
+  const int sms = dev.sm_count;
+  // Hybrid schedule: whole rounds of tiles run data-parallel; the last round plus the remainder (between one and
+  // two rounds' worth of tiles, or everything when there is less than one round) is split into equal unit ranges.
+  int dp_tiles = total_tiles;
+  if (stream_k) {
+    const int rounds = total_tiles / sms;
+    dp_tiles = (total_tiles % sms == 0) ? total_tiles : (rounds >= 1 ? (rounds - 1) * sms : 0);
+  }
+  if (dp_tiles > 0) {
+    p.num_tiles = dp_tiles;
+    const int grid = dp_tiles < sms ? dp_tiles : sms;
+    gateup_tile_kernel<false><<<grid, kTileThreads, kTileSmemBytes, stream>>>(tm_x, tm_g, tm_u, tm_o, p);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    if (cudaGetLastError() != cudaSuccess) return GU_ECUDA;
+  }
+  if (dp_tiles < total_tiles) {
+    p.tile_begin = dp_tiles;
+    p.num_tiles = total_tiles - dp_tiles;
+    int64_t grid = sms < kTileMaxGrid ? sms : kTileMaxGrid;
+    const int64_t units = int64_t(p.num_tiles) * p.kb;
+    if (units < grid) grid = units;
+    p.flags = static_cast<unsigned int*>(pr->workspace);
+    p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(pr->workspace) + kTileFlagBytes);
+    p.epoch = next_epoch();
+    gateup_tile_kernel<true><<<static_cast<int>(grid), kTileThreads, kTileSmemBytes, stream>>>(tm_x, tm_g, tm_u, tm_o, p);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    if (cudaGetLastError() != cudaSuccess) return GU_ECUDA;
+  }
+  return GU_OK;
 }
 
 template <int MPAD>
@@ -219,9 +278,7 @@ int launch_stream_t(const gu_problem* pr, const DeviceInfo& dev, cudaStream_t st
   p.stages = stages;
   p.flags = static_cast<unsigned int*>(pr->workspace);
   p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(pr->workspace) + kStreamFlagBytes);
-  unsigned int e = g_epoch.fetch_add(1, std::memory_order_relaxed) + 1;
-  if (e == 0) e = g_epoch.fetch_add(1, std::memory_order_relaxed) + 1;
-  p.epoch = e;
+  p.epoch = next_epoch();
 
   const int64_t units = int64_t(p.nb) * p.kb;
   int64_t grid = dev.sm_count < kStreamMaxGrid ? dev.sm_count : kStreamMaxGrid;
@@ -319,8 +376,11 @@ int gu_select_plan(int64_t m, int64_t k, int64_t n) {
 size_t gu_workspace_bytes(int64_t m, int64_t k, int64_t n, int plan) {
   if (!gu::shape_ok(m, k, n)) return 0;
   if (plan == GU_PLAN_AUTO) plan = gu_select_plan(m, k, n);
-  if (plan != GU_PLAN_STREAM || m > 64) return 0;
-  return gu::kStreamFlagBytes + size_t(gu::kStreamMaxGrid) * 2 * gu::stream_mpad(m) * 128 * sizeof(float);
+  if (plan == GU_PLAN_STREAM && m <= 64)
+    return gu::kStreamFlagBytes + size_t(gu::kStreamMaxGrid) * 2 * gu::stream_mpad(m) * 128 * sizeof(float);
+  if (plan == GU_PLAN_TILE_SK || (plan == GU_PLAN_TILE && gu::tile_prefers_stream_k(m, k, n, gu::sm_count_or_default())))
+    return gu::tile_stream_k_bytes();
+  return 0;
 }
 
 int gu_workspace_init(void* workspace, size_t bytes, void* stream) {
@@ -334,11 +394,23 @@ int gu_run(const gu_problem* pr, void* stream_v) {
   if (rc != GU_OK) return rc;
   int plan = pr->plan;
   if (plan == GU_PLAN_AUTO) plan = gu_select_plan(pr->m, pr->k, pr->n);
-  if (plan != GU_PLAN_TILE && plan != GU_PLAN_STREAM) return GU_EINVAL_PLAN;
+  if (plan != GU_PLAN_TILE && plan != GU_PLAN_STREAM && plan != GU_PLAN_TILE_DP && plan != GU_PLAN_TILE_SK)
+    return GU_EINVAL_PLAN;
   gu::DeviceInfo* dev = nullptr;
   if ((rc = gu::device_info(&dev)) != GU_OK) return rc;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-  if (plan == GU_PLAN_TILE) return gu::launch_tile(pr, *dev, stream);
+  if (plan != GU_PLAN_STREAM) {
+    const bool have_ws = pr->workspace && pr->workspace_bytes >= gu::tile_stream_k_bytes() && gu::aligned16(pr->workspace);
+    bool sk = false;
+    if (plan == GU_PLAN_TILE_SK) {
+      if (!have_ws) return GU_EWORKSPACE;
+      sk = true;
+    } else if (plan == GU_PLAN_TILE) {
+      // without scratch the data-parallel schedule is used: slower on awkward tile counts, never wrong
+      sk = have_ws && gu::tile_prefers_stream_k(pr->m, pr->k, pr->n, dev->sm_count);
+    }
+    return gu::launch_tile(pr, *dev, stream, sk);
+  }
 
   if (pr->m > 64) return GU_EINVAL_PLAN;
   const int mpad = gu::stream_mpad(pr->m);

@@ -15,6 +15,18 @@
 // 128-byte-swizzled staging tile in shared memory and a TMA store.  Gate and up
 // never reach HBM, X is read once per tile, and no CTA talks to another.
 //
+// Two schedules.  Data-parallel (kStreamK = false): CTA c takes tiles c, c+G,
+// c+2G, ... of an L2-friendly raster; right when the tile count fills the SMs for
+// many rounds.  Stream-K (kStreamK = true): the (tile, K block) units are cut into
+// G equal contiguous ranges, so a tile count that is not a multiple of the SM
+// count (112 tiles, 152 tiles, ...) no longer leaves SMs idle for a whole round.
+// A range that starts inside a tile publishes its fp32 running sums (128 values
+// per consumer thread) and an epoch-stamped flag; the range that holds the
+// tile's first K block adds the later ranges' sums in range order and finishes
+// the tile.  Hand-offs are produced at the start of a range and consumed at the
+// end of an earlier one, ranges are numbered against blockIdx so a CTA only
+// waits for CTAs dispatched before it, and the wait is bounded.
+//
 // Warp roles (12 warps, 3 warpgroups so register budgets can be moved):
 //   warp 0      TMA producer (one elected lane)
 //   warp 1      TMEM allocation + MMA issue (lane 0)
@@ -44,7 +56,7 @@ constexpr uint32_t kTileTmemCols = 512;  // 2 accumulator stages x 256 columns
 enum : unsigned {
   kWaitTileEmpty = 1, kWaitTileFull = 2, kWaitTileAccEmpty = 3, kWaitTileAccFull = 4,
   kWaitStreamEmpty = 5, kWaitStreamFull = 6, kWaitStreamAccEmpty = 7, kWaitStreamAccFull = 8,
-  kWaitStreamFlag = 9,
+  kWaitStreamFlag = 9, kWaitTileFlag = 10,
 };
 
 struct TileParams {
@@ -54,6 +66,51 @@ struct TileParams {
   int m, kb;                // tokens, K / 128
   int num_m_blocks, num_n_blocks, num_tiles;
   int group_m;              // M blocks per raster group (keeps a group's X tiles L2-resident)
+  int tile_begin;           // stream-K launch: covers tiles [tile_begin, tile_begin + num_tiles) of the raster
+  // stream-K schedule only
+  unsigned int* flags;      // [gridDim.x] epoch of the last call that filled slot i
+  float* partials;          // [gridDim.x][32][256] float4: values 4i..4i+3 of consumer thread t at [i * 256 + t]
+  unsigned int epoch;       // this call's stamp, never 0
+};
+
+constexpr uint32_t kTileFlagBytes = 4096;                       // hand-off flags at the start of the workspace
+constexpr int kTileMaxGrid = 256;                               // workspace is sized for at most this many ranges
+constexpr uint32_t kTilePartialFloats = 128 * 256;              // one tile's running sums
+
+// One CTA's walk over its work: whole tiles (data-parallel) or the tile segments of a unit range (stream-K).
+// Stream-K tile numbers are relative to TileParams::tile_begin.
+template <bool kStreamK>
+struct TileWalk {
+  uint32_t u, u_end;  // stream-K: next unit and end of the range (the host keeps tiles * kb below 2^31)
+  int tile, step;
+  __device__ __forceinline__ TileWalk(const TileParams& p, int worker, int workers)
+      : u(0), u_end(0), tile(worker), step(workers) {
+    if constexpr (kStreamK) {
+      const unsigned long long units = static_cast<unsigned long long>(p.num_tiles) * p.kb;
+      const int range = workers - 1 - worker;  // reverse order: see the file comment
+      u = static_cast<uint32_t>(units * range / workers);
+      u_end = static_cast<uint32_t>(units * (range + 1) / workers);
+    }
+  }
+  // next segment: tile index and K blocks [j_begin, j_end)
+  __device__ __forceinline__ bool next(const TileParams& p, int& t, int& j_begin, int& j_end) {
+    if constexpr (kStreamK) {
+      if (u >= u_end) return false;
+      t = static_cast<int>(u / static_cast<uint32_t>(p.kb));
+      j_begin = static_cast<int>(u - static_cast<uint32_t>(t) * p.kb);
+      const uint32_t e = min(static_cast<uint32_t>(t + 1) * p.kb, u_end);
+      j_end = j_begin + static_cast<int>(e - u);
+      u = e;
+      return true;
+    } else {
+      if (tile >= p.num_tiles) return false;
+      t = tile;
+      j_begin = 0;
+      j_end = p.kb;
+      tile += step;
+      return true;
+    }
+  }
 };
 
 __device__ __forceinline__ void tile_coords(const TileParams& p, int tile, int& mb, int& nb) {
@@ -66,6 +123,7 @@ __device__ __forceinline__ void tile_coords(const TileParams& p, int tile, int& 
   mb = first_m + (r - nb * gm);
 }
 
+template <bool kStreamK>
 __global__ void __launch_bounds__(kTileThreads, 1)
 gateup_tile_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_gate,
                    const __grid_constant__ CUtensorMap tm_up, const __grid_constant__ CUtensorMap tm_out,
@@ -125,10 +183,12 @@ gateup_tile_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
       // ------------------------------ TMA producer ------------------------------
       int stage = 0;
       uint32_t phase = 0;
-      for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
+      TileWalk<kStreamK> walk(p, blockIdx.x, gridDim.x);
+      int tile, jb, je;
+      while (walk.next(p, tile, jb, je)) {
         int mb, nb;
-        tile_coords(p, tile, mb, nb);
-        for (int j = 0; j < p.kb; ++j) {
+        tile_coords(p, kStreamK ? tile + p.tile_begin : tile, mb, nb);
+        for (int j = jb; j < je; ++j) {
           const bool ok = mbar_wait(ctx, bar_empty + 8 * stage, phase ^ 1u, kWaitTileEmpty);
           if (ok) {
             const uint32_t full = bar_full + 8 * stage;
@@ -146,8 +206,10 @@ gateup_tile_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
       constexpr uint32_t idesc = umma_idesc_e4m3_f32(kTileM, 2 * kTileN);
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
-      for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
-        for (int j = 0; j < p.kb; ++j) {
+      TileWalk<kStreamK> walk(p, blockIdx.x, gridDim.x);
+      int tile, jb, je;
+      while (walk.next(p, tile, jb, je)) {
+        for (int j = jb; j < je; ++j) {
           bool ok = mbar_wait(ctx, bar_acc_empty + 8 * acc, acc_phase ^ 1u, kWaitTileAccEmpty);
           ok = mbar_wait(ctx, bar_full + 8 * stage, phase, kWaitTileFull) && ok;
           if (ok) {
@@ -184,95 +246,225 @@ gateup_tile_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     int acc = 0;
     uint32_t acc_phase = 0;
 
-    int tile = blockIdx.x;
-    int mb = 0, nb = 0;
-    const float *sx_row = p.scale_x, *sg_row = p.scale_gate, *su_row = p.scale_up;
-    float sx0 = 0.f, sg0 = 0.f, su0 = 0.f, sx1 = 0.f, sg1 = 0.f, su1 = 0.f;
-    // first two K blocks' scales of a tile (fetched before the previous tile's epilogue)
-    auto start_tile = [&](int t) {
-      tile_coords(p, t, mb, nb);
-      const int m_global = min(mb * kTileM + row, p.m - 1);
-      sx_row = p.scale_x + static_cast<size_t>(m_global) * p.kb;
-      sg_row = p.scale_gate + static_cast<size_t>(nb) * p.kb;
-      su_row = p.scale_up + static_cast<size_t>(nb) * p.kb;
-      sx0 = __ldg(sx_row); sg0 = __ldg(sg_row); su0 = __ldg(su_row);
-      if (p.kb > 1) { sx1 = __ldg(sx_row + 1); sg1 = __ldg(sg_row + 1); su1 = __ldg(su_row + 1); }
-    };
-    if (tile < p.num_tiles) start_tile(tile);
+    if constexpr (!kStreamK) {
+      int tile = blockIdx.x;
+      int mb = 0, nb = 0;
+      const float *sx_row = p.scale_x, *sg_row = p.scale_gate, *su_row = p.scale_up;
+      float sx0 = 0.f, sg0 = 0.f, su0 = 0.f, sx1 = 0.f, sg1 = 0.f, su1 = 0.f;
+      // first two K blocks' scales of a tile (fetched before the previous tile's epilogue)
+      auto start_tile = [&](int t) {
+        tile_coords(p, t, mb, nb);
+        const int m_global = min(mb * kTileM + row, p.m - 1);
+        sx_row = p.scale_x + static_cast<size_t>(m_global) * p.kb;
+        sg_row = p.scale_gate + static_cast<size_t>(nb) * p.kb;
+        su_row = p.scale_up + static_cast<size_t>(nb) * p.kb;
+        sx0 = __ldg(sx_row); sg0 = __ldg(sg_row); su0 = __ldg(su_row);
+        if (p.kb > 1) { sx1 = __ldg(sx_row + 1); sg1 = __ldg(sg_row + 1); su1 = __ldg(su_row + 1); }
+      };
+      if (tile < p.num_tiles) start_tile(tile);
 
-    while (tile < p.num_tiles) {
-      float2 g[32], u[32];  // 64 gate + 64 up running sums
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        g[i] = make_float2(0.f, 0.f);
-        u[i] = make_float2(0.f, 0.f);
+      while (tile < p.num_tiles) {
+        float2 g[32], u[32];  // 64 gate + 64 up running sums
+  #pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          g[i] = make_float2(0.f, 0.f);
+          u[i] = make_float2(0.f, 0.f);
+        }
+
+        for (int j = 0; j < p.kb; ++j) {
+          // scales are fetched two K blocks ahead of their use
+          float sx2 = 0.f, sg2 = 0.f, su2 = 0.f;
+          if (j + 2 < p.kb) { sx2 = __ldg(sx_row + j + 2); sg2 = __ldg(sg_row + j + 2); su2 = __ldg(su_row + j + 2); }
+          const float sgx = sx0 * sg0;
+          const float sux = sx0 * su0;
+          const float2 sg2v = make_float2(sgx, sgx);
+          const float2 su2v = make_float2(sux, sux);
+
+          const bool ok = mbar_wait(ctx, my_acc_full + 8 * acc, acc_phase, kWaitTileAccFull);
+          tc_fence_after();
+          float v[64];
+          if (ok) {
+            const uint32_t t = lane_addr + acc * (2 * kTileN);
+            tmem_ld32(t, v);
+            tmem_ld32(t + 32, v + 32);
+            tmem_ld_wait_pin<64>(v);
+  #pragma unroll
+            for (int i = 0; i < 32; ++i) g[i] = __ffma2_rn(make_float2(v[2 * i], v[2 * i + 1]), sg2v, g[i]);
+            tmem_ld32(t + kTileN, v);
+            tmem_ld32(t + kTileN + 32, v + 32);
+            tmem_ld_wait_pin<64>(v);
+          } else {
+  #pragma unroll
+            for (int i = 0; i < 64; ++i) v[i] = 0.f;
+          }
+          // the partial is in registers: hand the TMEM stage back before the last FMAs
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(my_acc_empty + 8 * acc);
+  #pragma unroll
+          for (int i = 0; i < 32; ++i) u[i] = __ffma2_rn(make_float2(v[2 * i], v[2 * i + 1]), su2v, u[i]);
+          acc ^= 1;
+          if (acc == 0) acc_phase ^= 1u;
+          sx0 = sx1; sg0 = sg1; su0 = su1;
+          sx1 = sx2; sg1 = sg2; su1 = su2;
+        }
+
+        // next tile's coordinates and first scales, so their latency hides under the epilogue
+        const int cur_mb = mb, cur_nb = nb;
+        const int next = tile + gridDim.x;
+        if (next < p.num_tiles) start_tile(next);
+
+        // -------- epilogue: SwiGLU in registers, swizzled staging tile, TMA store --------
+        if (store_leader) tma_store_wait_read0();  // previous tile's store has finished reading the staging tile
+        named_bar_sync(1 + half, 128);
+        {
+          uint8_t* out_row = smem_gen + (out_half - smem_base) + row * 128;
+  #pragma unroll
+          for (int c = 0; c < 8; ++c) {  // 8 chunks of 8 bf16 = 16 bytes
+            uint4 q;
+            q.x = swiglu_bf16x2(g[4 * c + 0], u[4 * c + 0]);
+            q.y = swiglu_bf16x2(g[4 * c + 1], u[4 * c + 1]);
+            q.z = swiglu_bf16x2(g[4 * c + 2], u[4 * c + 2]);
+            q.w = swiglu_bf16x2(g[4 * c + 3], u[4 * c + 3]);
+            *reinterpret_cast<uint4*>(out_row + ((c ^ (row & 7)) << 4)) = q;
+          }
+        }
+        fence_proxy_async_smem();
+        named_bar_sync(1 + half, 128);
+        if (store_leader && !ctx.aborted) {
+          tma_store_2d(&tm_out, out_half, cur_nb * kTileN + half * 64, cur_mb * kTileM);
+          tma_store_commit();
+        }
+        tile = next;
       }
+    } else {
+      // ---- stream-K schedule: the same arithmetic in the same block order, but walking tile segments.  It runs
+      // where the op is HBM-bound or on the last partial round of tiles, so the partial is read in four
+      // 32-column pieces through one small buffer; the registers that frees hold the segment bookkeeping. ----
+      const int ctid = threadIdx.x - 128;  // 0..255
+      const int ranges = gridDim.x;
+      const int my_range = ranges - 1 - static_cast<int>(blockIdx.x);
+      TileWalk<true> walk(p, blockIdx.x, gridDim.x);
+      int tile, jb, je;
+      while (walk.next(p, tile, jb, je)) {
+        int mb, nb;
+        tile_coords(p, tile + p.tile_begin, mb, nb);
+        const int m_global = min(mb * kTileM + row, p.m - 1);
+        const float* sx_row = p.scale_x + static_cast<size_t>(m_global) * p.kb;
+        const float* sg_row = p.scale_gate + static_cast<size_t>(nb) * p.kb;
+        const float* su_row = p.scale_up + static_cast<size_t>(nb) * p.kb;
 
-      for (int j = 0; j < p.kb; ++j) {
-        // scales are fetched two K blocks ahead of their use
-        float sx2 = 0.f, sg2 = 0.f, su2 = 0.f;
-        if (j + 2 < p.kb) { sx2 = __ldg(sx_row + j + 2); sg2 = __ldg(sg_row + j + 2); su2 = __ldg(su_row + j + 2); }
-        const float sgx = sx0 * sg0;
-        const float sux = sx0 * su0;
-        const float2 sg2v = make_float2(sgx, sgx);
-        const float2 su2v = make_float2(sux, sux);
-
-        const bool ok = mbar_wait(ctx, my_acc_full + 8 * acc, acc_phase, kWaitTileAccFull);
-        tc_fence_after();
-        float v[64];
-        if (ok) {
+        float2 g[32], u[32];  // 64 gate + 64 up running sums
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          g[i] = make_float2(0.f, 0.f);
+          u[i] = make_float2(0.f, 0.f);
+        }
+        float sx_n = __ldg(sx_row + jb), sg_n = __ldg(sg_row + jb), su_n = __ldg(su_row + jb);
+        for (int j = jb; j < je; ++j) {
+          const float sgx = sx_n * sg_n;
+          const float sux = sx_n * su_n;
+          if (j + 1 < je) { sx_n = __ldg(sx_row + j + 1); sg_n = __ldg(sg_row + j + 1); su_n = __ldg(su_row + j + 1); }
+          const float2 sg2v = make_float2(sgx, sgx);
+          const float2 su2v = make_float2(sux, sux);
+          const bool ok = mbar_wait(ctx, my_acc_full + 8 * acc, acc_phase, kWaitTileAccFull);
+          tc_fence_after();
           const uint32_t t = lane_addr + acc * (2 * kTileN);
-          tmem_ld32(t, v);
-          tmem_ld32(t + 32, v + 32);
-          tmem_ld_wait_pin<64>(v);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) g[i] = __ffma2_rn(make_float2(v[2 * i], v[2 * i + 1]), sg2v, g[i]);
-          tmem_ld32(t + kTileN, v);
-          tmem_ld32(t + kTileN + 32, v + 32);
-          tmem_ld_wait_pin<64>(v);
-        } else {
+          for (int q = 0; q < 4; ++q) {  // gate columns 0-31, 32-63, then up columns 0-31, 32-63
+            float v[32];
+            if (ok) {
+              tmem_ld32(t + (q >> 1) * kTileN + (q & 1) * 32, v);
+              tmem_ld_wait_pin<32>(v);
+            } else {
 #pragma unroll
-          for (int i = 0; i < 64; ++i) v[i] = 0.f;
+              for (int i = 0; i < 32; ++i) v[i] = 0.f;
+            }
+            if (q == 3) {  // last piece is in registers: hand the TMEM stage back
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(my_acc_empty + 8 * acc);
+            }
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const float2 pv = make_float2(v[2 * i], v[2 * i + 1]);
+              if (q < 2) g[(q & 1) * 16 + i] = __ffma2_rn(pv, sg2v, g[(q & 1) * 16 + i]);
+              else u[(q & 1) * 16 + i] = __ffma2_rn(pv, su2v, u[(q & 1) * 16 + i]);
+            }
+          }
+          acc ^= 1;
+          if (acc == 0) acc_phase ^= 1u;
         }
-        // the partial is in registers: hand the TMEM stage back before the last FMAs
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(my_acc_empty + 8 * acc);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) u[i] = __ffma2_rn(make_float2(v[2 * i], v[2 * i + 1]), su2v, u[i]);
-        acc ^= 1;
-        if (acc == 0) acc_phase ^= 1u;
-        sx0 = sx1; sg0 = sg1; su0 = su1;
-        sx1 = sx2; sg1 = sg2; su1 = su2;
-      }
 
-      // next tile's coordinates and first scales, so their latency hides under the epilogue
-      const int cur_mb = mb, cur_nb = nb;
-      const int next = tile + gridDim.x;
-      if (next < p.num_tiles) start_tile(next);
-
-      // -------- epilogue: SwiGLU in registers, swizzled staging tile, TMA store --------
-      if (store_leader) tma_store_wait_read0();  // previous tile's store has finished reading the staging tile
-      named_bar_sync(1 + half, 128);
-      {
-        uint8_t* out_row = smem_gen + (out_half - smem_base) + row * 128;
+        if (jb != 0) {
+          // started inside the tile: publish the running sums for the range that owns the tile's first K block
+          float4* slot = reinterpret_cast<float4*>(p.partials + static_cast<size_t>(my_range) * kTilePartialFloats) + ctid;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {  // 8 chunks of 8 bf16 = 16 bytes
-          uint4 q;
-          q.x = swiglu_bf16x2(g[4 * c + 0], u[4 * c + 0]);
-          q.y = swiglu_bf16x2(g[4 * c + 1], u[4 * c + 1]);
-          q.z = swiglu_bf16x2(g[4 * c + 2], u[4 * c + 2]);
-          q.w = swiglu_bf16x2(g[4 * c + 3], u[4 * c + 3]);
-          *reinterpret_cast<uint4*>(out_row + ((c ^ (row & 7)) << 4)) = q;
+          for (int i = 0; i < 16; ++i) {  // 16-byte stores, consecutive threads 16 bytes apart
+            __stcg(slot + i * 256, make_float4(g[2 * i].x, g[2 * i].y, g[2 * i + 1].x, g[2 * i + 1].y));
+            __stcg(slot + (16 + i) * 256, make_float4(u[2 * i].x, u[2 * i].y, u[2 * i + 1].x, u[2 * i + 1].y));
+          }
+          __threadfence();
+          named_bar_sync(3, 256);
+          if (ctid == 0 && !ctx.aborted) st_release_gpu(p.flags + my_range, p.epoch);
+          continue;
+        }
+        if (je < p.kb) {
+          // owner of the tile's first K block: add the later ranges' sums, in range order
+          const unsigned long long units = static_cast<unsigned long long>(p.num_tiles) * p.kb;
+          const unsigned long long tile_end = static_cast<unsigned long long>(tile + 1) * p.kb;
+          for (int rr = my_range + 1; rr < ranges && units * rr / ranges < tile_end; ++rr) {
+            if (store_leader && !ctx.aborted) {
+              unsigned long long t0 = 0;
+              for (uint32_t it = 1; ld_acquire_gpu(p.flags + rr) != p.epoch; ++it) {
+                __nanosleep(64);
+                if ((it & 255u) == 0u) {
+                  const unsigned long long now = globaltimer_ns();
+                  if (t0 == 0) {
+                    t0 = now;
+                  } else if (now - t0 > kWaitTimeoutNs || *ctx.cta_abort) {
+                    ctx.fail(kWaitTileFlag, (kWaitTileFlag << 24) | (blockIdx.x & 0xffffffu));
+                    break;
+                  }
+                }
+              }
+            }
+            named_bar_sync(1 + half, 128);
+            if (!*ctx.cta_abort) {
+              const float4* slot =
+                  reinterpret_cast<const float4*>(p.partials + static_cast<size_t>(rr) * kTilePartialFloats) + ctid;
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                const float4 a = __ldcg(slot + i * 256);
+                const float4 b = __ldcg(slot + (16 + i) * 256);
+                g[2 * i].x += a.x; g[2 * i].y += a.y; g[2 * i + 1].x += a.z; g[2 * i + 1].y += a.w;
+                u[2 * i].x += b.x; u[2 * i].y += b.y; u[2 * i + 1].x += b.z; u[2 * i + 1].y += b.w;
+              }
+            }
+          }
+        }
+        // -------- epilogue, as in the data-parallel schedule --------
+        if (store_leader) tma_store_wait_read0();
+        named_bar_sync(1 + half, 128);
+        {
+          uint8_t* out_row = smem_gen + (out_half - smem_base) + row * 128;
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            uint4 q;
+            q.x = swiglu_bf16x2(g[4 * c + 0], u[4 * c + 0]);
+            q.y = swiglu_bf16x2(g[4 * c + 1], u[4 * c + 1]);
+            q.z = swiglu_bf16x2(g[4 * c + 2], u[4 * c + 2]);
+            q.w = swiglu_bf16x2(g[4 * c + 3], u[4 * c + 3]);
+            *reinterpret_cast<uint4*>(out_row + ((c ^ (row & 7)) << 4)) = q;
+          }
+        }
+        fence_proxy_async_smem();
+        named_bar_sync(1 + half, 128);
+        if (store_leader && !ctx.aborted) {
+          tma_store_2d(&tm_out, out_half, nb * kTileN + half * 64, mb * kTileM);
+          tma_store_commit();
         }
       }
-      fence_proxy_async_smem();
-      named_bar_sync(1 + half, 128);
-      if (store_leader && !ctx.aborted) {
-        tma_store_2d(&tm_out, out_half, cur_nb * kTileN + half * 64, cur_mb * kTileM);
-        tma_store_commit();
-      }
-      tile = next;
     }
     if (store_leader) tma_store_wait_all0();
   }

@@ -18,10 +18,10 @@ from typing import Dict, Optional, Tuple
 import torch
 
 from . import _cabi
-from ._cabi import PLAN_AUTO, PLAN_STREAM, PLAN_TILE, GuProblem
+from ._cabi import PLAN_AUTO, PLAN_STREAM, PLAN_TILE, PLAN_TILE_DP, PLAN_TILE_SK, GuProblem
 
 BLOCK = 128
-_PLANS = {"auto": PLAN_AUTO, "tile": PLAN_TILE, "stream": PLAN_STREAM}
+_PLANS = {"auto": PLAN_AUTO, "tile": PLAN_TILE, "stream": PLAN_STREAM, "tile_dp": PLAN_TILE_DP, "tile_sk": PLAN_TILE_SK}
 
 # Scratch for the stream-K hand-off, one buffer per (device, stream): it is
 # written and consumed inside a single call and carries no result across calls.
@@ -120,7 +120,8 @@ def run(x: torch.Tensor, scale_x: torch.Tensor, gate_proj_weight: torch.Tensor, 
 
 @torch.no_grad()
 def run_with_plan(x, scale_x, gate_proj_weight, scale_gate, up_proj_weight, scale_up, output, plan: str) -> None:
-    """`run` with the kernel forced ('tile', 'stream' or 'auto'); used by the M-sweep study and the tests."""
+    """`run` with the kernel forced: 'tile' (schedule by heuristic), 'tile_dp' / 'tile_sk' (data-parallel /
+    stream-K schedule), 'stream' or 'auto'; used by the M-sweep study and the tests."""
     if plan not in _PLANS:
         raise ValueError(f"unknown plan {plan!r}")
     _launch(x, scale_x, gate_proj_weight, scale_gate, up_proj_weight, scale_up, output, plan)

@@ -55,8 +55,13 @@ def test_plan_rejects_bad_shapes(gateup_lib, shape):
 
 def test_workspace_sizes(gateup_lib):
     lib = gateup_lib.lib
-    assert lib.gu_workspace_bytes(4096, 4096, 14336, gateup_lib.PLAN_AUTO) == 0
+    assert lib.gu_workspace_bytes(4096, 4096, 14336, gateup_lib.PLAN_AUTO) == 0      # 3584 tiles: data-parallel
     assert lib.gu_workspace_bytes(4096, 4096, 14336, gateup_lib.PLAN_TILE) == 0
+    assert lib.gu_workspace_bytes(4096, 4096, 14336, gateup_lib.PLAN_TILE_DP) == 0
+    sk = 4096 + 256 * 128 * 256 * 4
+    assert lib.gu_workspace_bytes(4096, 4096, 14336, gateup_lib.PLAN_TILE_SK) == sk
+    assert lib.gu_workspace_bytes(512, 4096, 14336, gateup_lib.PLAN_AUTO) == 0        # heuristic keeps data-parallel
+    assert lib.gu_workspace_bytes(128, 4096, 14336, gateup_lib.PLAN_TILE_SK) == sk
     w16 = lib.gu_workspace_bytes(16, 8192, 28672, gateup_lib.PLAN_AUTO)
     w64 = lib.gu_workspace_bytes(64, 8192, 28672, gateup_lib.PLAN_STREAM)
     assert w16 == 4096 + 256 * 2 * 16 * 128 * 4

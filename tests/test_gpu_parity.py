@@ -80,6 +80,16 @@ def test_tile_kernel_parity(pkg, shape):
     _check(_run(pkg, inp, "tile"), inp, f"tile {shape}")
 
 
+@pytest.mark.parametrize("shape", TILE_SHAPES + [(128, 4096, 2048), (512, 1024, 1792), (2000, 256, 640)])
+def test_tile_kernel_stream_k_schedule_parity(pkg, shape):
+    # same kernel, (tile, K block) units cut into equal ranges: partial sums cross CTAs through scratch
+    inp = W.make_inputs(*shape, seed=1)
+    out = _run(pkg, inp, "tile_sk")
+    _check(out, inp, f"tile_sk {shape}")
+    st = O.error_stats(out, _run(pkg, inp, "tile_dp"))
+    assert st["rel_l2"] <= 1e-4, st
+
+
 @pytest.mark.parametrize("shape", STREAM_SHAPES)
 def test_stream_kernel_parity(pkg, shape):
     inp = W.make_inputs(*shape, seed=2)
@@ -105,12 +115,13 @@ def test_small_config_through_public_run(pkg):
     before = pkg.launch_count()
     assert pkg.run(*g.args(), out) is None
     torch.cuda.synchronize()
-    assert pkg.launch_count() == before + 1          # one fused kernel, where the reference launches three
+    assert pkg.launch_count() == before + 1          # one fused kernel (44 tiles: one schedule), the reference launches three
     _check(out, inp, "small config")
 
 
 def test_deterministic(pkg):
-    for shape, plan in (((300, 512, 384), "tile"), ((16, 8192, 2048), "stream"), ((7, 2048, 5632), "stream")):
+    for shape, plan in (((300, 512, 384), "tile_dp"), ((300, 512, 384), "tile_sk"), ((128, 4096, 2048), "tile_sk"),
+                        ((16, 8192, 2048), "stream"), ((7, 2048, 5632), "stream")):
         inp = W.make_inputs(*shape, seed=4)
         a = _run(pkg, inp, plan).clone()
         for _ in range(3):

@@ -32,7 +32,11 @@ def test_shards_on_one_gpu_reproduce_unsharded_output(shape, world):
         assert pkg.run_sharded(inp.x, inp.scale_x, gw, sg, uw, su, full[:, lo:hi]) is None
     torch.cuda.synchronize()
     assert pkg.last_status()[0] == 0
-    assert torch.equal(full, ref)
+    # bit-identical unless a shard's tile count picks the other schedule (stream-K adds its partial sums in
+    # another grouping); then only isolated bf16 flips may differ
+    diff = (full.float() - ref.float()).abs()
+    assert float(torch.linalg.vector_norm(diff) / torch.linalg.vector_norm(ref.float())) <= 1e-4
+    assert int((diff > 2e-2).sum()) <= max(3, 5e-5 * diff.numel())
 
 
 _RANK_SCRIPT = r"""
