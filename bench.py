@@ -2,6 +2,7 @@
 """Benchmark of the FP8 gate/up + SwiGLU hot path.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME] [--gather]
+    python bench.py --sweep            # M in {1,8,32,128,512,2048,8192} at K=4096, N=14336: plan crossover
 
 A step is one pass of the fused op over one synthetic workload (seeded
 N(0,1) activations, N(0,0.02) weights, e4m3 block quantisation).
@@ -175,6 +176,42 @@ def cpu_baseline(inp_cpu, oracle, max_flops: float = 2.0e12):
     }
 
 
+def run_sweep(args):
+    """M sweep at K=4096, N=14336: every plan that can run each M, the heuristic's pick and the roofline fraction."""
+    import sol_execbench_b200_kernels_b200 as pkg
+    from sol_execbench_b200_kernels_b200 import workloads as W
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    peaks = load_peaks()
+    flush = torch.empty(L2_FLUSH_BYTES // 4, dtype=torch.int32, device=dev)
+    k, n = W.SWEEP_KN
+    rows = []
+    for m in W.SWEEP_M:
+        inp = W.make_inputs(m, k, n, seed=0, device=dev)
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+        entry = {"m": m, "auto_plan": pkg.select_plan(m, k, n), "plans": {}}
+        for plan in (("stream", "tile") if m <= 64 else ("tile",)):
+            ms, _ = time_device_steps(lambda: pkg.run_with_plan(*inp.args(), out, plan), args.steps, args.warmup, flush)
+            ms /= args.steps
+            roof = roofline_for(m, k, n, ms, peaks, W)
+            entry["plans"][plan] = {"us": round(ms * 1e3, 2), "bound": roof["bound"], "achieved": roof["achieved"],
+                                    "unit": roof["unit"], "frac": roof["frac"],
+                                    "tflops": round(W.algorithmic_flops(m, k, n) / (ms * 1e-3) / 1e12, 1),
+                                    "gbs": round(W.algorithmic_bytes(m, k, n) / (ms * 1e-3) / 1e9, 1)}
+        best = min(entry["plans"], key=lambda q: entry["plans"][q]["us"])
+        entry["fastest"] = best
+        rows.append(entry)
+        del inp, out
+    code, detail = pkg.last_status()
+    if code != 0:
+        raise SystemExit(f"bench.py: device status {code} detail {detail:#x}")
+    print(json.dumps({"metric": METRIC, "sweep": {"k": k, "n": n, "rows": rows}, "steps": args.steps,
+                      "warmup": args.warmup, "data": "synthetic",
+                      "peaks": {"fp8_tflops": 2.0 * peaks["bf16_tflops"], "hbm_gbs": peaks["hbm_gbs"],
+                                "source": peaks["_source"]}}), flush=True)
+
+
 def run_ours(args):
     import torch.distributed as dist
 
@@ -217,16 +254,16 @@ def run_ours(args):
             if n_gpus > 1 else pkg.run(*local.args(), out)
 
     barrier = (lambda: dist.barrier()) if n_gpus > 1 else None
-    launches0 = pkg.launch_count()
     with ClockSampler(local_rank) as clocks:
+        launches0 = pkg.launch_count()
         total_ms, per = time_device_steps(step, args.steps, args.warmup, flush, barrier)
+        launches_timed = (pkg.launch_count() - launches0) * args.steps // (args.steps + args.warmup)
         # keep the GPU busy long enough for a few clock samples when the steps are very short
         t_end = time.perf_counter() + max(0.0, 0.4 - total_ms * 1e-3)
         while time.perf_counter() < t_end:
             step()
         torch.cuda.synchronize()
-    launches_timed = args.steps  # one fused kernel per step (pkg.launch_count() confirms below)
-    assert pkg.launch_count() - launches0 >= args.steps + args.warmup
+    assert launches_timed >= args.steps  # at least one kernel of this library per step
     code, detail = pkg.last_status()
     if code != 0:
         raise SystemExit(f"bench.py: device status {code} detail {detail:#x}")
@@ -377,10 +414,13 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", default=None, help="override: one of workloads.SHAPES")
     ap.add_argument("--gather", action="store_true", help="N>1: also all-gather the contiguous [M, N] output")
+    ap.add_argument("--sweep", action="store_true", help="M sweep at K=4096, N=14336 on one GPU (plan crossover study)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)
+    elif args.sweep:
+        run_sweep(args)
     else:
         run_ours(args)
 

@@ -369,7 +369,15 @@ const char* gu_error_string(int code) {
 
 int gu_select_plan(int64_t m, int64_t k, int64_t n) {
   if (!gu::shape_ok(m, k, n)) return GU_EINVAL_SHAPE;
-  if (m <= 64 && gu::stream_stages(gu::stream_mpad(m), k / 128) > 0) return GU_PLAN_STREAM;
+  // Measured crossover on B200 (both kernels on the same shapes): with up to 16 tokens the weight-streaming
+  // kernel wins or ties once the weights exceed ~64 MB (its equal unit ranges keep all SMs streaming whatever
+  // N/128 is); with 17-32 tokens it still wins on large weights (M=32, K=8192, N=28672: 84 us against 94 us)
+  // but loses on mid-sized ones (K=4096, N=14336: 34.6 us against 28.8 us); from 33 tokens on the tile kernel
+  // is faster everywhere (its consumers do one FMA per element, the streaming kernel's do two).
+  const int64_t weight_bytes = 2 * n * k;
+  const bool can_stream = m <= 64 && gu::stream_stages(gu::stream_mpad(m), k / 128) > 0;
+  if (can_stream && ((m <= 16 && weight_bytes >= (64ll << 20)) || (m <= 32 && weight_bytes >= (256ll << 20))))
+    return GU_PLAN_STREAM;
   return GU_PLAN_TILE;
 }
 

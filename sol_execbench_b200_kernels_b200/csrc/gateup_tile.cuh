@@ -265,7 +265,7 @@ gateup_tile_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
 
       while (tile < p.num_tiles) {
         float2 g[32], u[32];  // 64 gate + 64 up running sums
-  #pragma unroll
+#pragma unroll
         for (int i = 0; i < 32; ++i) {
           g[i] = make_float2(0.f, 0.f);
           u[i] = make_float2(0.f, 0.f);
@@ -288,20 +288,20 @@ gateup_tile_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
             tmem_ld32(t, v);
             tmem_ld32(t + 32, v + 32);
             tmem_ld_wait_pin<64>(v);
-  #pragma unroll
+#pragma unroll
             for (int i = 0; i < 32; ++i) g[i] = __ffma2_rn(make_float2(v[2 * i], v[2 * i + 1]), sg2v, g[i]);
             tmem_ld32(t + kTileN, v);
             tmem_ld32(t + kTileN + 32, v + 32);
             tmem_ld_wait_pin<64>(v);
           } else {
-  #pragma unroll
+#pragma unroll
             for (int i = 0; i < 64; ++i) v[i] = 0.f;
           }
           // the partial is in registers: hand the TMEM stage back before the last FMAs
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(my_acc_empty + 8 * acc);
-  #pragma unroll
+#pragma unroll
           for (int i = 0; i < 32; ++i) u[i] = __ffma2_rn(make_float2(v[2 * i], v[2 * i + 1]), su2v, u[i]);
           acc ^= 1;
           if (acc == 0) acc_phase ^= 1u;
@@ -319,7 +319,7 @@ gateup_tile_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
         named_bar_sync(1 + half, 128);
         {
           uint8_t* out_row = smem_gen + (out_half - smem_base) + row * 128;
-  #pragma unroll
+#pragma unroll
           for (int c = 0; c < 8; ++c) {  // 8 chunks of 8 bf16 = 16 bytes
             uint4 q;
             q.x = swiglu_bf16x2(g[4 * c + 0], u[4 * c + 0]);

@@ -32,7 +32,7 @@ def select_plan(m: int, k: int, n: int) -> str:
     """Name of the kernel the heuristic picks for a shape ('tile' or 'stream').
 
     Counterpart of the reference's `_select_config` (kernel.py:232-249), which has
-    no small-M branch; here M <= 64 streams the weights with stream-K.
+    no small-M branch; here decode-sized M on large weights streams them with stream-K.
     """
     code = _cabi.lib.gu_select_plan(m, k, n)
     _cabi.check(min(code, 0))

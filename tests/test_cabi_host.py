@@ -38,7 +38,8 @@ def test_struct_layout_matches_header(gateup_lib):
 
 
 @pytest.mark.parametrize("shape,plan", [
-    ((16, 8192, 28672), "stream"), ((1, 4096, 14336), "stream"), ((64, 4096, 14336), "stream"),
+    ((16, 8192, 28672), "stream"), ((1, 4096, 14336), "stream"), ((32, 8192, 28672), "stream"),
+    ((32, 4096, 14336), "tile"), ((64, 8192, 28672), "tile"), ((16, 2048, 5632), "tile"),
     ((65, 4096, 14336), "tile"), ((128, 2048, 5632), "tile"), ((4096, 4096, 14336), "tile"),
     ((16384, 7168, 18432), "tile"),
 ])
