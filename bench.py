@@ -46,7 +46,7 @@ def flush_l2(buf: torch.Tensor) -> None:
 
 # Measured DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum from the ncu
 # captures summarised under profiles/), keyed by workload; None until a capture exists.
-NCU_TRAFFIC_BYTES = {}
+NCU_TRAFFIC_BYTES = {"prefill_8b": 227_744_256, "decode_70b": 477_501_184}
 
 
 def load_peaks():
@@ -184,7 +184,7 @@ def run_sweep(args):
     torch.cuda.set_device(0)
     dev = torch.device("cuda", 0)
     peaks = load_peaks()
-    flush = torch.empty(L2_FLUSH_BYTES // 4, dtype=torch.int32, device=dev)
+    flush = torch.empty(L2_FLUSH_BYTES // 4, dtype=torch.float32, device=dev)
     k, n = W.SWEEP_KN
     rows = []
     for m in W.SWEEP_M:
@@ -245,7 +245,7 @@ def run_ours(args):
         local = full
     n_local = local.gate_proj_weight.shape[0]
     out = torch.empty(m, n_local, dtype=torch.bfloat16, device=dev)
-    flush = torch.empty(L2_FLUSH_BYTES // 4, dtype=torch.int32, device=dev)
+    flush = torch.empty(L2_FLUSH_BYTES // 4, dtype=torch.float32, device=dev)
     gathered = torch.empty(m, n, dtype=torch.bfloat16, device=dev) if (args.gather and n_gpus > 1) else None
     scratch = torch.empty(world, m, n_local, dtype=torch.bfloat16, device=dev) if gathered is not None else None
 
