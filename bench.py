@@ -249,9 +249,15 @@ def run_ours(args):
     gathered = torch.empty(m, n, dtype=torch.bfloat16, device=dev) if (args.gather and n_gpus > 1) else None
     scratch = torch.empty(world, m, n_local, dtype=torch.bfloat16, device=dev) if gathered is not None else None
 
+    buffers = pkg.GatherBuffers(m, n, dev) if (args.fused_gather and n_gpus > 1) else None
+
     def step():
-        pkg.run_sharded(*local.args(), out, gather=gathered is not None, gathered_out=gathered, scratch=scratch) \
-            if n_gpus > 1 else pkg.run(*local.args(), out)
+        if buffers is not None:
+            pkg.run_sharded_fused(*local.args(), buffers)
+        elif n_gpus > 1:
+            pkg.run_sharded(*local.args(), out, gather=gathered is not None, gathered_out=gathered, scratch=scratch)
+        else:
+            pkg.run(*local.args(), out)
 
     barrier = (lambda: dist.barrier()) if n_gpus > 1 else None
     with ClockSampler(local_rank) as clocks:
@@ -322,7 +328,7 @@ def run_ours(args):
             "vs_baseline": None, "dtype": "fp8_e4m3 x fp8_e4m3 -> f32 accumulate -> bf16", "data": "synthetic",
             "config": {"workload": f"{workload}: M={m} K={k} N={n}", "sharding": f"N column-sharded over {n_gpus}" if n_gpus > 1 else "none",
                        "per_rank_n": n_local, "plan": pkg.select_plan(m, k, n_local),
-                       "gather": bool(gathered is not None),
+                       "gather": "fused peer stores" if buffers is not None else ("nccl" if gathered is not None else False),
                        "l2": f"flushed before every timed step by writing, then reading back, a {L2_FLUSH_BYTES >> 20} MiB buffer"},
             "roofline": roof, "e2e": e2e, "gpu_launches": launches_timed,
             "clocks": clocks.summary(),
@@ -414,6 +420,8 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", default=None, help="override: one of workloads.SHAPES")
     ap.add_argument("--gather", action="store_true", help="N>1: also all-gather the contiguous [M, N] output")
+    ap.add_argument("--fused-gather", action="store_true",
+                    help="N>1: contiguous [M, N] output on every rank through peer stores in the kernel epilogue")
     ap.add_argument("--sweep", action="store_true", help="M sweep at K=4096, N=14336 on one GPU (plan crossover study)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

@@ -114,6 +114,19 @@ int gu_run_concat(const void* x, const float* scale_x, const void* w2n, const fl
                   void* workspace, size_t workspace_bytes, int plan, void* stream);
 
 /*
+ * Column-parallel variant with the all-gather fused into the epilogue.  `problem` describes this
+ * rank's shard (n = N / world columns; `output`, `workspace`, `plan` are ignored); `rank_outputs[r]`
+ * is rank r's full bf16 [M, ld_full] buffer (N = n * world columns) mapped into this process (its own
+ * buffer for r == rank, peers' buffers through CUDA peer / symmetric-memory mappings).  Every output
+ * tile is written by plain TMA stores into all `world` buffers at column offset rank * n, so after
+ * all ranks' launches have completed (a cross-rank barrier is the caller's job) every rank holds the
+ * contiguous [M, N] result.  world <= 8.  No load ever touches peer memory.  The reference is
+ * single-GPU and has no counterpart; it stands where an NCCL all-gather + permute would follow gu_run.
+ */
+int gu_run_gather(const gu_problem* problem, void* const* rank_outputs, int world, int rank, int64_t ld_full,
+                  void* stream);
+
+/*
  * Device-side status of the current device: 0, or GU_ETIMEOUT with `detail`
  * = (wait id << 24 | block index) of the first wait that gave up.  Synchronises
  * the device; meant for tests and debugging, never for the timed path.  The

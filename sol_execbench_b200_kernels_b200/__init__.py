@@ -10,10 +10,10 @@ with `python -m sol_execbench_b200_kernels_b200.build`.  Importing the compute
 entry points without the built library raises: there is no fallback path.
 """
 from . import workloads  # noqa: F401  (pure torch, no native code)
-from .sharded import (assemble_gathered, gather_columns, run_sharded, shard_bounds,  # noqa: F401
-                      shard_concat_weights, shard_weights)
+from .sharded import (GatherBuffers, assemble_gathered, gather_columns, run_sharded,  # noqa: F401
+                      run_sharded_fused, shard_bounds, shard_concat_weights, shard_weights)
 
-_NATIVE = ("run", "run_concat", "run_with_plan", "select_plan", "last_status", "launch_count")
+_NATIVE = ("run", "run_concat", "run_with_plan", "run_gather", "select_plan", "last_status", "launch_count")
 
 
 def __getattr__(name):
@@ -24,5 +24,5 @@ def __getattr__(name):
     raise AttributeError(name)
 
 
-__all__ = list(_NATIVE) + ["workloads", "run_sharded", "shard_bounds", "shard_weights", "shard_concat_weights",
-                           "gather_columns", "assemble_gathered"]
+__all__ = list(_NATIVE) + ["workloads", "run_sharded", "run_sharded_fused", "GatherBuffers", "shard_bounds",
+                           "shard_weights", "shard_concat_weights", "gather_columns", "assemble_gathered"]

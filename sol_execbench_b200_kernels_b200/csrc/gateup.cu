@@ -116,6 +116,8 @@ int device_info(DeviceInfo** out) {
             cudaSuccess ||
         cudaFuncSetAttribute(gateup_tile_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
             cudaSuccess ||
+        cudaFuncSetAttribute(gateup_tile_gather_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
+            cudaSuccess ||
         cudaFuncSetAttribute(gateup_stream_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
             cudaSuccess ||
         cudaFuncSetAttribute(gateup_stream_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
@@ -225,6 +227,8 @@ int launch_tile(const gu_problem* pr, const DeviceInfo& dev, cudaStream_t stream
   p.partials = nullptr;
   p.epoch = 0;
   p.tile_begin = 0;
+  p.out_count = 1;
+  p.out_col0 = 0;
   const int total_tiles = p.num_tiles;
   const int sms = dev.sm_count;
   // Hybrid schedule: whole rounds of tiles run data-parallel; the last round plus the remainder (between one and
@@ -500,6 +504,64 @@ int gu_run_decode_static(const gu_problem* pr, void* stream_v) {
   const uint32_t smem = gu::StreamCfg<16>::smem_bytes(stages, p.kb);
   gu::gateup_stream_kernel<16><<<static_cast<int>(grid), gu::kStreamThreads, smem,
                                  static_cast<cudaStream_t>(stream_v)>>>(tm_x, tm_g, tm_u, p);
+  gu::g_launches.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError() == cudaSuccess ? GU_OK : GU_ECUDA;
+}
+
+int gu_run_gather(const gu_problem* pr, void* const* rank_outputs, int world, int rank, int64_t ld_full,
+                  void* stream_v) {
+  int rc = gu::check_problem(pr);
+  if (rc != GU_OK) return rc;
+  if (!rank_outputs) return GU_EINVAL_NULL;
+  if (world < 1 || world > 8 || rank < 0 || rank >= world) return GU_EINVAL_SHAPE;
+  const int64_t m = pr->m, k = pr->k, n = pr->n, n_full = n * world;
+  if (ld_full < n_full) return GU_EINVAL_SHAPE;
+  if (ld_full % 8 != 0) return GU_EINVAL_ALIGN;
+  for (int r = 0; r < world; ++r) {
+    if (!rank_outputs[r]) return GU_EINVAL_NULL;
+    if (!gu::aligned16(rank_outputs[r])) return GU_EINVAL_ALIGN;
+  }
+  gu::DeviceInfo* dev = nullptr;
+  if ((rc = gu::device_info(&dev)) != GU_OK) return rc;
+
+  CUtensorMap tm_x, tm_g, tm_u;
+  gu::PeerMaps peers;
+  std::memset(&peers, 0, sizeof(peers));
+  if ((rc = gu::get_map(&tm_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, pr->x, k, m, k, 128, 128)) != GU_OK) return rc;
+  if ((rc = gu::get_map(&tm_g, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, pr->gate_w, k, n, k, 128, 128)) != GU_OK) return rc;
+  if ((rc = gu::get_map(&tm_u, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, pr->up_w, k, n, k, 128, 128)) != GU_OK) return rc;
+  for (int r = 0; r < world; ++r) {
+    // each rank's full [M, N * world] buffer; stores land at this rank's column offset
+    if ((rc = gu::get_map(&peers.m[r], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rank_outputs[r], n_full, m, ld_full * 2,
+                          64, 128)) != GU_OK)
+      return rc;
+  }
+
+  gu::TileParams p;
+  p.scale_x = pr->scale_x;
+  p.scale_gate = pr->scale_gate;
+  p.scale_up = pr->scale_up;
+  p.m = static_cast<int>(m);
+  p.kb = static_cast<int>(k / 128);
+  p.num_m_blocks = static_cast<int>((m + gu::kTileM - 1) / gu::kTileM);
+  p.num_n_blocks = static_cast<int>(n / gu::kTileN);
+  const int64_t tiles = int64_t(p.num_m_blocks) * p.num_n_blocks;
+  if (tiles * (k / 128) >= (1ll << 31)) return GU_EINVAL_SHAPE;
+  p.num_tiles = static_cast<int>(tiles);
+  int64_t gm = (24ll << 20) / (128 * k);
+  if (gm < 1) gm = 1;
+  if (gm > p.num_m_blocks) gm = p.num_m_blocks;
+  p.group_m = static_cast<int>(gm);
+  p.tile_begin = 0;
+  p.flags = nullptr;
+  p.partials = nullptr;
+  p.epoch = 0;
+  p.out_count = world;
+  p.out_col0 = static_cast<int>(int64_t(rank) * n);
+
+  const int grid = p.num_tiles < dev->sm_count ? p.num_tiles : dev->sm_count;
+  gu::gateup_tile_gather_kernel<<<grid, gu::kTileThreads, gu::kTileSmemBytes, static_cast<cudaStream_t>(stream_v)>>>(
+      tm_x, tm_g, tm_u, peers, p);
   gu::g_launches.fetch_add(1, std::memory_order_relaxed);
   return cudaGetLastError() == cudaSuccess ? GU_OK : GU_ECUDA;
 }

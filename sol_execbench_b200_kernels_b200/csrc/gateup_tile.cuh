@@ -67,6 +67,10 @@ struct TileParams {
   int num_m_blocks, num_n_blocks, num_tiles;
   int group_m;              // M blocks per raster group (keeps a group's X tiles L2-resident)
   int tile_begin;           // stream-K launch: covers tiles [tile_begin, tile_begin + num_tiles) of the raster
+  // gather launch only: every output tile is stored into out_count buffers (one per rank of the box) at a
+  // column offset, so the all-gather of a column-sharded result happens inside the epilogue
+  int out_count;
+  int out_col0;
   // stream-K schedule only
   unsigned int* flags;      // [gridDim.x] epoch of the last call that filled slot i
   float* partials;          // [gridDim.x][32][256] float4: values 4i..4i+3 of consumer thread t at [i * 256 + t]
@@ -123,11 +127,16 @@ __device__ __forceinline__ void tile_coords(const TileParams& p, int tile, int& 
   mb = first_m + (r - nb * gm);
 }
 
-template <bool kStreamK>
-__global__ void __launch_bounds__(kTileThreads, 1)
-gateup_tile_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_gate,
-                   const __grid_constant__ CUtensorMap tm_up, const __grid_constant__ CUtensorMap tm_out,
-                   const TileParams p) {
+// Up to one output descriptor per GPU of the box (the gather launch stores every tile to all of them).
+struct PeerMaps {
+  CUtensorMap m[8];
+};
+
+// The kernel body; `outs` points at the output descriptor(s) in kernel parameter space.
+template <bool kStreamK, bool kGather>
+__device__ __forceinline__ void tile_kernel_body(const CUtensorMap& tm_x, const CUtensorMap& tm_gate,
+                                                 const CUtensorMap& tm_up, const CUtensorMap* outs,
+                                                 const TileParams& p) {
   extern __shared__ uint8_t smem_raw[];
   // operand tiles need 1024-byte alignment for the 128-byte swizzle pattern
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -164,7 +173,11 @@ gateup_tile_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     tma_prefetch_desc(&tm_x);
     tma_prefetch_desc(&tm_gate);
     tma_prefetch_desc(&tm_up);
-    tma_prefetch_desc(&tm_out);
+    if constexpr (kGather) {
+      for (int r = 0; r < p.out_count; ++r) tma_prefetch_desc(&outs[r]);
+    } else {
+      tma_prefetch_desc(&outs[0]);
+    }
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, kTileTmemCols);
@@ -332,7 +345,13 @@ gateup_tile_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
         fence_proxy_async_smem();
         named_bar_sync(1 + half, 128);
         if (store_leader && !ctx.aborted) {
-          tma_store_2d(&tm_out, out_half, cur_nb * kTileN + half * 64, cur_mb * kTileM);
+          if constexpr (kGather) {
+            // plain TMA stores, one per rank's buffer (own and peers' over NVLink); no load touches peer memory
+            for (int r = 0; r < p.out_count; ++r)
+              tma_store_2d(&outs[r], out_half, p.out_col0 + cur_nb * kTileN + half * 64, cur_mb * kTileM);
+          } else {
+            tma_store_2d(&outs[0], out_half, cur_nb * kTileN + half * 64, cur_mb * kTileM);
+          }
           tma_store_commit();
         }
         tile = next;
@@ -461,7 +480,7 @@ gateup_tile_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
         fence_proxy_async_smem();
         named_bar_sync(1 + half, 128);
         if (store_leader && !ctx.aborted) {
-          tma_store_2d(&tm_out, out_half, nb * kTileN + half * 64, mb * kTileM);
+          tma_store_2d(&outs[0], out_half, nb * kTileN + half * 64, mb * kTileM);
           tma_store_commit();
         }
       }
@@ -479,6 +498,22 @@ gateup_tile_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
   }
   if (warp == 1) tmem_dealloc(tmem_base, kTileTmemCols);
+}
+
+template <bool kStreamK>
+__global__ void __launch_bounds__(kTileThreads, 1)
+gateup_tile_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_gate,
+                   const __grid_constant__ CUtensorMap tm_up, const __grid_constant__ CUtensorMap tm_out,
+                   const TileParams p) {
+  tile_kernel_body<kStreamK, false>(tm_x, tm_gate, tm_up, &tm_out, p);
+}
+
+// Data-parallel schedule with the column all-gather fused into the epilogue (see TileParams::out_count).
+__global__ void __launch_bounds__(kTileThreads, 1)
+gateup_tile_gather_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_gate,
+                          const __grid_constant__ CUtensorMap tm_up, const __grid_constant__ PeerMaps peers,
+                          const TileParams p) {
+  tile_kernel_body<false, true>(tm_x, tm_gate, tm_up, peers.m, p);
 }
 
 }  // namespace gu

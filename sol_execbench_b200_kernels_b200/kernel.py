@@ -39,26 +39,30 @@ def select_plan(m: int, k: int, n: int) -> str:
     return _cabi.PLAN_NAMES[code]
 
 
-def _validate(x, scale_x, gate_w, scale_gate, up_w, scale_up, output) -> Tuple[int, int, int]:
-    """Same checks as the reference's `_debug_validate` / pybind `run`
-    (kernel.py:345-395, variants/cuda_cpp_v4/binding.cpp:26-72), for any K, N
-    multiple of 128 and any M >= 1; always on."""
-    if x.dim() != 2 or gate_w.dim() != 2 or up_w.dim() != 2 or output.dim() != 2:
-        raise ValueError("x, gate_proj_weight, up_proj_weight and output must be 2-D")
+def _expected_inputs(x, scale_x, gate_w, scale_gate, up_w, scale_up, m_expected=None, n_expected=None):
+    """(m, k, n) and the contract's (tensor, shape, dtype) per input name; raises on an unsupported M, K, N."""
+    if x.dim() != 2 or gate_w.dim() != 2 or up_w.dim() != 2:
+        raise ValueError("x, gate_proj_weight and up_proj_weight must be 2-D")
     m, k = x.shape
     n = gate_w.shape[0]
     if m < 1 or k % BLOCK or n % BLOCK or k < BLOCK or n < BLOCK:
         raise ValueError(f"Unsupported contract shape M={m}, K={k}, N={n}: need M >= 1 and K, N multiples of {BLOCK}")
+    if (m_expected is not None and m != m_expected) or (n_expected is not None and n != n_expected):
+        raise ValueError(f"Unsupported contract shape M={m}, N={n}: expected M={m_expected}, N={n_expected}")
     kb, nb = k // BLOCK, n // BLOCK
-    expected = {
+    return (m, k, n), {
         "x": (x, (m, k), torch.float8_e4m3fn),
         "scale_x": (scale_x, (m, kb), torch.float32),
         "gate_proj_weight": (gate_w, (n, k), torch.float8_e4m3fn),
         "scale_gate": (scale_gate, (nb, kb), torch.float32),
         "up_proj_weight": (up_w, (n, k), torch.float8_e4m3fn),
         "scale_up": (scale_up, (nb, kb), torch.float32),
-        "output": (output, (m, n), torch.bfloat16),
     }
+
+
+def _check(expected, device) -> None:
+    """Same checks as the reference's `_debug_validate` / pybind `run` (kernel.py:345-395,
+    variants/cuda_cpp_v4/binding.cpp:26-72): shapes and dtypes first, then device and layout; always on."""
     for name, (t, shape, dtype) in expected.items():
         if tuple(t.shape) != shape or t.dtype != dtype:
             raise ValueError(f"{name}: expected shape={shape}, dtype={dtype}; "
@@ -66,10 +70,25 @@ def _validate(x, scale_x, gate_w, scale_gate, up_w, scale_up, output) -> Tuple[i
     for name, (t, shape, dtype) in expected.items():
         if not t.is_cuda:
             raise ValueError(f"{name} must be a CUDA tensor (this package has no CPU path)")
-        if t.device != x.device:
-            raise ValueError(f"{name} is on {t.device}, x is on {x.device}")
+        if t.device != device:
+            raise ValueError(f"{name} is on {t.device}, x is on {device}")
         if name != "output" and not t.is_contiguous():
             raise ValueError(f"{name} must be contiguous")
+
+
+def _validate_inputs_only(x, scale_x, gate_w, scale_gate, up_w, scale_up, m_expected=None, n_expected=None):
+    (m, k, n), expected = _expected_inputs(x, scale_x, gate_w, scale_gate, up_w, scale_up, m_expected, n_expected)
+    _check(expected, x.device)
+    return m, k, n
+
+
+def _validate(x, scale_x, gate_w, scale_gate, up_w, scale_up, output) -> Tuple[int, int, int]:
+    """Inputs plus the destination: bf16 [M, N] on the same device, row-major with unit column stride."""
+    if output.dim() != 2:
+        raise ValueError("output must be 2-D")
+    (m, k, n), expected = _expected_inputs(x, scale_x, gate_w, scale_gate, up_w, scale_up)
+    expected["output"] = (output, (m, n), torch.bfloat16)
+    _check(expected, x.device)
     # output may be a column slice of a wider row-major buffer (sharded writes)
     if output.stride(1) != 1 or output.stride(0) < n:
         raise ValueError("output must be row-major with unit column stride")
@@ -141,6 +160,36 @@ def run_concat(x: torch.Tensor, scale_x: torch.Tensor, w: torch.Tensor, scale_w:
     if scale_w.dim() != 2 or scale_w.shape[0] != 2 * nb:
         raise ValueError(f"scale_w: expected {2 * nb} rows, got {tuple(scale_w.shape)}")
     run(x, scale_x, w[:n], scale_w[:nb], w[n:], scale_w[nb:], output)
+
+
+@torch.no_grad()
+def run_gather(x: torch.Tensor, scale_x: torch.Tensor, gate_shard: torch.Tensor, scale_gate_shard: torch.Tensor,
+               up_shard: torch.Tensor, scale_up_shard: torch.Tensor, rank_output_ptrs, rank: int,
+               m_n_full: Tuple[int, int], ld_full: int) -> None:
+    """This rank's column shard of the op, every output tile stored into all ranks' full [M, N] buffers.
+
+    `rank_output_ptrs[r]` is the device address of rank r's buffer as mapped into this process (see
+    `sharded.GatherBuffers`).  Asynchronous; the caller runs a cross-rank barrier before reading any buffer.
+    """
+    world = len(rank_output_ptrs)
+    m, n_full = m_n_full
+    n_local = gate_shard.shape[0]
+    if n_local * world != n_full:
+        raise ValueError(f"shard has {n_local} columns, expected {n_full} / {world}")
+    _validate_inputs_only(x, scale_x, gate_shard, scale_gate_shard, up_shard, scale_up_shard, m, n_local)
+    k = x.shape[1]
+    with torch.cuda.device(x.device):
+        stream_ptr = torch.cuda.current_stream(x.device).cuda_stream
+        ptrs = (ctypes.c_void_p * world)(*[int(p) for p in rank_output_ptrs])
+        pr = GuProblem(
+            x.data_ptr(), scale_x.data_ptr(), gate_shard.data_ptr(), scale_gate_shard.data_ptr(),
+            up_shard.data_ptr(), scale_up_shard.data_ptr(), int(rank_output_ptrs[rank]),
+            m, k, n_local, ld_full, None, 0, PLAN_TILE, 0)
+        code = _cabi.lib.gu_run_gather(ctypes.byref(pr), ptrs, world, rank, ld_full, stream_ptr)
+    if code != _cabi.GU_OK:
+        if code in (_cabi.GU_EINVAL_NULL, _cabi.GU_EINVAL_SHAPE, _cabi.GU_EINVAL_ALIGN, _cabi.GU_EINVAL_PLAN):
+            raise ValueError(f"libgateup: {_cabi.error_string(code)} (code {code})")
+        raise _cabi.GateUpError(code, _cabi.error_string(code))
 
 
 def last_status(clear: bool = True) -> Tuple[int, int]:

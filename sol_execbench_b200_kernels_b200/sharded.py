@@ -72,6 +72,50 @@ def gather_columns(local: torch.Tensor, group=None, out: Optional[torch.Tensor] 
     return assemble_gathered(scratch, out)
 
 
+class GatherBuffers:
+    """One bf16 [M, N] result buffer per rank, each mapped into every rank of the group.
+
+    Built on torch's symmetric memory (CUDA peer mappings over NVLink / NVSwitch).  `out` is this rank's
+    buffer; `ptrs[r]` the address of rank r's buffer in this process; `barrier()` enqueues a cross-rank
+    barrier on the current stream.  Allocate once and reuse: the rendezvous is collective and slow.
+    """
+
+    def __init__(self, m: int, n: int, device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.out = symm_mem.empty((m, n), dtype=torch.bfloat16, device=device)
+        self.handle = symm_mem.rendezvous(self.out, self.group)
+        self.rank = self.handle.rank
+        self.world = self.handle.world_size
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.shape = (m, n)
+
+    def barrier(self) -> None:
+        self.handle.barrier()
+
+
+@torch.no_grad()
+def run_sharded_fused(x: torch.Tensor, scale_x: torch.Tensor, gate_shard: torch.Tensor,
+                      scale_gate_shard: torch.Tensor, up_shard: torch.Tensor, scale_up_shard: torch.Tensor,
+                      buffers: GatherBuffers) -> torch.Tensor:
+    """Column-parallel op with the all-gather fused into the kernel epilogue.
+
+    Each rank computes its N/R columns and TMA-stores every output tile straight into all ranks' [M, N]
+    buffers (its own and, over NVLink, its peers'), so the transfer overlaps the math tile by tile and no
+    NCCL all-gather or permute follows.  A cross-rank barrier orders the stores before anyone reads.
+    Returns this rank's contiguous [M, N] result.
+    """
+    from .kernel import run_gather
+
+    # nobody may still be reading the buffers of the previous call when the first tile lands
+    buffers.barrier()
+    run_gather(x, scale_x, gate_shard, scale_gate_shard, up_shard, scale_up_shard, buffers.ptrs, buffers.rank,
+               buffers.shape, buffers.out.stride(0))
+    buffers.barrier()
+    return buffers.out
+
+
 @torch.no_grad()
 def run_sharded(x: torch.Tensor, scale_x: torch.Tensor, gate_shard: torch.Tensor, scale_gate_shard: torch.Tensor,
                 up_shard: torch.Tensor, scale_up_shard: torch.Tensor, output_shard: torch.Tensor,

@@ -58,6 +58,14 @@ pkg.run(*inp.args(), ref)
 torch.cuda.synchronize()
 assert pkg.last_status()[0] == 0
 assert torch.equal(full, ref), f"rank {rank}: gathered result differs"
+# the same gather fused into the kernel epilogue: tiles are stored straight into every rank's buffer
+bufs = pkg.GatherBuffers(m, n, dev)
+for _ in range(2):
+    bufs.out.fill_(float("nan"))
+    fused = pkg.run_sharded_fused(inp.x, inp.scale_x, gw, sg, uw, su, bufs)
+    torch.cuda.synchronize()
+    assert pkg.last_status()[0] == 0
+    assert torch.equal(fused, ref), f"rank {rank}: fused gather differs"
 dist.barrier()
 dist.destroy_process_group()
 print(f"rank {rank} ok")
