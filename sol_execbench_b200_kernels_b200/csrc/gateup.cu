@@ -233,6 +233,8 @@ int launch_tile(const gu_problem* pr, const DeviceInfo& dev, cudaStream_t stream
   const int sms = dev.sm_count;
   // Hybrid schedule: whole rounds of tiles run data-parallel; the last round plus the remainder (between one and
   // two rounds' worth of tiles, or everything when there is less than one round) is split into equal unit ranges.
+  // (Splitting only the remainder was measured too: a tile cut 32 ways makes its owner gather 31 partials one
+  // after the other, 134 us against 85 us data-parallel at M=512, K=4096, N=14336.)
   int dp_tiles = total_tiles;
   if (stream_k) {
     const int rounds = total_tiles / sms;
