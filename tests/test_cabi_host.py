@@ -94,6 +94,22 @@ def test_argument_validation_precedes_any_cuda_call(gateup_lib):
         == gateup_lib.GU_EINVAL_NULL
 
 
+def test_gather_entry_point_validates_before_any_cuda_call(gateup_lib):
+    lib = gateup_lib.lib
+    pr = _problem(gateup_lib)
+    ptrs = (ctypes.c_void_p * 2)(0x7000, 0x9000)
+    assert lib.gu_run_gather(None, ptrs, 2, 0, 256, None) == gateup_lib.GU_EINVAL_NULL
+    assert lib.gu_run_gather(ctypes.byref(pr), None, 2, 0, 256, None) == gateup_lib.GU_EINVAL_NULL
+    assert lib.gu_run_gather(ctypes.byref(pr), ptrs, 9, 0, 9 * 128, None) == gateup_lib.GU_EINVAL_SHAPE   # more than 8 ranks
+    assert lib.gu_run_gather(ctypes.byref(pr), ptrs, 2, 2, 256, None) == gateup_lib.GU_EINVAL_SHAPE       # rank out of range
+    assert lib.gu_run_gather(ctypes.byref(pr), ptrs, 2, 0, 128, None) == gateup_lib.GU_EINVAL_SHAPE       # pitch < N * world
+    assert lib.gu_run_gather(ctypes.byref(pr), ptrs, 2, 0, 260, None) == gateup_lib.GU_EINVAL_ALIGN
+    bad = (ctypes.c_void_p * 2)(0x7000, None)
+    assert lib.gu_run_gather(ctypes.byref(pr), bad, 2, 0, 256, None) == gateup_lib.GU_EINVAL_NULL
+    odd = (ctypes.c_void_p * 2)(0x7000, 0x9004)
+    assert lib.gu_run_gather(ctypes.byref(pr), odd, 2, 0, 256, None) == gateup_lib.GU_EINVAL_ALIGN
+
+
 @pytest.mark.skipif(torch.cuda.is_available(), reason="CPU-only check")
 def test_valid_problem_without_a_gpu_fails_loudly(gateup_lib):
     # nothing to fall back to: a well-formed call on a machine without a device is an error, not a CPU result

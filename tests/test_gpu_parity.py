@@ -321,3 +321,24 @@ def test_m_sweep_shapes(pkg, m):
     k, n = W.SWEEP_KN
     rows = sorted(set([0, m - 1] + list(range(0, m, max(1, m // 24)))))
     _sampled_check(pkg, f"sweep M={m}", (m, k, n), rows, [0, 56, n // 128 - 1])
+
+
+def test_host_pipeline_matches_device_run(pkg):
+    """Pinned-host activations in, pinned-host result out, chunked over three streams: same bits as `run`."""
+    from sol_execbench_b200_kernels_b200.host_pipeline import HostPipeline
+
+    m, k, n = 700, 512, 640
+    inp = W.make_inputs(m, k, n, seed=14)
+    ref = _run(pkg, inp, "auto").cpu()
+    g = inp.to("cuda:0")
+    pipe = HostPipeline(m, k, n, "cuda:0", chunks=3)
+    assert [hi - lo for lo, hi in pipe.bounds] == [256, 256, 188]
+    x_host = inp.x.view(torch.uint8).pin_memory().view(torch.float8_e4m3fn)
+    sx_host = inp.scale_x.pin_memory()
+    out_host = torch.zeros(m, n, dtype=torch.bfloat16).pin_memory()
+    for _ in range(2):
+        pipe.run(x_host, sx_host, g.gate_proj_weight, g.scale_gate, g.up_proj_weight, g.scale_up, out_host)
+        pipe.synchronize()
+        assert torch.equal(out_host, ref)
+    with pytest.raises(ValueError, match="pinned"):
+        pipe.run(inp.x, sx_host, g.gate_proj_weight, g.scale_gate, g.up_proj_weight, g.scale_up, out_host)
