@@ -364,6 +364,22 @@ def run_ours(args):
             "roofline": roofline_for(sm_, sk_, sn_, bms / bsteps, peaks, W)})
         del big, bout
         torch.cuda.empty_cache()
+        # the step in front of the path: bf16 activations -> e4m3 + 1x128 scales (pure streaming)
+        qx = torch.randn(sm_, sk_, device=dev, dtype=torch.bfloat16)
+        qq = torch.empty(sm_, sk_, dtype=torch.float8_e4m3fn, device=dev)
+        qs = torch.empty(sm_, sk_ // 128, dtype=torch.float32, device=dev)
+        qsteps = 20
+        qms, _ = time_device_steps(lambda: pkg.quantize_activation(qx, qq, qs), qsteps, 3, flush)
+        qbytes = sm_ * sk_ * 3 + sm_ * (sk_ // 128) * 4
+        qach = qbytes / (qms / qsteps * 1e-3) / 1e9
+        result["also"].append({
+            "workload": f"quantize_activation bf16 -> e4m3: M={sm_} K={sk_}", "ms_per_step": round(qms / qsteps, 5),
+            "steps": qsteps,
+            "roofline": {"bound": "hbm", "achieved": round(qach, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": round(qach / peaks["hbm_gbs"], 4), "traffic": None, "algorithmic_bytes": qbytes,
+                         "peak_source": "hbm_gbs, " + ("of measured" if peaks["_source"] == "measured" else "of fallback")}})
+        del qx, qq, qs
+        torch.cuda.empty_cache()
         from oracle import gateup_oracle as oracle  # CPU baseline leg: the only use of the checker here
 
         cpu_inp = W.make_inputs(m, k, n, seed=0, device="cpu")

@@ -127,6 +127,16 @@ int gu_run_gather(const gu_problem* problem, void* const* rank_outputs, int worl
                   void* stream);
 
 /*
+ * Activation quantiser, the step in front of gu_run: x[M, K] (bf16, or fp32 when x_is_f32 != 0; row pitch ld_x
+ * elements) -> q[M, K] e4m3 and scale[M, K/128] fp32 with scale = amax of the 1x128 block / 448, the layout
+ * `x` / `scale_x` of gu_problem.  The reference takes its activations already quantised
+ * (kernel.py:356-357), so it has no counterpart; the bits equal PyTorch's
+ * clamp(x / scale, -448, 448).to(float8_e4m3fn).  One streaming launch on `stream`.
+ */
+int gu_quantize_activation(const void* x, int x_is_f32, int64_t ld_x, void* q, float* scale, int64_t m, int64_t k,
+                           void* stream);
+
+/*
  * Device-side status of the current device: 0, or GU_ETIMEOUT with `detail`
  * = (wait id << 24 | block index) of the first wait that gave up.  Synchronises
  * the device; meant for tests and debugging, never for the timed path.  The

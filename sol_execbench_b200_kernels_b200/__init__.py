@@ -13,7 +13,8 @@ from . import workloads  # noqa: F401  (pure torch, no native code)
 from .sharded import (GatherBuffers, assemble_gathered, gather_columns, run_sharded,  # noqa: F401
                       run_sharded_fused, shard_bounds, shard_concat_weights, shard_weights)
 
-_NATIVE = ("run", "run_concat", "run_with_plan", "run_gather", "select_plan", "last_status", "launch_count")
+_NATIVE = ("run", "run_concat", "run_with_plan", "run_gather", "quantize_activation", "select_plan", "last_status",
+           "launch_count")
 
 
 def __getattr__(name):

@@ -13,6 +13,7 @@
 #include "../../include/gateup.h"
 #include "gateup_stream.cuh"
 #include "gateup_tile.cuh"
+#include "quantize_act.cuh"
 
 namespace gu {
 namespace {
@@ -564,6 +565,40 @@ int gu_run_gather(const gu_problem* pr, void* const* rank_outputs, int world, in
   const int grid = p.num_tiles < dev->sm_count ? p.num_tiles : dev->sm_count;
   gu::gateup_tile_gather_kernel<<<grid, gu::kTileThreads, gu::kTileSmemBytes, static_cast<cudaStream_t>(stream_v)>>>(
       tm_x, tm_g, tm_u, peers, p);
+  gu::g_launches.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError() == cudaSuccess ? GU_OK : GU_ECUDA;
+}
+
+int gu_quantize_activation(const void* x, int x_is_f32, int64_t ld_x, void* q, float* scale, int64_t m, int64_t k,
+                           void* stream_v) {
+  if (!x || !q || !scale) return GU_EINVAL_NULL;
+  if (m < 1 || k < 128 || (k % 128) != 0 || ld_x < k) return GU_EINVAL_SHAPE;
+  const int64_t elem = x_is_f32 ? 4 : 2;
+  if (!gu::aligned16(x) || !gu::aligned16(q) || (reinterpret_cast<uintptr_t>(scale) & 3u) || (ld_x * elem) % 16 != 0)
+    return GU_EINVAL_ALIGN;
+  gu::DeviceInfo* dev = nullptr;
+  int rc = gu::device_info(&dev);
+  if (rc != GU_OK) return rc;
+  const long long blocks = static_cast<long long>(m) * (k / 128);
+  if (blocks >= (1ll << 31)) return GU_EINVAL_SHAPE;  // the kernel counts 1x128 blocks in 32 bits
+  const long long per_cta = (gu::kQuantThreads / 16) * gu::kQuantUnroll;
+  long long grid = (blocks + per_cta - 1) / per_cta;
+  const long long cap = static_cast<long long>(dev->sm_count) * 8;  // 8 resident CTAs of 256 threads per SM
+  if (grid > cap) grid = cap;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  const int g = static_cast<int>(grid);
+  const uint32_t nblk = static_cast<uint32_t>(blocks), kb = static_cast<uint32_t>(k / 128);
+  uint8_t* qb = static_cast<uint8_t*>(q);
+  const bool pitched = ld_x != k;
+  if (x_is_f32) {
+    const float* xf = static_cast<const float*>(x);
+    if (pitched) gu::quantize_act_kernel<float, true><<<g, gu::kQuantThreads, 0, stream>>>(xf, qb, scale, nblk, ld_x, kb);
+    else gu::quantize_act_kernel<float, false><<<g, gu::kQuantThreads, 0, stream>>>(xf, qb, scale, nblk, ld_x, kb);
+  } else {
+    const __nv_bfloat16* xh = static_cast<const __nv_bfloat16*>(x);
+    if (pitched) gu::quantize_act_kernel<__nv_bfloat16, true><<<g, gu::kQuantThreads, 0, stream>>>(xh, qb, scale, nblk, ld_x, kb);
+    else gu::quantize_act_kernel<__nv_bfloat16, false><<<g, gu::kQuantThreads, 0, stream>>>(xh, qb, scale, nblk, ld_x, kb);
+  }
   gu::g_launches.fetch_add(1, std::memory_order_relaxed);
   return cudaGetLastError() == cudaSuccess ? GU_OK : GU_ECUDA;
 }

@@ -192,6 +192,41 @@ def run_gather(x: torch.Tensor, scale_x: torch.Tensor, gate_shard: torch.Tensor,
         raise _cabi.GateUpError(code, _cabi.error_string(code))
 
 
+@torch.no_grad()
+def quantize_activation(x: torch.Tensor, q: Optional[torch.Tensor] = None,
+                        scale: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """bf16 / fp32 activations [M, K] -> (e4m3 [M, K], fp32 scales [M, K/128]), scale = block amax / 448.
+
+    The producer of `run`'s first two arguments (the reference receives them ready-made:
+    kernel.py:356-357).  One streaming kernel on the current stream; rows of `x` may be pitched.
+    """
+    if x.dim() != 2 or x.dtype not in (torch.bfloat16, torch.float32):
+        raise ValueError("x must be a 2-D bf16 or fp32 tensor")
+    if not x.is_cuda:
+        raise ValueError("x must be a CUDA tensor (this package has no CPU path)")
+    m, k = x.shape
+    if m < 1 or k < BLOCK or k % BLOCK:
+        raise ValueError(f"Unsupported shape M={m}, K={k}: need M >= 1 and K a multiple of {BLOCK}")
+    if x.stride(1) != 1 or x.stride(0) < k:
+        raise ValueError("x must be row-major with unit column stride")
+    if q is None:
+        q = torch.empty(m, k, dtype=torch.float8_e4m3fn, device=x.device)
+    if scale is None:
+        scale = torch.empty(m, k // BLOCK, dtype=torch.float32, device=x.device)
+    for name, t, shape, dtype in (("q", q, (m, k), torch.float8_e4m3fn), ("scale", scale, (m, k // BLOCK), torch.float32)):
+        if tuple(t.shape) != shape or t.dtype != dtype or t.device != x.device or not t.is_contiguous():
+            raise ValueError(f"{name}: expected contiguous shape={shape}, dtype={dtype} on {x.device}")
+    with torch.cuda.device(x.device):
+        stream_ptr = torch.cuda.current_stream(x.device).cuda_stream
+        code = _cabi.lib.gu_quantize_activation(x.data_ptr(), 1 if x.dtype == torch.float32 else 0, x.stride(0),
+                                                q.data_ptr(), scale.data_ptr(), m, k, stream_ptr)
+    if code != _cabi.GU_OK:
+        if code in (_cabi.GU_EINVAL_NULL, _cabi.GU_EINVAL_SHAPE, _cabi.GU_EINVAL_ALIGN):
+            raise ValueError(f"libgateup: {_cabi.error_string(code)} (code {code})")
+        raise _cabi.GateUpError(code, _cabi.error_string(code))
+    return q, scale
+
+
 def last_status(clear: bool = True) -> Tuple[int, int]:
     """(code, detail) of the device-side status word; synchronises the device."""
     detail = ctypes.c_int(0)
