@@ -229,6 +229,7 @@ int launch_tile(const gu_problem* pr, const DeviceInfo& dev, cudaStream_t stream
   p.epoch = 0;
   p.tile_begin = 0;
   p.out_count = 1;
+  p.out_rank = 0;
   p.out_col0 = 0;
   const int total_tiles = p.num_tiles;
   const int sms = dev.sm_count;
@@ -560,6 +561,7 @@ int gu_run_gather(const gu_problem* pr, void* const* rank_outputs, int world, in
   p.partials = nullptr;
   p.epoch = 0;
   p.out_count = world;
+  p.out_rank = rank;
   p.out_col0 = static_cast<int>(int64_t(rank) * n);
 
   const int grid = p.num_tiles < dev->sm_count ? p.num_tiles : dev->sm_count;

@@ -70,6 +70,7 @@ struct TileParams {
   // gather launch only: every output tile is stored into out_count buffers (one per rank of the box) at a
   // column offset, so the all-gather of a column-sharded result happens inside the epilogue
   int out_count;
+  int out_rank;             // this rank's index among the out_count buffers
   int out_col0;
   // stream-K schedule only
   unsigned int* flags;      // [gridDim.x] epoch of the last call that filled slot i
@@ -346,9 +347,16 @@ __device__ __forceinline__ void tile_kernel_body(const CUtensorMap& tm_x, const 
         named_bar_sync(1 + half, 128);
         if (store_leader && !ctx.aborted) {
           if constexpr (kGather) {
-            // plain TMA stores, one per rank's buffer (own and peers' over NVLink); no load touches peer memory
-            for (int r = 0; r < p.out_count; ++r)
-              tma_store_2d(&outs[r], out_half, p.out_col0 + cur_nb * kTileN + half * 64, cur_mb * kTileM);
+            // Plain TMA stores, one per rank's buffer (own and peers' over NVLink); no load touches peer memory.
+            // Destinations are visited in a rotation that differs per source rank and per CTA, so that at any
+            // moment the box's ranks are writing to different peers instead of all to the same one.
+            const int peers = p.out_count - 1;
+            const int col = p.out_col0 + cur_nb * kTileN + half * 64;
+            tma_store_2d(&outs[p.out_rank], out_half, col, cur_mb * kTileM);
+            for (int i = 0; i < peers; ++i) {
+              const int hop = 1 + (i + static_cast<int>(blockIdx.x) + cur_mb) % peers;
+              tma_store_2d(&outs[(p.out_rank + hop) % p.out_count], out_half, col, cur_mb * kTileM);
+            }
           } else {
             tma_store_2d(&outs[0], out_half, cur_nb * kTileN + half * 64, cur_mb * kTileM);
           }
