@@ -127,6 +127,17 @@ int gu_run_gather(const gu_problem* problem, void* const* rank_outputs, int worl
                   void* stream);
 
 /*
+ * Plain block-scaled FP8 GEMM:  c[M, N] (bf16, row pitch ld_c) = sum over K blocks of
+ * scale_a[m, kb] * scale_b[n/128, kb] * (a[m, kb] . b[n, kb]^T), a e4m3 [M, K] with fp32 scales [M, K/128],
+ * b e4m3 [N, K] with fp32 scales [N/128, K/128].  This is the GEMM the reference launches twice per call
+ * (NVIDIA's BlockwiseGemmKernel, loaded at kernel.py:43-72 and launched at kernel.py:487-488; CUTLASS
+ * builder form at variants/cuda_cpp_v4/kernel.cu:185-233), run by the same tile kernel in
+ * single-projection mode.  It serves the MLP's down projection.  One launch on `stream`.
+ */
+int gu_blockwise_gemm(const void* a, const float* scale_a, const void* b, const float* scale_b, void* c, int64_t m,
+                      int64_t k, int64_t n, int64_t ld_c, void* stream);
+
+/*
  * Activation quantiser, the step in front of gu_run: x[M, K] (bf16, or fp32 when x_is_f32 != 0; row pitch ld_x
  * elements) -> q[M, K] e4m3 and scale[M, K/128] fp32 with scale = amax of the 1x128 block / 448, the layout
  * `x` / `scale_x` of gu_problem.  The reference takes its activations already quantised

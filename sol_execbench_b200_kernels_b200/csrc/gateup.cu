@@ -119,6 +119,8 @@ int device_info(DeviceInfo** out) {
             cudaSuccess ||
         cudaFuncSetAttribute(gateup_tile_gather_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
             cudaSuccess ||
+        cudaFuncSetAttribute(blockwise_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
+            cudaSuccess ||
         cudaFuncSetAttribute(gateup_stream_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
             cudaSuccess ||
         cudaFuncSetAttribute(gateup_stream_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
@@ -231,6 +233,7 @@ int launch_tile(const gu_problem* pr, const DeviceInfo& dev, cudaStream_t stream
   p.out_count = 1;
   p.out_rank = 0;
   p.out_col0 = 0;
+  p.n_blocks128 = 0;
   const int total_tiles = p.num_tiles;
   const int sms = dev.sm_count;
   // Hybrid schedule: whole rounds of tiles run data-parallel; the last round plus the remainder (between one and
@@ -560,6 +563,7 @@ int gu_run_gather(const gu_problem* pr, void* const* rank_outputs, int world, in
   p.flags = nullptr;
   p.partials = nullptr;
   p.epoch = 0;
+  p.n_blocks128 = 0;
   p.out_count = world;
   p.out_rank = rank;
   p.out_col0 = static_cast<int>(int64_t(rank) * n);
@@ -601,6 +605,53 @@ int gu_quantize_activation(const void* x, int x_is_f32, int64_t ld_x, void* q, f
     if (pitched) gu::quantize_act_kernel<__nv_bfloat16, true><<<g, gu::kQuantThreads, 0, stream>>>(xh, qb, scale, nblk, ld_x, kb);
     else gu::quantize_act_kernel<__nv_bfloat16, false><<<g, gu::kQuantThreads, 0, stream>>>(xh, qb, scale, nblk, ld_x, kb);
   }
+  gu::g_launches.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError() == cudaSuccess ? GU_OK : GU_ECUDA;
+}
+
+int gu_blockwise_gemm(const void* a, const float* scale_a, const void* b, const float* scale_b, void* c, int64_t m,
+                      int64_t k, int64_t n, int64_t ld_c, void* stream_v) {
+  if (!a || !scale_a || !b || !scale_b || !c) return GU_EINVAL_NULL;
+  if (!gu::shape_ok(m, k, n) || ld_c < n) return GU_EINVAL_SHAPE;
+  if (!gu::aligned16(a) || !gu::aligned16(b) || !gu::aligned16(c) || (reinterpret_cast<uintptr_t>(scale_a) & 3u) ||
+      (reinterpret_cast<uintptr_t>(scale_b) & 3u) || (ld_c % 8) != 0)
+    return GU_EINVAL_ALIGN;
+  gu::DeviceInfo* dev = nullptr;
+  int rc = gu::device_info(&dev);
+  if (rc != GU_OK) return rc;
+
+  CUtensorMap tm_a, tm_b, tm_c;
+  if ((rc = gu::get_map(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a, k, m, k, 128, 128)) != GU_OK) return rc;
+  if ((rc = gu::get_map(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b, k, n, k, 128, 128)) != GU_OK) return rc;
+  if ((rc = gu::get_map(&tm_c, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, c, n, m, ld_c * 2, 64, 128)) != GU_OK) return rc;
+
+  gu::TileParams p;
+  p.scale_x = scale_a;
+  p.scale_gate = scale_b;
+  p.scale_up = scale_b;
+  p.m = static_cast<int>(m);
+  p.kb = static_cast<int>(k / 128);
+  p.n_blocks128 = static_cast<int>(n / 128);
+  p.num_m_blocks = static_cast<int>((m + gu::kTileM - 1) / gu::kTileM);
+  p.num_n_blocks = (p.n_blocks128 + 1) / 2;  // a CTA tile spans two 128-column blocks of B
+  const int64_t tiles = int64_t(p.num_m_blocks) * p.num_n_blocks;
+  if (tiles * (k / 128) >= (1ll << 31)) return GU_EINVAL_SHAPE;
+  p.num_tiles = static_cast<int>(tiles);
+  int64_t gm = (24ll << 20) / (128 * k);
+  if (gm < 1) gm = 1;
+  if (gm > p.num_m_blocks) gm = p.num_m_blocks;
+  p.group_m = static_cast<int>(gm);
+  p.tile_begin = 0;
+  p.flags = nullptr;
+  p.partials = nullptr;
+  p.epoch = 0;
+  p.out_count = 1;
+  p.out_rank = 0;
+  p.out_col0 = 0;
+
+  const int grid = p.num_tiles < dev->sm_count ? p.num_tiles : dev->sm_count;
+  gu::blockwise_gemm_kernel<<<grid, gu::kTileThreads, gu::kTileSmemBytes, static_cast<cudaStream_t>(stream_v)>>>(
+      tm_a, tm_b, tm_c, p);
   gu::g_launches.fetch_add(1, std::memory_order_relaxed);
   return cudaGetLastError() == cudaSuccess ? GU_OK : GU_ECUDA;
 }

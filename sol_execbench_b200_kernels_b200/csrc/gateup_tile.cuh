@@ -27,6 +27,13 @@
 // end of an earlier one, ranges are numbered against blockIdx so a CTA only
 // waits for CTAs dispatched before it, and the wait is bounded.
 //
+// Single-projection mode (kSingle): the same kernel as a plain block-scaled GEMM,
+// C = bf16(sum_kb scale_a * scale_b * (A_kb . B_kb^T)) — the building block the
+// reference launches twice (kernel.py:487-488).  The two 128-row weight tiles of a
+// K block are then two ADJACENT 128-column blocks of one B matrix (scale rows 2n
+// and 2n+1), so a CTA tile is 128 x 256 outputs, and the epilogue is two bf16
+// casts and two stores instead of SwiGLU.  Used for the MLP's down projection.
+//
 // Warp roles (12 warps, 3 warpgroups so register budgets can be moved):
 //   warp 0      TMA producer (one elected lane)
 //   warp 1      TMEM allocation + MMA issue (lane 0)
@@ -72,6 +79,7 @@ struct TileParams {
   int out_count;
   int out_rank;             // this rank's index among the out_count buffers
   int out_col0;
+  int n_blocks128;          // single-projection launch only: N / 128 of the B matrix
   // stream-K schedule only
   unsigned int* flags;      // [gridDim.x] epoch of the last call that filled slot i
   float* partials;          // [gridDim.x][32][256] float4: values 4i..4i+3 of consumer thread t at [i * 256 + t]
@@ -134,7 +142,7 @@ struct PeerMaps {
 };
 
 // The kernel body; `outs` points at the output descriptor(s) in kernel parameter space.
-template <bool kStreamK, bool kGather>
+template <bool kStreamK, bool kGather, bool kSingle = false>
 __device__ __forceinline__ void tile_kernel_body(const CUtensorMap& tm_x, const CUtensorMap& tm_gate,
                                                  const CUtensorMap& tm_up, const CUtensorMap* outs,
                                                  const TileParams& p) {
@@ -209,8 +217,13 @@ __device__ __forceinline__ void tile_kernel_body(const CUtensorMap& tm_x, const 
             const uint32_t dst = ring + stage * kTileStageBytes;
             mbar_arrive_expect_tx(full, kTileStageBytes);
             tma_load_2d(dst, &tm_x, full, j * kBlockK, mb * kTileM);
-            tma_load_2d(dst + kOperandTileBytes, &tm_gate, full, j * kBlockK, nb * kTileN);
-            tma_load_2d(dst + 2 * kOperandTileBytes, &tm_up, full, j * kBlockK, nb * kTileN);
+            if constexpr (kSingle) {  // two adjacent 128-row blocks of the one B matrix (rows past N read as zero)
+              tma_load_2d(dst + kOperandTileBytes, &tm_gate, full, j * kBlockK, 2 * nb * kTileN);
+              tma_load_2d(dst + 2 * kOperandTileBytes, &tm_gate, full, j * kBlockK, (2 * nb + 1) * kTileN);
+            } else {
+              tma_load_2d(dst + kOperandTileBytes, &tm_gate, full, j * kBlockK, nb * kTileN);
+              tma_load_2d(dst + 2 * kOperandTileBytes, &tm_up, full, j * kBlockK, nb * kTileN);
+            }
           }
           if (++stage == kTileStages) { stage = 0; phase ^= 1u; }
         }
@@ -270,8 +283,13 @@ __device__ __forceinline__ void tile_kernel_body(const CUtensorMap& tm_x, const 
         tile_coords(p, t, mb, nb);
         const int m_global = min(mb * kTileM + row, p.m - 1);
         sx_row = p.scale_x + static_cast<size_t>(m_global) * p.kb;
-        sg_row = p.scale_gate + static_cast<size_t>(nb) * p.kb;
-        su_row = p.scale_up + static_cast<size_t>(nb) * p.kb;
+        if constexpr (kSingle) {
+          sg_row = p.scale_gate + static_cast<size_t>(2 * nb) * p.kb;
+          su_row = p.scale_gate + static_cast<size_t>(min(2 * nb + 1, p.n_blocks128 - 1)) * p.kb;
+        } else {
+          sg_row = p.scale_gate + static_cast<size_t>(nb) * p.kb;
+          su_row = p.scale_up + static_cast<size_t>(nb) * p.kb;
+        }
         sx0 = __ldg(sx_row); sg0 = __ldg(sg_row); su0 = __ldg(su_row);
         if (p.kb > 1) { sx1 = __ldg(sx_row + 1); sg1 = __ldg(sg_row + 1); su1 = __ldg(su_row + 1); }
       };
@@ -328,39 +346,65 @@ __device__ __forceinline__ void tile_kernel_body(const CUtensorMap& tm_x, const 
         const int next = tile + gridDim.x;
         if (next < p.num_tiles) start_tile(next);
 
-        // -------- epilogue: SwiGLU in registers, swizzled staging tile, TMA store --------
-        if (store_leader) tma_store_wait_read0();  // previous tile's store has finished reading the staging tile
-        named_bar_sync(1 + half, 128);
-        {
-          uint8_t* out_row = smem_gen + (out_half - smem_base) + row * 128;
+        if constexpr (kSingle) {
+          // -------- epilogue of the plain GEMM: two 128-column blocks, each cast to bf16 and stored --------
 #pragma unroll
-          for (int c = 0; c < 8; ++c) {  // 8 chunks of 8 bf16 = 16 bytes
-            uint4 q;
-            q.x = swiglu_bf16x2(g[4 * c + 0], u[4 * c + 0]);
-            q.y = swiglu_bf16x2(g[4 * c + 1], u[4 * c + 1]);
-            q.z = swiglu_bf16x2(g[4 * c + 2], u[4 * c + 2]);
-            q.w = swiglu_bf16x2(g[4 * c + 3], u[4 * c + 3]);
-            *reinterpret_cast<uint4*>(out_row + ((c ^ (row & 7)) << 4)) = q;
-          }
-        }
-        fence_proxy_async_smem();
-        named_bar_sync(1 + half, 128);
-        if (store_leader && !ctx.aborted) {
-          if constexpr (kGather) {
-            // Plain TMA stores, one per rank's buffer (own and peers' over NVLink); no load touches peer memory.
-            // Destinations are visited in a rotation that differs per source rank and per CTA, so that at any
-            // moment the box's ranks are writing to different peers instead of all to the same one.
-            const int peers = p.out_count - 1;
-            const int col = p.out_col0 + cur_nb * kTileN + half * 64;
-            tma_store_2d(&outs[p.out_rank], out_half, col, cur_mb * kTileM);
-            for (int i = 0; i < peers; ++i) {
-              const int hop = 1 + (i + static_cast<int>(blockIdx.x) + cur_mb) % peers;
-              tma_store_2d(&outs[(p.out_rank + hop) % p.out_count], out_half, col, cur_mb * kTileM);
+          for (int part = 0; part < 2; ++part) {
+            if (store_leader) tma_store_wait_read0();  // the previous store has finished reading the staging tile
+            named_bar_sync(1 + half, 128);
+            uint8_t* out_row = smem_gen + (out_half - smem_base) + row * 128;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+              const float2* src = part == 0 ? g : u;
+              uint4 q;
+              q.x = pack_bf16x2(src[4 * c + 0].x, src[4 * c + 0].y);
+              q.y = pack_bf16x2(src[4 * c + 1].x, src[4 * c + 1].y);
+              q.z = pack_bf16x2(src[4 * c + 2].x, src[4 * c + 2].y);
+              q.w = pack_bf16x2(src[4 * c + 3].x, src[4 * c + 3].y);
+              *reinterpret_cast<uint4*>(out_row + ((c ^ (row & 7)) << 4)) = q;
             }
-          } else {
-            tma_store_2d(&outs[0], out_half, cur_nb * kTileN + half * 64, cur_mb * kTileM);
+            fence_proxy_async_smem();
+            named_bar_sync(1 + half, 128);
+            if (store_leader && !ctx.aborted && 2 * cur_nb + part < p.n_blocks128) {
+              tma_store_2d(&outs[0], out_half, (2 * cur_nb + part) * kTileN + half * 64, cur_mb * kTileM);
+              tma_store_commit();
+            }
           }
-          tma_store_commit();
+        } else {
+          // -------- epilogue: SwiGLU in registers, swizzled staging tile, TMA store --------
+          if (store_leader) tma_store_wait_read0();  // previous tile's store has finished reading the staging tile
+          named_bar_sync(1 + half, 128);
+          {
+            uint8_t* out_row = smem_gen + (out_half - smem_base) + row * 128;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {  // 8 chunks of 8 bf16 = 16 bytes
+              uint4 q;
+              q.x = swiglu_bf16x2(g[4 * c + 0], u[4 * c + 0]);
+              q.y = swiglu_bf16x2(g[4 * c + 1], u[4 * c + 1]);
+              q.z = swiglu_bf16x2(g[4 * c + 2], u[4 * c + 2]);
+              q.w = swiglu_bf16x2(g[4 * c + 3], u[4 * c + 3]);
+              *reinterpret_cast<uint4*>(out_row + ((c ^ (row & 7)) << 4)) = q;
+            }
+          }
+          fence_proxy_async_smem();
+          named_bar_sync(1 + half, 128);
+          if (store_leader && !ctx.aborted) {
+            if constexpr (kGather) {
+              // Plain TMA stores, one per rank's buffer (own and peers' over NVLink); no load touches peer memory.
+              // Destinations are visited in a rotation that differs per source rank and per CTA, so that at any
+              // moment the box's ranks are writing to different peers instead of all to the same one.
+              const int peers = p.out_count - 1;
+              const int col = p.out_col0 + cur_nb * kTileN + half * 64;
+              tma_store_2d(&outs[p.out_rank], out_half, col, cur_mb * kTileM);
+              for (int i = 0; i < peers; ++i) {
+                const int hop = 1 + (i + static_cast<int>(blockIdx.x) + cur_mb) % peers;
+                tma_store_2d(&outs[(p.out_rank + hop) % p.out_count], out_half, col, cur_mb * kTileM);
+              }
+            } else {
+              tma_store_2d(&outs[0], out_half, cur_nb * kTileN + half * 64, cur_mb * kTileM);
+            }
+            tma_store_commit();
+          }
         }
         tile = next;
       }
@@ -514,6 +558,13 @@ gateup_tile_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
                    const __grid_constant__ CUtensorMap tm_up, const __grid_constant__ CUtensorMap tm_out,
                    const TileParams p) {
   tile_kernel_body<kStreamK, false>(tm_x, tm_gate, tm_up, &tm_out, p);
+}
+
+// Plain block-scaled GEMM (single-projection mode), data-parallel schedule.
+__global__ void __launch_bounds__(kTileThreads, 1)
+blockwise_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                      const __grid_constant__ CUtensorMap tm_c, const TileParams p) {
+  tile_kernel_body<false, false, true>(tm_a, tm_b, tm_b, &tm_c, p);
 }
 
 // Data-parallel schedule with the column all-gather fused into the epilogue (see TileParams::out_count).

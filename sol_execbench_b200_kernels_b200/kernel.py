@@ -193,6 +193,38 @@ def run_gather(x: torch.Tensor, scale_x: torch.Tensor, gate_shard: torch.Tensor,
 
 
 @torch.no_grad()
+def blockwise_gemm(a: torch.Tensor, scale_a: torch.Tensor, b: torch.Tensor, scale_b: torch.Tensor,
+                   output: torch.Tensor) -> None:
+    """output[M, N] (bf16) = block-scaled a[M, K] @ b[N, K]^T with 1x128 scales on a and 128x128 scales on b.
+
+    The single GEMM the reference launches twice per call (kernel.py:487-488), here as one launch of the tile
+    kernel in single-projection mode; used for the MLP's down projection.  Destination passing, current stream.
+    """
+    if a.dim() != 2 or b.dim() != 2 or output.dim() != 2:
+        raise ValueError("a, b and output must be 2-D")
+    m, k = a.shape
+    n = b.shape[0]
+    if m < 1 or k % BLOCK or n % BLOCK or k < BLOCK or n < BLOCK:
+        raise ValueError(f"Unsupported contract shape M={m}, K={k}, N={n}: need M >= 1 and K, N multiples of {BLOCK}")
+    expected = {
+        "a": (a, (m, k), torch.float8_e4m3fn), "scale_a": (scale_a, (m, k // BLOCK), torch.float32),
+        "b": (b, (n, k), torch.float8_e4m3fn), "scale_b": (scale_b, (n // BLOCK, k // BLOCK), torch.float32),
+        "output": (output, (m, n), torch.bfloat16),
+    }
+    _check(expected, a.device)
+    if output.stride(1) != 1 or output.stride(0) < n:
+        raise ValueError("output must be row-major with unit column stride")
+    with torch.cuda.device(a.device):
+        stream_ptr = torch.cuda.current_stream(a.device).cuda_stream
+        code = _cabi.lib.gu_blockwise_gemm(a.data_ptr(), scale_a.data_ptr(), b.data_ptr(), scale_b.data_ptr(),
+                                           output.data_ptr(), m, k, n, output.stride(0), stream_ptr)
+    if code != _cabi.GU_OK:
+        if code in (_cabi.GU_EINVAL_NULL, _cabi.GU_EINVAL_SHAPE, _cabi.GU_EINVAL_ALIGN):
+            raise ValueError(f"libgateup: {_cabi.error_string(code)} (code {code})")
+        raise _cabi.GateUpError(code, _cabi.error_string(code))
+
+
+@torch.no_grad()
 def quantize_activation(x: torch.Tensor, q: Optional[torch.Tensor] = None,
                         scale: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """bf16 / fp32 activations [M, K] -> (e4m3 [M, K], fp32 scales [M, K/128]), scale = block amax / 448.

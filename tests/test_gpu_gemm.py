@@ -1,0 +1,51 @@
+"""The tile kernel in single-projection mode (plain block-scaled FP8 GEMM, bf16 out) against the oracle."""
+import pytest
+import torch
+
+from oracle import gateup_oracle as O
+from sol_execbench_b200_kernels_b200 import workloads as W
+
+pytestmark = pytest.mark.gpu
+
+
+def _operands(m, k, n, seed):
+    gen = torch.Generator().manual_seed(seed)
+    a, sa = W.quantize_activation_1x128(torch.randn(m, k, generator=gen))
+    b, sb = W.quantize_weight_128x128(torch.randn(n, k, generator=gen) * 0.02)
+    return a, sa, b, sb
+
+
+@pytest.mark.parametrize("shape", [(128, 128, 128), (128, 256, 256), (100, 384, 384), (300, 512, 640), (257, 1024, 128),
+                                   (512, 14336 // 4, 1024), (64, 2048, 4096)])
+def test_blockwise_gemm_parity(shape):
+    import sol_execbench_b200_kernels_b200 as pkg
+
+    m, k, n = shape
+    a, sa, b, sb = _operands(m, k, n, seed=40 + m)
+    out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda:0")
+    pkg.blockwise_gemm(a.cuda(), sa.cuda(), b.cuda(), sb.cuda(), out)
+    torch.cuda.synchronize()
+    assert pkg.last_status()[0] == 0
+    for ref in (O.gemm_blockwise(a, sa, b, sb), O.gemm_dequant(a, sa, b, sb)):
+        st = O.error_stats(out, ref)
+        assert st["finite"] and not st["all_zero"], st
+        assert st["rel_l2"] <= 1e-2, st
+        # one bf16 ulp of the result is the worst a correct sum in another order can be off by
+        assert st["max_abs"] <= max(2e-2, 2 ** -7 * float(ref.float().abs().max())), st
+    assert torch.equal(out.cpu(), O.gemm_blockwise(a, sa, b, sb)) or O.error_stats(out, O.gemm_blockwise(a, sa, b, sb))["rel_l2"] < 1e-4
+
+
+def test_blockwise_gemm_pitched_output_and_errors():
+    import sol_execbench_b200_kernels_b200 as pkg
+
+    m, k, n = 130, 256, 384
+    a, sa, b, sb = _operands(m, k, n, seed=41)
+    wide = torch.full((m, n + 128), 5.0, dtype=torch.bfloat16, device="cuda:0")
+    pkg.blockwise_gemm(a.cuda(), sa.cuda(), b.cuda(), sb.cuda(), wide[:, :n])
+    torch.cuda.synchronize()
+    assert (wide[:, n:] == 5.0).all()
+    assert O.error_stats(wide[:, :n], O.gemm_blockwise(a, sa, b, sb))["rel_l2"] <= 1e-3
+    with pytest.raises(ValueError, match="scale_b"):
+        pkg.blockwise_gemm(a.cuda(), sa.cuda(), b.cuda(), sb.cuda()[:, :1], wide[:, :n])
+    with pytest.raises(ValueError, match="CUDA"):
+        pkg.blockwise_gemm(a, sa, b, sb, torch.empty(m, n, dtype=torch.bfloat16))
