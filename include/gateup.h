@@ -127,6 +127,15 @@ int gu_run_gather(const gu_problem* problem, void* const* rank_outputs, int worl
                   void* stream);
 
 /*
+ * gu_run with the result re-quantised in the epilogue: out_q[M, N] e4m3 (contiguous) and out_scale[M, N/128]
+ * fp32, scale = amax over the token's 128 columns / 448 — the operand format of the next block-scaled GEMM
+ * (gu_blockwise_gemm as the down projection), so the bf16 intermediate never reaches HBM.  Bits equal
+ * quantising gu_run's bf16 result with gu_quantize_activation.  `output`, `workspace` and `plan` of the
+ * problem are ignored.  No counterpart in the reference, whose path ends at the bf16 result.
+ */
+int gu_run_fp8out(const gu_problem* problem, void* out_q, float* out_scale, void* stream);
+
+/*
  * Plain block-scaled FP8 GEMM:  c[M, N] (bf16, row pitch ld_c) = sum over K blocks of
  * scale_a[m, kb] * scale_b[n/128, kb] * (a[m, kb] . b[n, kb]^T), a e4m3 [M, K] with fp32 scales [M, K/128],
  * b e4m3 [N, K] with fp32 scales [N/128, K/128].  This is the GEMM the reference launches twice per call

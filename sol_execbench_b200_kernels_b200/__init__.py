@@ -13,7 +13,7 @@ from . import workloads  # noqa: F401  (pure torch, no native code)
 from .sharded import (GatherBuffers, assemble_gathered, gather_columns, run_sharded,  # noqa: F401
                       run_sharded_fused, shard_bounds, shard_concat_weights, shard_weights)
 
-_NATIVE = ("run", "run_concat", "run_with_plan", "run_gather", "quantize_activation", "blockwise_gemm", "select_plan", "last_status",
+_NATIVE = ("run", "run_concat", "run_with_plan", "run_gather", "quantize_activation", "blockwise_gemm", "run_fp8_output", "mlp_block", "select_plan", "last_status",
            "launch_count")
 
 

@@ -121,6 +121,8 @@ int device_info(DeviceInfo** out) {
             cudaSuccess ||
         cudaFuncSetAttribute(blockwise_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
             cudaSuccess ||
+        cudaFuncSetAttribute(gateup_tile_fp8out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
+            cudaSuccess ||
         cudaFuncSetAttribute(gateup_stream_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
             cudaSuccess ||
         cudaFuncSetAttribute(gateup_stream_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
@@ -234,6 +236,7 @@ int launch_tile(const gu_problem* pr, const DeviceInfo& dev, cudaStream_t stream
   p.out_rank = 0;
   p.out_col0 = 0;
   p.n_blocks128 = 0;
+  p.scale_out = nullptr;
   const int total_tiles = p.num_tiles;
   const int sms = dev.sm_count;
   // Hybrid schedule: whole rounds of tiles run data-parallel; the last round plus the remainder (between one and
@@ -564,6 +567,7 @@ int gu_run_gather(const gu_problem* pr, void* const* rank_outputs, int world, in
   p.partials = nullptr;
   p.epoch = 0;
   p.n_blocks128 = 0;
+  p.scale_out = nullptr;
   p.out_count = world;
   p.out_rank = rank;
   p.out_col0 = static_cast<int>(int64_t(rank) * n);
@@ -609,6 +613,56 @@ int gu_quantize_activation(const void* x, int x_is_f32, int64_t ld_x, void* q, f
   return cudaGetLastError() == cudaSuccess ? GU_OK : GU_ECUDA;
 }
 
+int gu_run_fp8out(const gu_problem* pr, void* out_q, float* out_scale, void* stream_v) {
+  if (!pr || !out_q || !out_scale) return GU_EINVAL_NULL;
+  if (!pr->x || !pr->scale_x || !pr->gate_w || !pr->scale_gate || !pr->up_w || !pr->scale_up) return GU_EINVAL_NULL;
+  if (!gu::shape_ok(pr->m, pr->k, pr->n)) return GU_EINVAL_SHAPE;
+  if (!gu::aligned16(pr->x) || !gu::aligned16(pr->gate_w) || !gu::aligned16(pr->up_w) || !gu::aligned16(out_q) ||
+      (reinterpret_cast<uintptr_t>(pr->scale_x) & 3u) || (reinterpret_cast<uintptr_t>(pr->scale_gate) & 3u) ||
+      (reinterpret_cast<uintptr_t>(pr->scale_up) & 3u) || (reinterpret_cast<uintptr_t>(out_scale) & 3u))
+    return GU_EINVAL_ALIGN;
+  gu::DeviceInfo* dev = nullptr;
+  int rc = gu::device_info(&dev);
+  if (rc != GU_OK) return rc;
+  const int64_t m = pr->m, k = pr->k, n = pr->n;
+  CUtensorMap tm_x, tm_g, tm_u, tm_q;
+  if ((rc = gu::get_map(&tm_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, pr->x, k, m, k, 128, 128)) != GU_OK) return rc;
+  if ((rc = gu::get_map(&tm_g, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, pr->gate_w, k, n, k, 128, 128)) != GU_OK) return rc;
+  if ((rc = gu::get_map(&tm_u, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, pr->up_w, k, n, k, 128, 128)) != GU_OK) return rc;
+  if ((rc = gu::get_map(&tm_q, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, out_q, n, m, n, 128, 128)) != GU_OK) return rc;
+
+  gu::TileParams p;
+  p.scale_x = pr->scale_x;
+  p.scale_gate = pr->scale_gate;
+  p.scale_up = pr->scale_up;
+  p.m = static_cast<int>(m);
+  p.kb = static_cast<int>(k / 128);
+  p.num_m_blocks = static_cast<int>((m + gu::kTileM - 1) / gu::kTileM);
+  p.num_n_blocks = static_cast<int>(n / gu::kTileN);
+  const int64_t tiles = int64_t(p.num_m_blocks) * p.num_n_blocks;
+  if (tiles * (k / 128) >= (1ll << 31)) return GU_EINVAL_SHAPE;
+  p.num_tiles = static_cast<int>(tiles);
+  int64_t gm = (24ll << 20) / (128 * k);
+  if (gm < 1) gm = 1;
+  if (gm > p.num_m_blocks) gm = p.num_m_blocks;
+  p.group_m = static_cast<int>(gm);
+  p.tile_begin = 0;
+  p.flags = nullptr;
+  p.partials = nullptr;
+  p.epoch = 0;
+  p.out_count = 1;
+  p.out_rank = 0;
+  p.out_col0 = 0;
+  p.n_blocks128 = static_cast<int>(n / 128);
+  p.scale_out = out_scale;
+
+  const int grid = p.num_tiles < dev->sm_count ? p.num_tiles : dev->sm_count;
+  gu::gateup_tile_fp8out_kernel<<<grid, gu::kTileThreads, gu::kTileSmemBytes, static_cast<cudaStream_t>(stream_v)>>>(
+      tm_x, tm_g, tm_u, tm_q, p);
+  gu::g_launches.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError() == cudaSuccess ? GU_OK : GU_ECUDA;
+}
+
 int gu_blockwise_gemm(const void* a, const float* scale_a, const void* b, const float* scale_b, void* c, int64_t m,
                       int64_t k, int64_t n, int64_t ld_c, void* stream_v) {
   if (!a || !scale_a || !b || !scale_b || !c) return GU_EINVAL_NULL;
@@ -632,6 +686,7 @@ int gu_blockwise_gemm(const void* a, const float* scale_a, const void* b, const 
   p.m = static_cast<int>(m);
   p.kb = static_cast<int>(k / 128);
   p.n_blocks128 = static_cast<int>(n / 128);
+  p.scale_out = nullptr;
   p.num_m_blocks = static_cast<int>((m + gu::kTileM - 1) / gu::kTileM);
   p.num_n_blocks = (p.n_blocks128 + 1) / 2;  // a CTA tile spans two 128-column blocks of B
   const int64_t tiles = int64_t(p.num_m_blocks) * p.num_n_blocks;

@@ -34,6 +34,12 @@
 // and 2n+1), so a CTA tile is 128 x 256 outputs, and the epilogue is two bf16
 // casts and two stores instead of SwiGLU.  Used for the MLP's down projection.
 //
+// FP8-output mode (kFp8Out): the SwiGLU result is re-quantised in the epilogue to e4m3 with one fp32 scale
+// per token and 128 columns (amax / 448) — the tile is exactly one scale block wide, so the row maximum is
+// the larger of two threads' maxima, exchanged through shared memory — and stored as e4m3 [M, N] plus
+// scales [M, N/128]: the operand format of the next block-scaled GEMM (the down projection), so the bf16
+// intermediate never reaches HBM either.  The bits equal quantising the bf16 result with the torch quantiser.
+//
 // Warp roles (12 warps, 3 warpgroups so register budgets can be moved):
 //   warp 0      TMA producer (one elected lane)
 //   warp 1      TMEM allocation + MMA issue (lane 0)
@@ -42,6 +48,8 @@
 //               32*(w%4)..+31; warps 4-7 own output columns 0-63 of the tile,
 //               warps 8-11 columns 64-127 (gate and up of the same columns).
 #pragma once
+
+#include <cuda_fp8.h>
 
 #include "ptx_sm100.cuh"
 
@@ -79,7 +87,8 @@ struct TileParams {
   int out_count;
   int out_rank;             // this rank's index among the out_count buffers
   int out_col0;
-  int n_blocks128;          // single-projection launch only: N / 128 of the B matrix
+  int n_blocks128;          // single-projection and fp8-output launches: N / 128
+  float* scale_out;         // fp8-output launch only: [M, N/128] scales of the re-quantised result
   // stream-K schedule only
   unsigned int* flags;      // [gridDim.x] epoch of the last call that filled slot i
   float* partials;          // [gridDim.x][32][256] float4: values 4i..4i+3 of consumer thread t at [i * 256 + t]
@@ -142,7 +151,7 @@ struct PeerMaps {
 };
 
 // The kernel body; `outs` points at the output descriptor(s) in kernel parameter space.
-template <bool kStreamK, bool kGather, bool kSingle = false>
+template <bool kStreamK, bool kGather, bool kSingle = false, bool kFp8Out = false>
 __device__ __forceinline__ void tile_kernel_body(const CUtensorMap& tm_x, const CUtensorMap& tm_gate,
                                                  const CUtensorMap& tm_up, const CUtensorMap* outs,
                                                  const TileParams& p) {
@@ -346,7 +355,53 @@ __device__ __forceinline__ void tile_kernel_body(const CUtensorMap& tm_x, const 
         const int next = tile + gridDim.x;
         if (next < p.num_tiles) start_tile(next);
 
-        if constexpr (kSingle) {
+        if constexpr (kFp8Out) {
+          // -------- epilogue with re-quantisation: SwiGLU, row amax over the tile's 128 columns, e4m3 + scale --------
+          uint32_t o2[32];  // this thread's 64 bf16 outputs, packed in pairs
+          float amax = 0.f;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            o2[i] = swiglu_bf16x2(g[i], u[i]);
+            amax = fmaxf(amax, fmaxf(fabsf(__uint_as_float(o2[i] << 16)), fabsf(__uint_as_float(o2[i] & 0xffff0000u))));
+          }
+          if (store_leader) tma_store_wait_read0();  // the previous store has finished reading the staging tile
+          float* row_max = reinterpret_cast<float*>(smem_gen + (out_stage - smem_base) + kTileOutHalfBytes);  // [2][128]
+          row_max[half * 128 + row] = amax;
+          named_bar_sync(3, 256);
+          amax = fmaxf(amax, row_max[(half ^ 1) * 128 + row]);
+          const float sc = fmaxf(amax, 1e-12f) / 448.0f;
+          const float rc = __frcp_rn(sc);
+          // 64 e4m3 of this half at bytes [64*half, 64*half+64) of the row's 128 bytes (128-byte swizzle)
+          uint8_t* out_row = smem_gen + (out_stage - smem_base) + row * 128;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {  // 4 chunks of 16 e4m3
+            uint32_t w[4];
+#pragma unroll
+            for (int k4 = 0; k4 < 4; ++k4) {
+              uint32_t word = 0;
+#pragma unroll
+              for (int e = 0; e < 2; ++e) {
+                const uint32_t pr = o2[8 * c + 2 * k4 + e];
+                const float a = __uint_as_float(pr << 16), b = __uint_as_float(pr & 0xffff0000u);
+                const float qa0 = a * rc, qb0 = b * rc;  // correctly rounded a / sc, b / sc (exact-residual step)
+                const float qa = fmaf(fmaf(-qa0, sc, a), rc, qa0), qb = fmaf(fmaf(-qb0, sc, b), rc, qb0);
+                word |= static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(make_float2(qa, qb), __NV_SATFINITE, __NV_E4M3))
+                        << (16 * e);
+              }
+              w[k4] = word;
+            }
+            const int chunk = half * 4 + c;
+            *reinterpret_cast<uint4*>(out_row + ((chunk ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+          if (half == 0 && cur_mb * kTileM + row < p.m)
+            p.scale_out[static_cast<size_t>(cur_mb * kTileM + row) * p.n_blocks128 + cur_nb] = sc;
+          fence_proxy_async_smem();
+          named_bar_sync(3, 256);
+          if (threadIdx.x == 128 && !ctx.aborted) {
+            tma_store_2d(&outs[0], out_stage, cur_nb * kTileN, cur_mb * kTileM);
+            tma_store_commit();
+          }
+        } else if constexpr (kSingle) {
           // -------- epilogue of the plain GEMM: two 128-column blocks, each cast to bf16 and stored --------
 #pragma unroll
           for (int part = 0; part < 2; ++part) {
@@ -558,6 +613,15 @@ gateup_tile_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
                    const __grid_constant__ CUtensorMap tm_up, const __grid_constant__ CUtensorMap tm_out,
                    const TileParams p) {
   tile_kernel_body<kStreamK, false>(tm_x, tm_gate, tm_up, &tm_out, p);
+}
+
+// Gate/up + SwiGLU with the result re-quantised to e4m3 + 1x128 scales in the epilogue; `tm_outq` describes
+// the e4m3 [M, N] destination with 128-byte x 128-row boxes.
+__global__ void __launch_bounds__(kTileThreads, 1)
+gateup_tile_fp8out_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_gate,
+                          const __grid_constant__ CUtensorMap tm_up, const __grid_constant__ CUtensorMap tm_outq,
+                          const TileParams p) {
+  tile_kernel_body<false, false, false, true>(tm_x, tm_gate, tm_up, &tm_outq, p);
 }
 
 // Plain block-scaled GEMM (single-projection mode), data-parallel schedule.

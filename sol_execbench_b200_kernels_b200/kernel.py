@@ -193,6 +193,52 @@ def run_gather(x: torch.Tensor, scale_x: torch.Tensor, gate_shard: torch.Tensor,
 
 
 @torch.no_grad()
+def run_fp8_output(x: torch.Tensor, scale_x: torch.Tensor, gate_proj_weight: torch.Tensor, scale_gate: torch.Tensor,
+                   up_proj_weight: torch.Tensor, scale_up: torch.Tensor, out_q: torch.Tensor,
+                   out_scale: torch.Tensor) -> None:
+    """`run` with the result re-quantised in the kernel epilogue: e4m3 [M, N] + fp32 scales [M, N/128].
+
+    Feeds `blockwise_gemm` (the down projection) without a bf16 round trip through HBM; the bits equal
+    `quantize_activation(run(...))`.
+    """
+    m, k, n = _validate_inputs_only(x, scale_x, gate_proj_weight, scale_gate, up_proj_weight, scale_up)
+    _check({"out_q": (out_q, (m, n), torch.float8_e4m3fn), "out_scale": (out_scale, (m, n // BLOCK), torch.float32)},
+           x.device)
+    with torch.cuda.device(x.device):
+        stream_ptr = torch.cuda.current_stream(x.device).cuda_stream
+        pr = GuProblem(
+            x.data_ptr(), scale_x.data_ptr(), gate_proj_weight.data_ptr(), scale_gate.data_ptr(),
+            up_proj_weight.data_ptr(), scale_up.data_ptr(), None, m, k, n, n, None, 0, PLAN_TILE, 0)
+        code = _cabi.lib.gu_run_fp8out(ctypes.byref(pr), out_q.data_ptr(), out_scale.data_ptr(), stream_ptr)
+    if code != _cabi.GU_OK:
+        if code in (_cabi.GU_EINVAL_NULL, _cabi.GU_EINVAL_SHAPE, _cabi.GU_EINVAL_ALIGN):
+            raise ValueError(f"libgateup: {_cabi.error_string(code)} (code {code})")
+        raise _cabi.GateUpError(code, _cabi.error_string(code))
+
+
+@torch.no_grad()
+def mlp_block(x: torch.Tensor, gate_proj_weight: torch.Tensor, scale_gate: torch.Tensor, up_proj_weight: torch.Tensor,
+              scale_up: torch.Tensor, down_proj_weight: torch.Tensor, scale_down: torch.Tensor,
+              output: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """bf16 / fp32 activations [M, H] -> bf16 [M, H_out]: quantise, gate/up + SwiGLU (e4m3 out), down projection.
+
+    Three launches: `quantize_activation`, `run_fp8_output`, `blockwise_gemm`.  `down_proj_weight` is e4m3
+    [H_out, N] with scales [H_out/128, N/128].  The intermediate [M, N] exists only as e4m3 + scales.
+    """
+    m = x.shape[0]
+    n = gate_proj_weight.shape[0]
+    h_out = down_proj_weight.shape[0]
+    xq, sx = quantize_activation(x)
+    mid_q = torch.empty(m, n, dtype=torch.float8_e4m3fn, device=x.device)
+    mid_s = torch.empty(m, n // BLOCK, dtype=torch.float32, device=x.device)
+    run_fp8_output(xq, sx, gate_proj_weight, scale_gate, up_proj_weight, scale_up, mid_q, mid_s)
+    if output is None:
+        output = torch.empty(m, h_out, dtype=torch.bfloat16, device=x.device)
+    blockwise_gemm(mid_q, mid_s, down_proj_weight, scale_down, output)
+    return output
+
+
+@torch.no_grad()
 def blockwise_gemm(a: torch.Tensor, scale_a: torch.Tensor, b: torch.Tensor, scale_b: torch.Tensor,
                    output: torch.Tensor) -> None:
     """output[M, N] (bf16) = block-scaled a[M, K] @ b[N, K]^T with 1x128 scales on a and 128x128 scales on b.

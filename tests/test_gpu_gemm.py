@@ -49,3 +49,43 @@ def test_blockwise_gemm_pitched_output_and_errors():
         pkg.blockwise_gemm(a.cuda(), sa.cuda(), b.cuda(), sb.cuda()[:, :1], wide[:, :n])
     with pytest.raises(ValueError, match="CUDA"):
         pkg.blockwise_gemm(a, sa, b, sb, torch.empty(m, n, dtype=torch.bfloat16))
+
+
+@pytest.mark.parametrize("shape", [(128, 256, 128), (300, 512, 384), (1000, 1024, 640)])
+def test_fp8_output_epilogue_equals_quantising_the_bf16_result(shape):
+    """Fused re-quantisation: e4m3 bytes and scales identical to quantising `run`'s bf16 output afterwards."""
+    import sol_execbench_b200_kernels_b200 as pkg
+
+    m, k, n = shape
+    inp = W.make_inputs(m, k, n, seed=50 + m).to("cuda:0")
+    ref = torch.empty(m, n, dtype=torch.bfloat16, device="cuda:0")
+    pkg.run_with_plan(*inp.args(), ref, "tile_dp")
+    q = torch.zeros(m, n, dtype=torch.uint8, device="cuda:0").view(torch.float8_e4m3fn)
+    s = torch.zeros(m, n // 128, dtype=torch.float32, device="cuda:0")
+    pkg.run_fp8_output(*inp.args(), q, s)
+    torch.cuda.synchronize()
+    assert pkg.last_status()[0] == 0
+    q_ref, s_ref = W.quantize_activation_1x128(ref.cpu().float())
+    assert torch.equal(s.cpu(), s_ref)
+    assert torch.equal(q.cpu().view(torch.uint8), q_ref.view(torch.uint8))
+
+
+def test_mlp_block_against_oracle_chain():
+    import sol_execbench_b200_kernels_b200 as pkg
+
+    m, h, n = 200, 512, 1024
+    gen = torch.Generator().manual_seed(60)
+    x = torch.randn(m, h, generator=gen).to(torch.bfloat16)
+    gq, sg = W.quantize_weight_128x128(torch.randn(n, h, generator=gen) * 0.02)
+    uq, su = W.quantize_weight_128x128(torch.randn(n, h, generator=gen) * 0.02)
+    dq, sd = W.quantize_weight_128x128(torch.randn(h, n, generator=gen) * 0.02)
+    out = pkg.mlp_block(x.cuda(), gq.cuda(), sg.cuda(), uq.cuda(), su.cuda(), dq.cuda(), sd.cuda())
+    torch.cuda.synchronize()
+    assert pkg.last_status()[0] == 0
+    # the same chain on the CPU: quantise, gate/up + SwiGLU (bf16), quantise, down projection
+    xq, sx = W.quantize_activation_1x128(x.float())
+    mid = O.gateup_blockwise(xq, sx, gq, sg, uq, su)
+    mq, ms = W.quantize_activation_1x128(mid.float())
+    ref = O.gemm_blockwise(mq, ms, dq, sd)
+    st = O.error_stats(out, ref)
+    assert st["finite"] and not st["all_zero"] and st["rel_l2"] <= 1e-2 and st["max_abs"] <= 2e-2, st
