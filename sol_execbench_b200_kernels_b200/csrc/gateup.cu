@@ -591,7 +591,7 @@ int gu_quantize_activation(const void* x, int x_is_f32, int64_t ld_x, void* q, f
   if (rc != GU_OK) return rc;
   const long long blocks = static_cast<long long>(m) * (k / 128);
   if (blocks >= (1ll << 31)) return GU_EINVAL_SHAPE;  // the kernel counts 1x128 blocks in 32 bits
-  const long long per_cta = (gu::kQuantThreads / 16) * gu::kQuantUnroll;
+  const long long per_cta = (gu::kQuantThreads / 16) * (x_is_f32 ? gu::quant_unroll<float>() : gu::quant_unroll<__nv_bfloat16>());
   long long grid = (blocks + per_cta - 1) / per_cta;
   const long long cap = static_cast<long long>(dev->sm_count) * 8;  // 8 resident CTAs of 256 threads per SM
   if (grid > cap) grid = cap;

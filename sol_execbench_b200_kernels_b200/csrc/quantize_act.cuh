@@ -21,35 +21,52 @@
 namespace gu {
 
 constexpr int kQuantThreads = 256;
-constexpr int kQuantUnroll = 4;  // blocks-pairs in flight per warp
 
-// Eight consecutive elements as fp32, and the largest magnitude among them.
-__device__ __forceinline__ float load8(const __nv_bfloat16* p, float (&v)[8]) {
-  const uint4 raw = __ldcs(reinterpret_cast<const uint4*>(p));  // streamed once: evict-first
-  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-  __nv_bfloat162 m2 = __habs2(h[0]);  // the maximum of bf16 values is exact in bf16: two elements per instruction
+// Eight consecutive elements, kept as loaded (packed) while further loads are in flight.
+template <typename T>
+struct Raw8;
+template <>
+struct Raw8<__nv_bfloat16> {
+  uint4 w;
+  __device__ __forceinline__ void load(const __nv_bfloat16* p) { w = __ldcs(reinterpret_cast<const uint4*>(p)); }
+  __device__ __forceinline__ void zero() { w = make_uint4(0, 0, 0, 0); }
+  // fp32 values and the largest magnitude (the maximum of bf16 values is exact in bf16: two elements per instruction)
+  __device__ __forceinline__ float unpack(float (&v)[8]) const {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&w);
+    __nv_bfloat162 m2 = __habs2(h[0]);
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    if (i > 0) m2 = __hmax2(m2, __habs2(h[i]));
-    const float2 f = __bfloat1622float2(h[i]);
-    v[2 * i] = f.x;
-    v[2 * i + 1] = f.y;
+    for (int i = 0; i < 4; ++i) {
+      if (i > 0) m2 = __hmax2(m2, __habs2(h[i]));
+      const float2 f = __bfloat1622float2(h[i]);
+      v[2 * i] = f.x;
+      v[2 * i + 1] = f.y;
+    }
+    const float2 mf = __bfloat1622float2(m2);
+    return fmaxf(mf.x, mf.y);
   }
-  const float2 mf = __bfloat1622float2(m2);
-  return fmaxf(mf.x, mf.y);
-}
-__device__ __forceinline__ float load8(const float* p, float (&v)[8]) {
-  const float4 a = __ldcs(reinterpret_cast<const float4*>(p));
-  const float4 b = __ldcs(reinterpret_cast<const float4*>(p) + 1);
-  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-  v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-  float m = 0.f;
+};
+template <>
+struct Raw8<float> {
+  float4 a, b;
+  __device__ __forceinline__ void load(const float* p) {
+    a = __ldcs(reinterpret_cast<const float4*>(p));
+    b = __ldcs(reinterpret_cast<const float4*>(p) + 1);
+  }
+  __device__ __forceinline__ void zero() { a = b = make_float4(0.f, 0.f, 0.f, 0.f); }
+  __device__ __forceinline__ float unpack(float (&v)[8]) const {
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+    v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    float m = 0.f;
 #pragma unroll
-  for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(v[i]));
-  return m;
-}
+    for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(v[i]));
+    return m;
+  }
+};
 
-// One half-warp per 1x128 block; `blocks` = M * K / 128 blocks, numbered row-major (row, K block).
+// Blocks in flight per half-warp: enough 16-byte loads outstanding to cover HBM latency at full bandwidth
+template <typename T>
+__host__ __device__ constexpr int quant_unroll() { return sizeof(T) == 2 ? 8 : 4; }
+
 // kPitched = false: rows are contiguous (ld_x == K), block b starts at element 128 * b and no division is needed.
 template <typename T, bool kPitched>
 __global__ void __launch_bounds__(kQuantThreads)
@@ -57,11 +74,11 @@ quantize_act_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, float* __r
                     long long ld_x, uint32_t kb) {
   const int lane = threadIdx.x & 31;
   const int sub = lane & 15;                 // position inside the half-warp: elements 8*sub .. 8*sub+7 of the block
+  constexpr int kQuantUnroll = quant_unroll<T>();
   const uint32_t half_warps = gridDim.x * (kQuantThreads / 16);
   // the host keeps blocks + kQuantUnroll * half_warps below 2^32
   for (uint32_t b = blockIdx.x * (kQuantThreads / 16) + (threadIdx.x >> 4); b < blocks; b += half_warps * kQuantUnroll) {
-    float v[kQuantUnroll][8];
-    float local_max[kQuantUnroll];
+    Raw8<T> raw[kQuantUnroll];
     bool live[kQuantUnroll];
 #pragma unroll
     for (int u = 0; u < kQuantUnroll; ++u) {
@@ -71,19 +88,18 @@ quantize_act_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, float* __r
         if constexpr (kPitched) {
           const uint32_t row = bb / kb;
           const uint32_t j = bb - row * kb;
-          local_max[u] = load8(x + row * ld_x + static_cast<long long>(j) * 128 + sub * 8, v[u]);
+          raw[u].load(x + row * ld_x + static_cast<long long>(j) * 128 + sub * 8);
         } else {
-          local_max[u] = load8(x + static_cast<long long>(bb) * 128 + sub * 8, v[u]);
+          raw[u].load(x + static_cast<long long>(bb) * 128 + sub * 8);
         }
       } else {
-        local_max[u] = 0.f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[u][i] = 0.f;
+        raw[u].zero();
       }
     }
 #pragma unroll
     for (int u = 0; u < kQuantUnroll; ++u) {
-      float amax = local_max[u];
+      float v[8];
+      float amax = raw[u].unpack(v);
 #pragma unroll
       for (int o = 8; o >= 1; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
       const float s = fmaxf(amax, 1e-12f) / 448.0f;
@@ -101,8 +117,8 @@ quantize_act_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, float* __r
 #pragma unroll
           for (int i = 0; i < 2; ++i) {
             // |x| <= amax, so |x / s| <= 448 up to one rounding; the saturating conversion does the clamp
-            const float a = quot(v[u][4 * w + 2 * i]);
-            const float c = quot(v[u][4 * w + 2 * i + 1]);
+            const float a = quot(v[4 * w + 2 * i]);
+            const float c = quot(v[4 * w + 2 * i + 1]);
             const __nv_fp8x2_storage_t pair = __nv_cvt_float2_to_fp8x2(make_float2(a, c), __NV_SATFINITE, __NV_E4M3);
             word |= static_cast<uint32_t>(pair) << (16 * i);
           }
