@@ -52,6 +52,18 @@ def shard_concat_weights(w: torch.Tensor, scale_w: torch.Tensor, rank: int, worl
     return shard_weights(w[:n], scale_w[:nb], w[n:], scale_w[nb:], rank, world)
 
 
+def shard_down_weights(down_w: torch.Tensor, scale_down: torch.Tensor, rank: int, world: int):
+    """Row-parallel shard of the down projection: the K range (intermediate columns) this rank produced.
+
+    `down_w` is e4m3 [H, N], `scale_down` fp32 [H/128, N/128]; returns contiguous copies of
+    down_w[:, lo:hi] and scale_down[:, lo/128:hi/128] (do this once, when the weights are loaded).
+    """
+    n = down_w.shape[1]
+    lo, hi = shard_bounds(n, rank, world)
+    w8 = down_w.view(torch.uint8)[:, lo:hi].contiguous().view(down_w.dtype)
+    return w8, scale_down[:, lo // BLOCK:hi // BLOCK].contiguous()
+
+
 def assemble_gathered(gathered: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Rank-major [R, M, N/R] -> row-major [M, N]."""
     r, m, ns = gathered.shape
@@ -114,6 +126,32 @@ def run_sharded_fused(x: torch.Tensor, scale_x: torch.Tensor, gate_shard: torch.
                buffers.shape, buffers.out.stride(0))
     buffers.barrier()
     return buffers.out
+
+
+@torch.no_grad()
+def mlp_block_sharded(x: torch.Tensor, gate_shard: torch.Tensor, scale_gate_shard: torch.Tensor,
+                      up_shard: torch.Tensor, scale_up_shard: torch.Tensor, down_shard: torch.Tensor,
+                      scale_down_shard: torch.Tensor, group=None) -> torch.Tensor:
+    """Tensor-parallel MLP block: column-parallel gate/up, row-parallel down projection, one all-reduce.
+
+    Every rank quantises the replicated activations, computes its N/R intermediate columns (kept as e4m3 +
+    scales, never exchanged), multiplies them with its K-shard of the down weights (`shard_down_weights`) and
+    the bf16 partial results [M, H] are summed over the ranks with an NCCL all-reduce (the one exchange step
+    this block has).  Returns the full bf16 [M, H] on every rank.
+    """
+    from .kernel import BLOCK as _B, blockwise_gemm, quantize_activation, run_fp8_output
+
+    m = x.shape[0]
+    n_local = gate_shard.shape[0]
+    xq, sx = quantize_activation(x)
+    mid_q = torch.empty(m, n_local, dtype=torch.float8_e4m3fn, device=x.device)
+    mid_s = torch.empty(m, n_local // _B, dtype=torch.float32, device=x.device)
+    run_fp8_output(xq, sx, gate_shard, scale_gate_shard, up_shard, scale_up_shard, mid_q, mid_s)
+    partial = torch.empty(m, down_shard.shape[0], dtype=torch.bfloat16, device=x.device)
+    blockwise_gemm(mid_q, mid_s, down_shard, scale_down_shard, partial)
+    if dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=group)
+    return partial
 
 
 @torch.no_grad()

@@ -5,7 +5,7 @@ Needs a B200, the image's CUTLASS tree (the reference loads NVIDIA's CuTe-DSL bl
 example from $CUTLASS_DIR) and an unmodified copy of the reference's kernel directory at
 baseline/_ref/179_fp8_mlp_gate_up_projection (git-ignored).  Usage, from the repository root:
 
-    python tests/golden/make_golden.py --out gpurun_out/golden [--time]
+    python tests/golden/make_golden.py --out <directory> [--time]
 
 Each shape runs in a fresh process because the reference caches its compiled kernel under a key
 that omits K and N (kernel.py:263).  For every shape a `<name>.pt` (sampled rows/columns of the
@@ -118,7 +118,7 @@ def _time(name: str, out_dir: str) -> None:
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--out", default=os.path.join(ROOT, "gpurun_out", "golden"))
+    ap.add_argument("--out", default=os.path.join(ROOT, "tests", "golden", "_generated"))
     ap.add_argument("--time", action="store_true", help="also time the reference kernel on two large shapes")
     ap.add_argument("--one", default=None)
     ap.add_argument("--time-one", default=None)

@@ -66,6 +66,18 @@ for _ in range(2):
     torch.cuda.synchronize()
     assert pkg.last_status()[0] == 0
     assert torch.equal(fused, ref), f"rank {rank}: fused gather differs"
+# tensor-parallel MLP block: column-parallel gate/up, row-parallel down projection, one all-reduce
+torch.manual_seed(5)
+h = k
+xb = torch.randn(m, h, device=dev).to(torch.bfloat16)
+dq, sd = W.quantize_weight_128x128(torch.randn(h, n, device=dev) * 0.02)
+ref_y = pkg.mlp_block(xb, inp.gate_proj_weight, inp.scale_gate, inp.up_proj_weight, inp.scale_up, dq, sd)
+dw, ds = pkg.shard_down_weights(dq, sd, rank, world)
+y = pkg.mlp_block_sharded(xb, gw, sg, uw, su, dw, ds)
+torch.cuda.synchronize()
+err = (y.float() - ref_y.float())
+rel = float(torch.linalg.vector_norm(err) / torch.linalg.vector_norm(ref_y.float()))
+assert rel <= 1e-2, f"rank {rank}: sharded MLP rel-L2 {rel}"     # bf16 partial sums instead of one fp32 sum
 dist.barrier()
 dist.destroy_process_group()
 print(f"rank {rank} ok")

@@ -12,7 +12,7 @@ import torch.multiprocessing as mp
 from oracle import gateup_oracle as O
 from sol_execbench_b200_kernels_b200 import workloads as W
 from sol_execbench_b200_kernels_b200.sharded import (assemble_gathered, gather_columns, shard_bounds,
-                                                      shard_concat_weights, shard_weights)
+                                                      shard_concat_weights, shard_down_weights, shard_weights)
 
 
 def test_shard_bounds_cover_and_tile():
@@ -97,3 +97,21 @@ def test_sharded_gather_matches_unsharded_gloo(world):
         p.join(120)
         assert p.exitcode == 0
     assert q.get() is True
+
+
+def test_row_parallel_down_projection_shards_sum_to_the_unsharded_result():
+    """The K-shards of the down projection (each rank's intermediate columns) add up to the full product."""
+    m, h, n, world = 24, 256, 1024, 4
+    gen = torch.Generator().manual_seed(17)
+    mid = torch.randn(m, n, generator=gen)
+    mq, ms = W.quantize_activation_1x128(mid)
+    dq, sd = W.quantize_weight_128x128(torch.randn(h, n, generator=gen) * 0.02)
+    full = O._blockwise_gemm(mq, ms, dq, sd)
+    acc = torch.zeros(m, h)
+    for r in range(world):
+        lo, hi = shard_bounds(n, r, world)
+        dw, ds = shard_down_weights(dq, sd, r, world)
+        assert dw.is_contiguous() and tuple(dw.shape) == (h, n // world) and tuple(ds.shape) == (h // 128, n // world // 128)
+        acc += O._blockwise_gemm(mq.view(torch.uint8)[:, lo:hi].contiguous().view(torch.float8_e4m3fn),
+                                 ms[:, lo // 128:hi // 128].contiguous(), dw, ds)
+    assert torch.allclose(acc, full, rtol=1e-5, atol=1e-5)
