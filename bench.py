@@ -457,6 +457,57 @@ def run_reference(args):
     }), flush=True)
 
 
+def run_mlp(args):
+    """Tensor-parallel MLP block (quantise -> gate/up + SwiGLU -> down projection -> sum over ranks) on N GPUs:
+    the NCCL all-reduce form against the form whose reduction runs in this library's kernels over peer memory.
+    A study line, not the headline metric."""
+    import torch.distributed as dist
+
+    import sol_execbench_b200_kernels_b200 as pkg
+    from sol_execbench_b200_kernels_b200 import workloads as W
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world < 2:
+        raise SystemExit("bench.py --mlp: launch under torch.distributed.run with 2 or more ranks")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist.init_process_group("nccl", device_id=dev)
+    m, h, n = W.SHAPES["prefill_8b"]
+    full = W.make_inputs(m, h, n, seed=0, device=dev)
+    gw, sg, uw, su = (t.clone() for t in pkg.shard_weights(full.gate_proj_weight, full.scale_gate,
+                                                           full.up_proj_weight, full.scale_up, rank, world))
+    del full
+    torch.manual_seed(1)
+    dq, sd = W.quantize_weight_128x128(torch.randn(h, n, device=dev) * 0.02)
+    dw, ds = pkg.shard_down_weights(dq, sd, rank, world)
+    del dq, sd
+    xb = torch.randn(m, h, device=dev).to(torch.bfloat16)
+    flush = torch.empty(L2_FLUSH_BYTES // 4, dtype=torch.float32, device=dev)
+    bufs = pkg.ReduceBuffers(m, h, dev)
+    forms = {
+        "nccl_all_reduce": lambda: pkg.mlp_block_sharded(xb, gw, sg, uw, su, dw, ds),
+        "fused_peer_stores": lambda: pkg.mlp_block_sharded_fused(xb, gw, sg, uw, su, dw, ds, bufs),
+    }
+    res = {}
+    for name, fn in forms.items():
+        total_ms, _ = time_device_steps(fn, args.steps, args.warmup, flush, lambda: dist.barrier())
+        t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        res[name] = round(float(t.item()) / args.steps, 5)
+    code, detail = pkg.last_status()
+    if code != 0:
+        raise SystemExit(f"bench.py: device status {code} detail {detail:#x}")
+    if rank == 0:
+        flops = 2.0 * m * h * n * 3
+        print(json.dumps({"study": "tensor-parallel MLP block", "n_gpus": world, "m": m, "hidden": h, "intermediate": n,
+                          "ms_per_step": res, "tflops": {k: round(flops / (v * 1e-3) / 1e12, 1) for k, v in res.items()},
+                          "steps": args.steps, "warmup": args.warmup}), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -467,11 +518,15 @@ def main():
     ap.add_argument("--gather", action="store_true", help="N>1: also all-gather the contiguous [M, N] output")
     ap.add_argument("--fused-gather", action="store_true",
                     help="N>1: contiguous [M, N] output on every rank through peer stores in the kernel epilogue")
+    ap.add_argument("--mlp", action="store_true",
+                    help="N>1: tensor-parallel MLP block, NCCL all-reduce against the fused peer-store reduction")
     ap.add_argument("--sweep", action="store_true", help="M sweep at K=4096, N=14336 on one GPU (plan crossover study)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)
+    elif args.mlp:
+        run_mlp(args)
     elif args.sweep:
         run_sweep(args)
     else:

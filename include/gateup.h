@@ -147,6 +147,31 @@ int gu_blockwise_gemm(const void* a, const float* scale_a, const void* b, const 
                       int64_t k, int64_t n, int64_t ld_c, void* stream);
 
 /*
+ * Row-parallel block-scaled GEMM with the reduce-scatter fused into its epilogue — first half of a fused
+ * GEMM + all-reduce over `world` GPUs of one box (the MLP's down projection when the intermediate dimension
+ * is sharded).  This rank multiplies a[M, K_local] by b[N, K_local]^T (same operand formats as
+ * gu_blockwise_gemm) and stores every bf16 partial tile with a plain TMA store straight into the buffer of
+ * the rank that owns those token rows: rank r owns rows [r*M/world, (r+1)*M/world); rank_slots[r] is r's
+ * buffer [world][M/world][N] bf16 as mapped into this process (symmetric memory / CUDA peer mapping), and
+ * this rank writes slot `rank` of it.  M must be a multiple of 128 * world.  No load touches peer memory.
+ * The caller runs a cross-rank barrier, then gu_reduce_gather.  The reference is single-GPU: no counterpart.
+ */
+int gu_blockwise_gemm_scatter(const void* a, const float* scale_a, const void* b, const float* scale_b,
+                              void* const* rank_slots, int world, int rank, int64_t m, int64_t k, int64_t n,
+                              void* stream);
+
+/*
+ * Second half: sums this rank's `world` slots ([world][M/world][H] bf16, filled by all ranks'
+ * gu_blockwise_gemm_scatter) in rank order in fp32, rounds once to bf16 and writes the reduced rows into
+ * every rank's full result rank_outputs[r] ([M][H] bf16, contiguous) at row rank*M/world, with 16-byte
+ * stores (over NVLink for the peers).  After a second cross-rank barrier every rank holds the full sum.
+ * The summation order is fixed, so all ranks hold identical bits.  H a multiple of 8.  No counterpart in the
+ * reference; it stands where an NCCL all-reduce would follow gu_blockwise_gemm.
+ */
+int gu_reduce_gather(const void* slots, void* const* rank_outputs, int world, int rank, int64_t m, int64_t h,
+                     void* stream);
+
+/*
  * Activation quantiser, the step in front of gu_run: x[M, K] (bf16, or fp32 when x_is_f32 != 0; row pitch ld_x
  * elements) -> q[M, K] e4m3 and scale[M, K/128] fp32 with scale = amax of the 1x128 block / 448, the layout
  * `x` / `scale_x` of gu_problem.  The reference takes its activations already quantised

@@ -28,6 +28,7 @@ PLAN_NAMES = {PLAN_AUTO: "auto", PLAN_TILE: "tile", PLAN_STREAM: "stream", PLAN_
 EXPORTS = (
     "gu_version", "gu_error_string", "gu_select_plan", "gu_workspace_bytes", "gu_workspace_init",
     "gu_run", "gu_run_concat", "gu_last_status", "gu_launch_count", "gu_run_decode_static", "gu_run_gather", "gu_quantize_activation", "gu_blockwise_gemm", "gu_run_fp8out",
+    "gu_blockwise_gemm_scatter", "gu_reduce_gather",
 )
 
 
@@ -79,6 +80,11 @@ def _load() -> ctypes.CDLL:
     lib.gu_blockwise_gemm.restype = c_int
     lib.gu_blockwise_gemm.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                       c_int64, c_void_p]
+    lib.gu_blockwise_gemm_scatter.restype = c_int
+    lib.gu_blockwise_gemm_scatter.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, POINTER(c_void_p), c_int, c_int,
+                                              c_int64, c_int64, c_int64, c_void_p]
+    lib.gu_reduce_gather.restype = c_int
+    lib.gu_reduce_gather.argtypes = [c_void_p, POINTER(c_void_p), c_int, c_int, c_int64, c_int64, c_void_p]
     lib.gu_run_fp8out.restype = c_int
     lib.gu_run_fp8out.argtypes = [POINTER(GuProblem), c_void_p, c_void_p, c_void_p]
     lib.gu_last_status.restype = c_int

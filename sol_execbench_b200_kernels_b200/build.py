@@ -15,7 +15,7 @@ PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 LIB_PATH = PKG_DIR / "libgateup.so"
 SOURCES = [CSRC / "gateup.cu"]
-HEADERS = [CSRC / "ptx_sm100.cuh", CSRC / "gateup_tile.cuh", CSRC / "gateup_stream.cuh", CSRC / "quantize_act.cuh",
+HEADERS = [CSRC / "ptx_sm100.cuh", CSRC / "gateup_tile.cuh", CSRC / "gateup_stream.cuh", CSRC / "quantize_act.cuh", CSRC / "reduce_gather.cuh",
            PKG_DIR.parent / "include" / "gateup.h"]
 
 NVCC_FLAGS = [

@@ -14,6 +14,7 @@
 #include "gateup_stream.cuh"
 #include "gateup_tile.cuh"
 #include "quantize_act.cuh"
+#include "reduce_gather.cuh"
 
 namespace gu {
 namespace {
@@ -122,6 +123,8 @@ int device_info(DeviceInfo** out) {
         cudaFuncSetAttribute(blockwise_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
             cudaSuccess ||
         cudaFuncSetAttribute(gateup_tile_fp8out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
+            cudaSuccess ||
+        cudaFuncSetAttribute(blockwise_gemm_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
             cudaSuccess ||
         cudaFuncSetAttribute(gateup_stream_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
             cudaSuccess ||
@@ -237,6 +240,8 @@ int launch_tile(const gu_problem* pr, const DeviceInfo& dev, cudaStream_t stream
   p.out_col0 = 0;
   p.n_blocks128 = 0;
   p.scale_out = nullptr;
+  p.blocks_per_owner = 1;
+  p.slot_rows = 0;
   const int total_tiles = p.num_tiles;
   const int sms = dev.sm_count;
   // Hybrid schedule: whole rounds of tiles run data-parallel; the last round plus the remainder (between one and
@@ -568,6 +573,8 @@ int gu_run_gather(const gu_problem* pr, void* const* rank_outputs, int world, in
   p.epoch = 0;
   p.n_blocks128 = 0;
   p.scale_out = nullptr;
+  p.blocks_per_owner = 1;
+  p.slot_rows = 0;
   p.out_count = world;
   p.out_rank = rank;
   p.out_col0 = static_cast<int>(int64_t(rank) * n);
@@ -575,6 +582,98 @@ int gu_run_gather(const gu_problem* pr, void* const* rank_outputs, int world, in
   const int grid = p.num_tiles < dev->sm_count ? p.num_tiles : dev->sm_count;
   gu::gateup_tile_gather_kernel<<<grid, gu::kTileThreads, gu::kTileSmemBytes, static_cast<cudaStream_t>(stream_v)>>>(
       tm_x, tm_g, tm_u, peers, p);
+  gu::g_launches.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError() == cudaSuccess ? GU_OK : GU_ECUDA;
+}
+
+int gu_blockwise_gemm_scatter(const void* a, const float* scale_a, const void* b, const float* scale_b,
+                              void* const* rank_slots, int world, int rank, int64_t m, int64_t k, int64_t n,
+                              void* stream_v) {
+  if (!a || !scale_a || !b || !scale_b || !rank_slots) return GU_EINVAL_NULL;
+  if (!gu::shape_ok(m, k, n) || world < 1 || world > 8 || rank < 0 || rank >= world) return GU_EINVAL_SHAPE;
+  if (m % (128 * int64_t(world)) != 0) return GU_EINVAL_SHAPE;  // every rank owns the same whole number of token blocks
+  if (!gu::aligned16(a) || !gu::aligned16(b) || (reinterpret_cast<uintptr_t>(scale_a) & 3u) ||
+      (reinterpret_cast<uintptr_t>(scale_b) & 3u))
+    return GU_EINVAL_ALIGN;
+  for (int r = 0; r < world; ++r) {
+    if (!rank_slots[r]) return GU_EINVAL_NULL;
+    if (!gu::aligned16(rank_slots[r])) return GU_EINVAL_ALIGN;
+  }
+  gu::DeviceInfo* dev = nullptr;
+  int rc = gu::device_info(&dev);
+  if (rc != GU_OK) return rc;
+  const int64_t slot_rows = m / world;
+
+  CUtensorMap tm_a, tm_b;
+  gu::PeerMaps peers;
+  std::memset(&peers, 0, sizeof(peers));
+  if ((rc = gu::get_map(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a, k, m, k, 128, 128)) != GU_OK) return rc;
+  if ((rc = gu::get_map(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b, k, n, k, 128, 128)) != GU_OK) return rc;
+  for (int r = 0; r < world; ++r) {
+    // rank r's buffer: `world` slots of [slot_rows, n] bf16, one per sending rank
+    if ((rc = gu::get_map(&peers.m[r], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rank_slots[r], n, slot_rows * world, n * 2,
+                          64, 128)) != GU_OK)
+      return rc;
+  }
+  gu::TileParams p;
+  p.scale_x = scale_a;
+  p.scale_gate = scale_b;
+  p.scale_up = scale_b;
+  p.m = static_cast<int>(m);
+  p.kb = static_cast<int>(k / 128);
+  p.n_blocks128 = static_cast<int>(n / 128);
+  p.scale_out = nullptr;
+  p.num_m_blocks = static_cast<int>(m / gu::kTileM);
+  p.num_n_blocks = (p.n_blocks128 + 1) / 2;
+  const int64_t tiles = int64_t(p.num_m_blocks) * p.num_n_blocks;
+  if (tiles * (k / 128) >= (1ll << 31)) return GU_EINVAL_SHAPE;
+  p.num_tiles = static_cast<int>(tiles);
+  int64_t gm = (24ll << 20) / (128 * k);
+  if (gm < 1) gm = 1;
+  if (gm > p.num_m_blocks) gm = p.num_m_blocks;
+  p.group_m = static_cast<int>(gm);
+  p.tile_begin = 0;
+  p.flags = nullptr;
+  p.partials = nullptr;
+  p.epoch = 0;
+  p.out_count = world;
+  p.out_rank = rank;
+  p.out_col0 = 0;
+  p.blocks_per_owner = p.num_m_blocks / world;
+  p.slot_rows = static_cast<int>(slot_rows);
+
+  const int grid = p.num_tiles < dev->sm_count ? p.num_tiles : dev->sm_count;
+  gu::blockwise_gemm_scatter_kernel<<<grid, gu::kTileThreads, gu::kTileSmemBytes, static_cast<cudaStream_t>(stream_v)>>>(
+      tm_a, tm_b, peers, p);
+  gu::g_launches.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError() == cudaSuccess ? GU_OK : GU_ECUDA;
+}
+
+int gu_reduce_gather(const void* slots, void* const* rank_outputs, int world, int rank, int64_t m, int64_t h,
+                     void* stream_v) {
+  if (!slots || !rank_outputs) return GU_EINVAL_NULL;
+  if (world < 1 || world > 8 || rank < 0 || rank >= world || m < 1 || h < 8 || m % world != 0 || h % 8 != 0)
+    return GU_EINVAL_SHAPE;
+  if (!gu::aligned16(slots)) return GU_EINVAL_ALIGN;
+  gu::DeviceInfo* dev = nullptr;
+  int rc = gu::device_info(&dev);
+  if (rc != GU_OK) return rc;
+  gu::ReduceGatherParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.slots = static_cast<const uint4*>(slots);
+  for (int r = 0; r < world; ++r) {
+    if (!rank_outputs[r]) return GU_EINVAL_NULL;
+    if (!gu::aligned16(rank_outputs[r])) return GU_EINVAL_ALIGN;
+    p.outputs[r] = static_cast<uint4*>(rank_outputs[r]);
+  }
+  const int64_t slot_rows = m / world;
+  p.words_per_slot = slot_rows * h / 8;
+  p.out_word0 = int64_t(rank) * p.words_per_slot;
+  p.world = world;
+  long long grid = (p.words_per_slot + 255) / 256;
+  const long long cap = static_cast<long long>(dev->sm_count) * 8;
+  if (grid > cap) grid = cap;
+  gu::reduce_gather_kernel<<<static_cast<int>(grid), 256, 0, static_cast<cudaStream_t>(stream_v)>>>(p);
   gu::g_launches.fetch_add(1, std::memory_order_relaxed);
   return cudaGetLastError() == cudaSuccess ? GU_OK : GU_ECUDA;
 }
@@ -687,6 +786,8 @@ int gu_blockwise_gemm(const void* a, const float* scale_a, const void* b, const 
   p.kb = static_cast<int>(k / 128);
   p.n_blocks128 = static_cast<int>(n / 128);
   p.scale_out = nullptr;
+  p.blocks_per_owner = 1;
+  p.slot_rows = 0;
   p.num_m_blocks = static_cast<int>((m + gu::kTileM - 1) / gu::kTileM);
   p.num_n_blocks = (p.n_blocks128 + 1) / 2;  // a CTA tile spans two 128-column blocks of B
   const int64_t tiles = int64_t(p.num_m_blocks) * p.num_n_blocks;

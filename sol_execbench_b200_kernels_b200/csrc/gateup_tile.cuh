@@ -89,6 +89,11 @@ struct TileParams {
   int out_col0;
   int n_blocks128;          // single-projection and fp8-output launches: N / 128
   float* scale_out;         // fp8-output launch only: [M, N/128] scales of the re-quantised result
+  // scatter launch only (row-parallel GEMM whose partial results are summed over the ranks): the token blocks
+  // are owned by ranks in runs of `blocks_per_owner`; a tile goes to its owner's buffer, into the slot of the
+  // sending rank (slot s starts at row s * slot_rows of that buffer)
+  int blocks_per_owner;
+  int slot_rows;
   // stream-K schedule only
   unsigned int* flags;      // [gridDim.x] epoch of the last call that filled slot i
   float* partials;          // [gridDim.x][32][256] float4: values 4i..4i+3 of consumer thread t at [i * 256 + t]
@@ -151,7 +156,7 @@ struct PeerMaps {
 };
 
 // The kernel body; `outs` points at the output descriptor(s) in kernel parameter space.
-template <bool kStreamK, bool kGather, bool kSingle = false, bool kFp8Out = false>
+template <bool kStreamK, bool kGather, bool kSingle = false, bool kFp8Out = false, bool kScatter = false>
 __device__ __forceinline__ void tile_kernel_body(const CUtensorMap& tm_x, const CUtensorMap& tm_gate,
                                                  const CUtensorMap& tm_up, const CUtensorMap* outs,
                                                  const TileParams& p) {
@@ -191,7 +196,7 @@ __device__ __forceinline__ void tile_kernel_body(const CUtensorMap& tm_x, const 
     tma_prefetch_desc(&tm_x);
     tma_prefetch_desc(&tm_gate);
     tma_prefetch_desc(&tm_up);
-    if constexpr (kGather) {
+    if constexpr (kGather || kScatter) {
       for (int r = 0; r < p.out_count; ++r) tma_prefetch_desc(&outs[r]);
     } else {
       tma_prefetch_desc(&outs[0]);
@@ -421,7 +426,15 @@ __device__ __forceinline__ void tile_kernel_body(const CUtensorMap& tm_x, const 
             fence_proxy_async_smem();
             named_bar_sync(1 + half, 128);
             if (store_leader && !ctx.aborted && 2 * cur_nb + part < p.n_blocks128) {
-              tma_store_2d(&outs[0], out_half, (2 * cur_nb + part) * kTileN + half * 64, cur_mb * kTileM);
+              if constexpr (kScatter) {
+                // partial result of a row-parallel GEMM: plain TMA store into the owner rank's buffer (over
+                // NVLink unless it is this rank), in the slot reserved for this rank; the owner sums the slots
+                const int owner = cur_mb / p.blocks_per_owner;
+                const int y = p.out_rank * p.slot_rows + (cur_mb - owner * p.blocks_per_owner) * kTileM;
+                tma_store_2d(&outs[owner], out_half, (2 * cur_nb + part) * kTileN + half * 64, y);
+              } else {
+                tma_store_2d(&outs[0], out_half, (2 * cur_nb + part) * kTileN + half * 64, cur_mb * kTileM);
+              }
               tma_store_commit();
             }
           }
@@ -629,6 +642,14 @@ __global__ void __launch_bounds__(kTileThreads, 1)
 blockwise_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                       const __grid_constant__ CUtensorMap tm_c, const TileParams p) {
   tile_kernel_body<false, false, true>(tm_a, tm_b, tm_b, &tm_c, p);
+}
+
+// Plain block-scaled GEMM whose output tiles are scattered to the ranks that own their token rows
+// (see TileParams::blocks_per_owner): the compute half of a fused GEMM + reduce-scatter.
+__global__ void __launch_bounds__(kTileThreads, 1)
+blockwise_gemm_scatter_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                              const __grid_constant__ PeerMaps peers, const TileParams p) {
+  tile_kernel_body<false, false, true, false, true>(tm_a, tm_b, tm_b, peers.m, p);
 }
 
 // Data-parallel schedule with the column all-gather fused into the epilogue (see TileParams::out_count).

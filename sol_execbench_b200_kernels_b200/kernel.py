@@ -271,6 +271,54 @@ def blockwise_gemm(a: torch.Tensor, scale_a: torch.Tensor, b: torch.Tensor, scal
 
 
 @torch.no_grad()
+def blockwise_gemm_scatter(a: torch.Tensor, scale_a: torch.Tensor, b: torch.Tensor, scale_b: torch.Tensor,
+                           rank_slot_ptrs, rank: int) -> None:
+    """Row-parallel `blockwise_gemm` whose bf16 partial tiles go straight to the ranks owning their token rows.
+
+    `rank_slot_ptrs[r]` is the device address of rank r's [world, M/world, N] slot buffer as mapped into this
+    process (see `sharded.ReduceBuffers`); this rank fills slot `rank` of every buffer.  M must be a multiple
+    of 128 * world.  Asynchronous; a cross-rank barrier and `reduce_gather` follow.
+    """
+    world = len(rank_slot_ptrs)
+    m, k = a.shape
+    n = b.shape[0]
+    if k % BLOCK or n % BLOCK or k < BLOCK or n < BLOCK or m % (BLOCK * world):
+        raise ValueError(f"Unsupported contract shape M={m}, K={k}, N={n}: need K, N multiples of {BLOCK} "
+                         f"and M a multiple of {BLOCK} * world")
+    expected = {
+        "a": (a, (m, k), torch.float8_e4m3fn), "scale_a": (scale_a, (m, k // BLOCK), torch.float32),
+        "b": (b, (n, k), torch.float8_e4m3fn), "scale_b": (scale_b, (n // BLOCK, k // BLOCK), torch.float32),
+    }
+    _check(expected, a.device)
+    with torch.cuda.device(a.device):
+        stream_ptr = torch.cuda.current_stream(a.device).cuda_stream
+        ptrs = (ctypes.c_void_p * world)(*[int(p) for p in rank_slot_ptrs])
+        code = _cabi.lib.gu_blockwise_gemm_scatter(a.data_ptr(), scale_a.data_ptr(), b.data_ptr(),
+                                                   scale_b.data_ptr(), ptrs, world, rank, m, k, n, stream_ptr)
+    if code != _cabi.GU_OK:
+        if code in (_cabi.GU_EINVAL_NULL, _cabi.GU_EINVAL_SHAPE, _cabi.GU_EINVAL_ALIGN):
+            raise ValueError(f"libgateup: {_cabi.error_string(code)} (code {code})")
+        raise _cabi.GateUpError(code, _cabi.error_string(code))
+
+
+@torch.no_grad()
+def reduce_gather(slots: torch.Tensor, rank_output_ptrs, rank: int, m: int, h: int) -> None:
+    """Sum this rank's slots [world, M/world, H] (bf16, fp32 accumulation in rank order) and write the reduced
+    rows into every rank's [M, H] result (`rank_output_ptrs[r]`, mapped into this process).  Asynchronous."""
+    world = len(rank_output_ptrs)
+    if slots.dtype != torch.bfloat16 or not slots.is_contiguous() or slots.numel() != m * h or m % world:
+        raise ValueError("slots must be a contiguous bf16 [world, M/world, H] tensor")
+    with torch.cuda.device(slots.device):
+        stream_ptr = torch.cuda.current_stream(slots.device).cuda_stream
+        ptrs = (ctypes.c_void_p * world)(*[int(p) for p in rank_output_ptrs])
+        code = _cabi.lib.gu_reduce_gather(slots.data_ptr(), ptrs, world, rank, m, h, stream_ptr)
+    if code != _cabi.GU_OK:
+        if code in (_cabi.GU_EINVAL_NULL, _cabi.GU_EINVAL_SHAPE, _cabi.GU_EINVAL_ALIGN):
+            raise ValueError(f"libgateup: {_cabi.error_string(code)} (code {code})")
+        raise _cabi.GateUpError(code, _cabi.error_string(code))
+
+
+@torch.no_grad()
 def quantize_activation(x: torch.Tensor, q: Optional[torch.Tensor] = None,
                         scale: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """bf16 / fp32 activations [M, K] -> (e4m3 [M, K], fp32 scales [M, K/128]), scale = block amax / 448.

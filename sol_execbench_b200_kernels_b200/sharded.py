@@ -154,6 +154,59 @@ def mlp_block_sharded(x: torch.Tensor, gate_shard: torch.Tensor, scale_gate_shar
     return partial
 
 
+class ReduceBuffers:
+    """Symmetric buffers of the fused row-parallel GEMM + all-reduce: per rank a bf16 slot buffer
+    [world, M/world, H] (one partial result per sending rank, for the token rows this rank owns) and a bf16
+    [M, H] result, both mapped into every rank of the group.  Allocate once and reuse."""
+
+    def __init__(self, m: int, h: int, device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.group = group if group is not None else dist.group.WORLD
+        world = dist.get_world_size(self.group)
+        if m % (BLOCK * world):
+            raise ValueError(f"M={m} must be a multiple of {BLOCK} * world ({world})")
+        self.slots = symm_mem.empty((world, m // world, h), dtype=torch.bfloat16, device=device)
+        self.slots_handle = symm_mem.rendezvous(self.slots, self.group)
+        self.out = symm_mem.empty((m, h), dtype=torch.bfloat16, device=device)
+        self.handle = symm_mem.rendezvous(self.out, self.group)
+        self.rank = self.handle.rank
+        self.world = self.handle.world_size
+        self.slot_ptrs = [int(p) for p in self.slots_handle.buffer_ptrs]
+        self.out_ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.shape = (m, h)
+
+    def barrier(self) -> None:
+        self.handle.barrier()
+
+
+@torch.no_grad()
+def mlp_block_sharded_fused(x: torch.Tensor, gate_shard: torch.Tensor, scale_gate_shard: torch.Tensor,
+                            up_shard: torch.Tensor, scale_up_shard: torch.Tensor, down_shard: torch.Tensor,
+                            scale_down_shard: torch.Tensor, buffers: ReduceBuffers) -> torch.Tensor:
+    """`mlp_block_sharded` with the all-reduce done by the library's own kernels over peer memory.
+
+    The down projection's epilogue TMA-stores each bf16 partial tile into the slot buffer of the rank that
+    owns those token rows (reduce-scatter, overlapped with the math tile by tile); after a barrier each rank
+    sums its slots in rank order and writes the reduced rows into every rank's [M, H] result (all-gather by
+    peer stores).  Three cross-rank barriers, no NCCL call.  All ranks return identical bits.
+    """
+    from .kernel import BLOCK as _B, blockwise_gemm_scatter, quantize_activation, reduce_gather, run_fp8_output
+
+    m, h = buffers.shape
+    n_local = gate_shard.shape[0]
+    xq, sx = quantize_activation(x)
+    mid_q = torch.empty(m, n_local, dtype=torch.float8_e4m3fn, device=x.device)
+    mid_s = torch.empty(m, n_local // _B, dtype=torch.float32, device=x.device)
+    run_fp8_output(xq, sx, gate_shard, scale_gate_shard, up_shard, scale_up_shard, mid_q, mid_s)
+    buffers.barrier()  # the previous call's reduce has read every slot and nobody still reads `out`
+    blockwise_gemm_scatter(mid_q, mid_s, down_shard, scale_down_shard, buffers.slot_ptrs, buffers.rank)
+    buffers.barrier()  # all partial tiles have landed in their owners' slots
+    reduce_gather(buffers.slots, buffers.out_ptrs, buffers.rank, m, h)
+    buffers.barrier()  # every rank's rows have landed in every result
+    return buffers.out
+
+
 @torch.no_grad()
 def run_sharded(x: torch.Tensor, scale_x: torch.Tensor, gate_shard: torch.Tensor, scale_gate_shard: torch.Tensor,
                 up_shard: torch.Tensor, scale_up_shard: torch.Tensor, output_shard: torch.Tensor,

@@ -78,10 +78,78 @@ torch.cuda.synchronize()
 err = (y.float() - ref_y.float())
 rel = float(torch.linalg.vector_norm(err) / torch.linalg.vector_norm(ref_y.float()))
 assert rel <= 1e-2, f"rank {rank}: sharded MLP rel-L2 {rel}"     # bf16 partial sums instead of one fp32 sum
+# the same block with the all-reduce done by the library's kernels over peer memory: partial tiles TMA-stored
+# into the owners' slots, slots summed in fp32 in rank order, reduced rows stored into every rank's result
+partial = torch.empty(m, h, dtype=torch.bfloat16, device=dev)
+xq, sx = pkg.quantize_activation(xb)
+mid_q = torch.empty(m, n // world, dtype=torch.float8_e4m3fn, device=dev)
+mid_s = torch.empty(m, n // world // 128, dtype=torch.float32, device=dev)
+pkg.run_fp8_output(xq, sx, gw, sg, uw, su, mid_q, mid_s)
+pkg.blockwise_gemm(mid_q, mid_s, dw, ds, partial)
+parts = torch.empty(world, m, h, dtype=torch.bfloat16, device=dev)
+dist.all_gather_into_tensor(parts.view(world * m, h), partial)
+want = torch.zeros(m, h, dtype=torch.float32, device=dev)
+for r in range(world):
+    want += parts[r].float()
+want = want.to(torch.bfloat16)
+rb = pkg.ReduceBuffers(m, h, dev)
+for _ in range(2):
+    rb.out.fill_(float("nan"))
+    rb.slots.fill_(float("nan"))
+    yf = pkg.mlp_block_sharded_fused(xb, gw, sg, uw, su, dw, ds, rb)
+    torch.cuda.synchronize()
+    assert pkg.last_status()[0] == 0
+    assert torch.equal(yf, want), f"rank {rank}: fused reduce differs from the fp32 sum of the bf16 partials"
+    rel = float(torch.linalg.vector_norm(yf.float() - ref_y.float()) / torch.linalg.vector_norm(ref_y.float()))
+    assert rel <= 1e-2, f"rank {rank}: fused sharded MLP rel-L2 {rel}"
 dist.barrier()
 dist.destroy_process_group()
 print(f"rank {rank} ok")
 """
+
+
+@pytest.mark.parametrize("shape,world", [((128, 256, 128), 1), ((512, 512, 384), 2), ((1024, 1024, 256), 8),
+                                         ((1536, 512, 1024), 4)])
+def test_scatter_and_reduce_on_one_gpu_sum_the_partial_products(shape, world):
+    """All ranks of the fused GEMM + all-reduce emulated one after another on one GPU (separate buffers, no kernel
+    waits on another): every rank's result must equal the fp32 sum, in rank order, of the bf16 partial products."""
+    import sol_execbench_b200_kernels_b200 as pkg
+
+    m, k, h = shape  # k = the full intermediate dimension, split over the ranks
+    dev = torch.device("cuda:0")
+    torch.manual_seed(21)
+    a, sa = W.quantize_activation_1x128(torch.randn(m, k, device=dev))
+    b, sb = W.quantize_weight_128x128(torch.randn(h, k, device=dev) * 0.05)
+    slots = [torch.full((world, m // world, h), float("nan"), dtype=torch.bfloat16, device=dev) for _ in range(world)]
+    outs = [torch.full((m, h), float("nan"), dtype=torch.bfloat16, device=dev) for _ in range(world)]
+    want = torch.zeros(m, h, dtype=torch.float32, device=dev)
+    for r in range(world):
+        lo, hi = pkg.shard_bounds(k, r, world)
+        a_r = a.view(torch.uint8)[:, lo:hi].contiguous().view(a.dtype)
+        sa_r = sa[:, lo // 128:hi // 128].contiguous()
+        b_r, sb_r = pkg.shard_down_weights(b, sb, r, world)
+        part = torch.empty(m, h, dtype=torch.bfloat16, device=dev)
+        pkg.blockwise_gemm(a_r, sa_r, b_r, sb_r, part)
+        want += part.float()
+        pkg.blockwise_gemm_scatter(a_r, sa_r, b_r, sb_r, [s.data_ptr() for s in slots], r)
+    for r in range(world):
+        pkg.reduce_gather(slots[r], [o.data_ptr() for o in outs], r, m, h)
+    torch.cuda.synchronize()
+    assert pkg.last_status()[0] == 0
+    want = want.to(torch.bfloat16)
+    for r in range(world):
+        assert torch.equal(outs[r], want), f"rank {r}"
+
+
+def test_scatter_rejects_token_counts_that_do_not_split_into_whole_blocks():
+    import sol_execbench_b200_kernels_b200 as pkg
+
+    dev = torch.device("cuda:0")
+    a, sa = W.quantize_activation_1x128(torch.randn(384, 256, device=dev))
+    b, sb = W.quantize_weight_128x128(torch.randn(128, 256, device=dev))
+    slots = [torch.empty(2, 192, 128, dtype=torch.bfloat16, device=dev) for _ in range(2)]
+    with pytest.raises(ValueError):
+        pkg.blockwise_gemm_scatter(a, sa, b, sb, [s.data_ptr() for s in slots], 0)
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
