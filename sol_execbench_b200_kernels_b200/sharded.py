@@ -189,7 +189,8 @@ def mlp_block_sharded_fused(x: torch.Tensor, gate_shard: torch.Tensor, scale_gat
     The down projection's epilogue TMA-stores each bf16 partial tile into the slot buffer of the rank that
     owns those token rows (reduce-scatter, overlapped with the math tile by tile); after a barrier each rank
     sums its slots in rank order and writes the reduced rows into every rank's [M, H] result (all-gather by
-    peer stores).  Three cross-rank barriers, no NCCL call.  All ranks return identical bits.
+    peer stores).  Two cross-rank barriers, no NCCL call.  All ranks return identical bits.  Consume the
+    result on the stream this was called on (or synchronise with it) before the next call on `buffers`.
     """
     from .kernel import BLOCK as _B, blockwise_gemm_scatter, quantize_activation, reduce_gather, run_fp8_output
 
@@ -199,7 +200,9 @@ def mlp_block_sharded_fused(x: torch.Tensor, gate_shard: torch.Tensor, scale_gat
     mid_q = torch.empty(m, n_local, dtype=torch.float8_e4m3fn, device=x.device)
     mid_s = torch.empty(m, n_local // _B, dtype=torch.float32, device=x.device)
     run_fp8_output(xq, sx, gate_shard, scale_gate_shard, up_shard, scale_up_shard, mid_q, mid_s)
-    buffers.barrier()  # the previous call's reduce has read every slot and nobody still reads `out`
+    # No barrier in front of the scatter: the barrier that ended the previous call on these buffers already ordered
+    # every rank's reads of its slots before this point, and `out` is not written before the next barrier, by
+    # which every rank has enqueued (on this stream) whatever reads the previous result.
     blockwise_gemm_scatter(mid_q, mid_s, down_shard, scale_down_shard, buffers.slot_ptrs, buffers.rank)
     buffers.barrier()  # all partial tiles have landed in their owners' slots
     reduce_gather(buffers.slots, buffers.out_ptrs, buffers.rank, m, h)
