@@ -1,4 +1,4 @@
-"""Builds libgateup.so (sm_100a only) next to this file with a single nvcc call.
+"""Builds libgateup.so and libsideops.so (sm_100a only) next to this file, one nvcc call each.
 
 Run as ``python -m sol_execbench_b200_kernels_b200.build``; nvcc cross-compiles
 without a GPU.  The library is kept in-tree so it travels with the sources.
@@ -18,6 +18,10 @@ SOURCES = [CSRC / "gateup.cu"]
 HEADERS = [CSRC / "ptx_sm100.cuh", CSRC / "gateup_tile.cuh", CSRC / "gateup_stream.cuh", CSRC / "quantize_act.cuh", CSRC / "reduce_gather.cuh",
            PKG_DIR.parent / "include" / "gateup.h"]
 
+SIDE_LIB_PATH = PKG_DIR / "libsideops.so"
+SIDE_SOURCES = [CSRC / "sideops.cu"]
+SIDE_HEADERS = [PKG_DIR.parent / "include" / "sideops.h"]
+
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",
@@ -33,26 +37,35 @@ def find_nvcc() -> str:
     return nvcc
 
 
-def is_stale() -> bool:
-    if not LIB_PATH.exists():
+def _stale(lib: Path, deps) -> bool:
+    if not lib.exists():
         return True
-    built = LIB_PATH.stat().st_mtime
-    return any(p.stat().st_mtime > built for p in SOURCES + HEADERS)
+    built = lib.stat().st_mtime
+    return any(p.stat().st_mtime > built for p in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compile the library if it is missing or older than its sources."""
-    if not force and not is_stale():
-        return LIB_PATH
+def is_stale() -> bool:
+    return _stale(LIB_PATH, SOURCES + HEADERS) or _stale(SIDE_LIB_PATH, SIDE_SOURCES + SIDE_HEADERS)
+
+
+def _compile(lib: Path, sources, verbose: bool) -> None:
     cmd = [find_nvcc(), *NVCC_FLAGS]
     if verbose:
         cmd += ["-Xptxas", "-v"]
-    cmd += ["-o", str(LIB_PATH), *map(str, SOURCES)]
+    cmd += ["-o", str(lib), *map(str, sources)]
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if proc.returncode != 0:
         raise RuntimeError(f"nvcc failed ({proc.returncode}):\n{proc.stdout}\n{proc.stderr}")
     if verbose:
         sys.stderr.write(proc.stderr)
+
+
+def build(force: bool = False, verbose: bool = False) -> Path:
+    """Compile each library that is missing or older than its sources; returns the path of libgateup.so."""
+    if force or _stale(LIB_PATH, SOURCES + HEADERS):
+        _compile(LIB_PATH, SOURCES, verbose)
+    if force or _stale(SIDE_LIB_PATH, SIDE_SOURCES + SIDE_HEADERS):
+        _compile(SIDE_LIB_PATH, SIDE_SOURCES, verbose)
     return LIB_PATH
 
 

@@ -1,0 +1,375 @@
+// libsideops.so: the two HBM-bound operators that sit beside the FP8 gate/up path in the reference
+// repository — per-head RMSNorm of the Flux query / key tensors (problem 038) and the depthwise
+// convolution + SiLU tail of the Mamba mixer (problem 029).  sm_100a only; the C ABI is include/sideops.h.
+#include "../../include/sideops.h"
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <atomic>
+
+namespace so {
+
+std::atomic<long long> g_launches{0};
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// ------------------------------------------------------------------------------------------------------------
+// Per-head RMSNorm of query and key (problem 038).
+//
+// A row is one (token, head) vector of 128 fp32 = 512 bytes = one float4 per lane.  A warp owns
+// kRowsPerWarp consecutive rows and issues all of their loads before the first reduction, so that every
+// thread keeps 64 bytes in flight; blockIdx.y selects the tensor (0 query, 1 key).  Algorithmic traffic:
+// 2 tensors x (read + write) x 512 bytes per row; the [heads, 128] weights stay in L1/L2.
+// ------------------------------------------------------------------------------------------------------------
+constexpr int kNormRowsPerWarp = 4;
+constexpr int kNormWarps = 8;
+constexpr int kNormRowsPerBlock = kNormRowsPerWarp * kNormWarps;
+
+__global__ void __launch_bounds__(kNormWarps * 32)
+rmsnorm_qk_kernel(const float4* __restrict__ query, const float4* __restrict__ key,
+                  const float4* __restrict__ weight_q, const float4* __restrict__ weight_k, float eps,
+                  float4* __restrict__ query_norm, float4* __restrict__ key_norm, long long rows, int heads) {
+  const bool is_key = blockIdx.y != 0;
+  const float4* __restrict__ in = is_key ? key : query;
+  const float4* __restrict__ weight = is_key ? weight_k : weight_q;
+  float4* __restrict__ out = is_key ? key_norm : query_norm;
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const long long row0 = (static_cast<long long>(blockIdx.x) * kNormWarps + warp) * kNormRowsPerWarp;
+
+  float4 v[kNormRowsPerWarp];
+  float sum[kNormRowsPerWarp];
+#pragma unroll
+  for (int i = 0; i < kNormRowsPerWarp; ++i) {
+    v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (row0 + i < rows) v[i] = __ldcs(in + (row0 + i) * 32 + lane);
+  }
+#pragma unroll
+  for (int i = 0; i < kNormRowsPerWarp; ++i)
+    sum[i] = fmaf(v[i].w, v[i].w, fmaf(v[i].z, v[i].z, fmaf(v[i].y, v[i].y, v[i].x * v[i].x)));
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) {
+#pragma unroll
+    for (int i = 0; i < kNormRowsPerWarp; ++i) sum[i] += __shfl_xor_sync(0xffffffffu, sum[i], offset);
+  }
+  int head = static_cast<int>(row0 % heads);
+#pragma unroll
+  for (int i = 0; i < kNormRowsPerWarp; ++i) {
+    if (row0 + i < rows) {
+      const float4 w = __ldg(weight + head * 32 + lane);
+      const float s = rsqrtf(fmaf(sum[i], 1.0f / 128.0f, eps));
+      float4 r;
+      r.x = (v[i].x * s) * w.x;
+      r.y = (v[i].y * s) * w.y;
+      r.z = (v[i].z * s) * w.z;
+      r.w = (v[i].w * s) * w.w;
+      __stcs(out + (row0 + i) * 32 + lane, r);
+    }
+    if (++head == heads) head = 0;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// Mamba conv1d tail (problem 029): mask -> depthwise causal conv (4 taps) + bias -> SiLU -> mask, with the
+// [sequence, channel] -> [channel, sequence] transposition done through shared memory.
+//
+// A CTA owns 64 channels x 128 positions.  Load phase: 131 rows (3 rows of history) of 128 contiguous bytes,
+// 16 bytes per thread, pre-masked.  Compute phase: a lane owns a channel PAIR (one 32-bit shared-memory word
+// per row, so a warp reads 128 contiguous bytes), a warp owns 16 positions and slides the 4-tap window along
+// them; the fp32 arithmetic is done on (channel, channel+1) pairs with the packed f32x2 instructions.  Two
+// positions of one channel are packed into one word of the transposed output tile (pitch 65 words).  Store
+// phase: 128 contiguous bytes per warp instruction.  Algorithmic traffic: 2 bytes read + 2 bytes written per
+// (token, channel).
+//
+// The sigmoid costs 1.25 special-function operations per element instead of 2: e = 2^(-|x| log2 e) lies in
+// (0, 1], so the four denominators 1 + e of a 2 x 2 block lie in (1, 2] and are inverted with ONE reciprocal
+// of their product (products of the other three give each quotient back); sigmoid = 1/(1+e) for x >= 0 and
+// e/(1+e) for x < 0, which keeps full relative accuracy in the negative tail.
+// ------------------------------------------------------------------------------------------------------------
+constexpr int kConvChannels = 64;
+constexpr int kConvPositions = 128;
+constexpr int kConvTaps = 4;
+constexpr int kConvRows = kConvPositions + kConvTaps - 1;  // 131
+constexpr int kConvThreads = 256;
+constexpr int kConvOutPitch = kConvPositions / 2 + 1;  // words; odd, so lanes that differ in channel differ in bank
+constexpr int kConvRun = kConvPositions / (kConvThreads / 32);  // positions per warp = 16
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+__device__ __forceinline__ float rcp_approx(float x) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+__device__ __forceinline__ float2 bf16x2_to_float2(uint32_t w) {
+  return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
+__device__ __forceinline__ uint32_t float2_to_bf16x2(float2 v) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(v.y), "f"(v.x));
+  return r;
+}
+__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+// bf16(a * m) for both halves of a packed word; the fp32 product of two bf16 values is exact, so this is the
+// single rounding of the eager masked multiply
+__device__ __forceinline__ uint32_t mask_mul_bf16x2(uint32_t a, uint32_t m2) { return mul_bf16x2(a, m2); }
+
+// convolution + bias for one position of a channel pair, rounded to bf16 (packed)
+__device__ __forceinline__ uint32_t conv_pair(float2 x0, float2 x1, float2 x2, float2 x3, const float2 (&w)[4],
+                                              float2 bias) {
+  float2 acc = __fmul2_rn(x0, w[0]);
+  acc = __ffma2_rn(x1, w[1], acc);
+  acc = __ffma2_rn(x2, w[2], acc);
+  acc = __ffma2_rn(x3, w[3], acc);
+  acc = __fadd2_rn(acc, bias);
+  return float2_to_bf16x2(acc);
+}
+
+// sigmoid of one value in full relative accuracy at any magnitude: e = 2^(-|x| log2 e) with log2 e split into a
+// 16-bit head (its product with an 8-bit bf16 significand is exact in fp32) and a tail applied as a first-order
+// factor; 1/(1+e) for x >= 0, e/(1+e) for x < 0
+__device__ __noinline__ float sigmoid_wide(float x) {
+  constexpr float kLog2eHead = 1.44268798828125f;      // 0x3fb8aa00
+  constexpr float kLog2eTailLn2 = 4.888495152129525e-06f;  // (log2 e - head) * ln 2
+  const float a = fabsf(x);
+  const float e0 = ex2_approx(-a * kLog2eHead);
+  const float e = fmaf(e0, -a * kLog2eTailLn2, e0);
+  const float r = rcp_approx(1.0f + e);
+  return x < 0.f ? e * r : r;
+}
+
+// bf16(sigmoid) of the four bf16 values in two packed words (channel pair at two positions).
+// Common case (all four arguments >= -20): sigmoid = 1 / (1 + 2^(-x log2 e)) directly; each denominator is
+// below 2^30, so the product of the four stays finite and ONE reciprocal of it serves all four (products of the
+// other three give each quotient back): 1.25 special-function operations per element instead of 2.  Below -20
+// the rounding of the exponent's argument would show in the bf16 result, and the product could overflow: those
+// (rare) blocks take sigmoid_wide.
+__device__ __forceinline__ void sigmoid_2x2(uint32_t ca, uint32_t cb, uint32_t& sa, uint32_t& sb) {
+  constexpr float kNegLog2e = -1.4426950408889634f;
+  const float2 xa = bf16x2_to_float2(ca);
+  const float2 xb = bf16x2_to_float2(cb);
+  const __nv_bfloat162 lowest = __hmin2(*reinterpret_cast<const __nv_bfloat162*>(&ca),
+                                        *reinterpret_cast<const __nv_bfloat162*>(&cb));
+  float2 ra, rb;
+  if (__hbge2(lowest, __floats2bfloat162_rn(-20.f, -20.f))) {
+    const float2 scale = make_float2(kNegLog2e, kNegLog2e);
+    const float2 ta = __fmul2_rn(xa, scale);
+    const float2 tb = __fmul2_rn(xb, scale);
+    const float2 one = make_float2(1.f, 1.f);
+    const float2 ya = __fadd2_rn(make_float2(ex2_approx(ta.x), ex2_approx(ta.y)), one);
+    const float2 yb = __fadd2_rn(make_float2(ex2_approx(tb.x), ex2_approx(tb.y)), one);
+    const float2 pab = __fmul2_rn(ya, yb);        // (ya.x*yb.x, ya.y*yb.y)
+    const float inv = rcp_approx(pab.x * pab.y);  // 1 / (all four)
+    const float2 rab = make_float2(inv * pab.y, inv * pab.x);  // 1/(ya.x*yb.x), 1/(ya.y*yb.y)
+    ra = __fmul2_rn(rab, yb);                     // 1/ya
+    rb = __fmul2_rn(rab, ya);                     // 1/yb
+  } else {  // also taken for a NaN
+    ra = make_float2(sigmoid_wide(xa.x), sigmoid_wide(xa.y));
+    rb = make_float2(sigmoid_wide(xb.x), sigmoid_wide(xb.y));
+  }
+  sa = float2_to_bf16x2(ra);
+  sb = float2_to_bf16x2(rb);
+}
+
+__global__ void __launch_bounds__(kConvThreads)
+mamba_conv1d_tail_kernel(const __nv_bfloat16* __restrict__ projected, const __nv_bfloat16* __restrict__ mask,
+                         const __nv_bfloat16* __restrict__ conv_weight, const __nv_bfloat16* __restrict__ conv_bias,
+                         __nv_bfloat16* __restrict__ output, int sequence, int channels, long long width) {
+  __shared__ __align__(16) uint32_t s_in[kConvRows * (kConvChannels / 2)];  // [row][channel pair]
+  __shared__ uint32_t s_out[kConvChannels * kConvOutPitch];                 // [channel][position pair]
+  __shared__ uint32_t s_keep[kConvPositions / 2];  // per position pair: 0xffff in the half of a kept position
+
+  const int tid = threadIdx.x;
+  const int batch = blockIdx.z;
+  const int c0 = blockIdx.x * kConvChannels;
+  const int l0 = blockIdx.y * kConvPositions;
+  const long long token0 = static_cast<long long>(batch) * sequence;
+  const uint16_t* mask_bits = reinterpret_cast<const uint16_t*>(mask);
+
+  // ---- load phase: 131 rows x 8 chunks of 16 bytes; all global loads of a thread are issued first ----
+  constexpr int kChunks = kConvRows * (kConvChannels / 8);                   // 1048
+  constexpr int kLoadsPerThread = (kChunks + kConvThreads - 1) / kConvThreads;  // 5
+  uint4 raw[kLoadsPerThread];
+  uint32_t m2[kLoadsPerThread];
+#pragma unroll
+  for (int i = 0; i < kLoadsPerThread; ++i) {
+    const int idx = tid + i * kConvThreads;
+    const int row = idx >> 3;
+    const int l = l0 + row - (kConvTaps - 1);
+    raw[i] = make_uint4(0u, 0u, 0u, 0u);
+    m2[i] = 0u;
+    if (idx < kChunks && l >= 0 && l < sequence) {
+      const long long token = token0 + l;
+      raw[i] = __ldcs(reinterpret_cast<const uint4*>(projected + token * width + c0) + (idx & 7));
+      const uint32_t mb = __ldg(mask_bits + token);
+      m2[i] = mb | (mb << 16);
+    }
+  }
+  if (tid < kConvPositions / 2) {
+    // the reference keeps an output only where the mask is at least one half (bf16 bits 0x3f00 .. 0x7f80)
+    uint32_t keep = 0u;
+    const int l = l0 + 2 * tid;
+    if (l < sequence && __ldg(mask_bits + token0 + l) - 0x3f00u <= 0x4080u) keep |= 0x0000ffffu;
+    if (l + 1 < sequence && __ldg(mask_bits + token0 + l + 1) - 0x3f00u <= 0x4080u) keep |= 0xffff0000u;
+    s_keep[tid] = keep;
+  }
+#pragma unroll
+  for (int i = 0; i < kLoadsPerThread; ++i) {
+    const int idx = tid + i * kConvThreads;
+    if (idx < kChunks) {
+      uint4 v = raw[i];
+      if (m2[i] != 0x3f803f80u) {  // a mask of exactly 1 leaves the values as they are
+        v.x = mask_mul_bf16x2(v.x, m2[i]);
+        v.y = mask_mul_bf16x2(v.y, m2[i]);
+        v.z = mask_mul_bf16x2(v.z, m2[i]);
+        v.w = mask_mul_bf16x2(v.w, m2[i]);
+      }
+      reinterpret_cast<uint4*>(s_in)[idx] = v;
+    }
+  }
+
+  // ---- per-thread constants: taps and bias of this lane's channel pair ----
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+  float2 w[4], bias;
+  {
+    const int c = c0 + 2 * lane;
+    const uint4 wq = __ldg(reinterpret_cast<const uint4*>(conv_weight + static_cast<long long>(c) * kConvTaps));
+    const float2 wa01 = bf16x2_to_float2(wq.x), wa23 = bf16x2_to_float2(wq.y);  // channel c, taps 0..3
+    const float2 wb01 = bf16x2_to_float2(wq.z), wb23 = bf16x2_to_float2(wq.w);  // channel c + 1
+    w[0] = make_float2(wa01.x, wb01.x);
+    w[1] = make_float2(wa01.y, wb01.y);
+    w[2] = make_float2(wa23.x, wb23.x);
+    w[3] = make_float2(wa23.y, wb23.y);
+    bias = bf16x2_to_float2(__ldg(reinterpret_cast<const uint32_t*>(conv_bias + c)));
+  }
+  __syncthreads();
+
+  // ---- compute phase: this warp's 16 positions, two at a time ----
+  {
+    const int p0 = warp * kConvRun;
+    const uint32_t* col = s_in + lane;
+    float2 x0 = bf16x2_to_float2(col[(p0 + 0) * 32]);
+    float2 x1 = bf16x2_to_float2(col[(p0 + 1) * 32]);
+    float2 x2 = bf16x2_to_float2(col[(p0 + 2) * 32]);
+    // tile row of channel c is (c & 1) * 32 + (c >> 1): both stores of a warp then hit 32 different banks
+    uint32_t* dst_a = s_out + lane * kConvOutPitch + (p0 >> 1);
+    uint32_t* dst_b = dst_a + 32 * kConvOutPitch;
+#pragma unroll
+    for (int j = 0; j < kConvRun; j += 2) {
+      const int p = p0 + j;
+      const float2 x3 = bf16x2_to_float2(col[(p + 3) * 32]);
+      const float2 x4 = bf16x2_to_float2(col[(p + 4) * 32]);
+      const uint32_t ca = conv_pair(x0, x1, x2, x3, w, bias);  // position p, channels (c, c+1)
+      const uint32_t cb = conv_pair(x1, x2, x3, x4, w, bias);  // position p + 1
+      uint32_t sa, sb;
+      sigmoid_2x2(ca, cb, sa, sb);
+      const uint32_t ra = mul_bf16x2(ca, sa);
+      const uint32_t rb = mul_bf16x2(cb, sb);
+      const uint32_t keep = s_keep[p >> 1];
+      dst_a[j >> 1] = __byte_perm(ra, rb, 0x5410) & keep;  // channel c:     positions p, p + 1
+      dst_b[j >> 1] = __byte_perm(ra, rb, 0x7632) & keep;  // channel c + 1: positions p, p + 1
+      x0 = x2;
+      x1 = x3;
+      x2 = x4;
+    }
+  }
+  __syncthreads();
+
+  // ---- store phase: rows of the transposed tile, 128 contiguous bytes per warp instruction ----
+  const long long out_row0 = (static_cast<long long>(batch) * channels + c0) * sequence + l0;
+  if ((sequence & 1) == 0) {
+#pragma unroll 4
+    for (int idx = tid; idx < kConvChannels * (kConvPositions / 2); idx += kConvThreads) {
+      const int r = idx >> 6;
+      const int c = ((r & 31) << 1) | (r >> 5);
+      const int wd = idx & 63;
+      if (l0 + 2 * wd < sequence)
+        __stcs(reinterpret_cast<uint32_t*>(output + out_row0 + static_cast<long long>(c) * sequence) + wd,
+               s_out[r * kConvOutPitch + wd]);
+    }
+  } else {  // odd row pitch: rows are only 2-byte aligned
+    const uint16_t* s_out16 = reinterpret_cast<const uint16_t*>(s_out);
+    uint16_t* out16 = reinterpret_cast<uint16_t*>(output);
+    for (int idx = tid; idx < kConvChannels * kConvPositions; idx += kConvThreads) {
+      const int r = idx >> 7;
+      const int c = ((r & 31) << 1) | (r >> 5);
+      const int p = idx & 127;
+      if (l0 + p < sequence) out16[out_row0 + static_cast<long long>(c) * sequence + p] = s_out16[r * (2 * kConvOutPitch) + p];
+    }
+  }
+}
+
+}  // namespace so
+
+extern "C" {
+
+int so_version(void) { return 1; }
+
+const char* so_error_string(int code) {
+  switch (code) {
+    case SO_OK: return "ok";
+    case SO_EINVAL_NULL: return "a required pointer is null";
+    case SO_EINVAL_SHAPE: return "a size is outside the contract";
+    case SO_EINVAL_ALIGN: return "a pointer is not 16-byte aligned";
+    case SO_ECUDA: return "the CUDA launch failed";
+    default: return "unknown error code";
+  }
+}
+
+int64_t so_launch_count(void) { return so::g_launches.load(std::memory_order_relaxed); }
+
+int so_rmsnorm_qk(const float* query, const float* key, const float* weight_q, const float* weight_k, float eps,
+                  float* query_norm, float* key_norm, int64_t tokens, int heads, void* stream) {
+  if (!query || !key || !weight_q || !weight_k || !query_norm || !key_norm) return SO_EINVAL_NULL;
+  if (tokens < 0 || heads < 1 || tokens > (1ll << 40) / heads) return SO_EINVAL_SHAPE;
+  if (!so::aligned16(query) || !so::aligned16(key) || !so::aligned16(weight_q) || !so::aligned16(weight_k) ||
+      !so::aligned16(query_norm) || !so::aligned16(key_norm))
+    return SO_EINVAL_ALIGN;
+  if (tokens == 0) return SO_OK;
+  const long long rows = tokens * heads;
+  const long long blocks = (rows + so::kNormRowsPerBlock - 1) / so::kNormRowsPerBlock;
+  if (blocks > 0x7fffffffll) return SO_EINVAL_SHAPE;
+  const dim3 grid(static_cast<unsigned>(blocks), 2);
+  so::rmsnorm_qk_kernel<<<grid, so::kNormWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const float4*>(query), reinterpret_cast<const float4*>(key),
+      reinterpret_cast<const float4*>(weight_q), reinterpret_cast<const float4*>(weight_k), eps,
+      reinterpret_cast<float4*>(query_norm), reinterpret_cast<float4*>(key_norm), rows, heads);
+  so::g_launches.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError() == cudaSuccess ? SO_OK : SO_ECUDA;
+}
+
+int so_mamba_conv1d_tail(const void* projected, const void* attention_mask, const void* conv_weight,
+                         const void* conv_bias, void* output, int64_t batch, int64_t sequence, int64_t channels,
+                         int64_t projected_width, void* stream) {
+  if (!projected || !attention_mask || !conv_weight || !conv_bias || !output) return SO_EINVAL_NULL;
+  if (batch < 0 || sequence < 0 || channels < so::kConvChannels || channels % so::kConvChannels != 0 ||
+      projected_width < channels || projected_width % 8 != 0 || batch > 65535 || sequence > (1ll << 30) ||
+      channels > (1ll << 30))
+    return SO_EINVAL_SHAPE;
+  if (!so::aligned16(projected) || !so::aligned16(conv_weight) || (reinterpret_cast<uintptr_t>(conv_bias) & 3u) ||
+      (reinterpret_cast<uintptr_t>(attention_mask) & 1u) || (reinterpret_cast<uintptr_t>(output) & 3u))
+    return SO_EINVAL_ALIGN;
+  if (batch == 0 || sequence == 0) return SO_OK;
+  const long long seq_tiles = (sequence + so::kConvPositions - 1) / so::kConvPositions;
+  if (seq_tiles > 65535) return SO_EINVAL_SHAPE;
+  const dim3 grid(static_cast<unsigned>(channels / so::kConvChannels), static_cast<unsigned>(seq_tiles),
+                  static_cast<unsigned>(batch));
+  so::mamba_conv1d_tail_kernel<<<grid, so::kConvThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(projected), static_cast<const __nv_bfloat16*>(attention_mask),
+      static_cast<const __nv_bfloat16*>(conv_weight), static_cast<const __nv_bfloat16*>(conv_bias),
+      static_cast<__nv_bfloat16*>(output), static_cast<int>(sequence), static_cast<int>(channels), projected_width);
+  so::g_launches.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError() == cudaSuccess ? SO_OK : SO_ECUDA;
+}
+
+}  // extern "C"

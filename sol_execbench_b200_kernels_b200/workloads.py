@@ -127,3 +127,41 @@ def algorithmic_bytes(m: int, k: int, n: int) -> int:
     """Every operand touched once: X, scale_x, both W, both W scale grids, bf16 output."""
     kb, nb = k // BLOCK, n // BLOCK
     return m * k + 4 * m * kb + 2 * n * k + 8 * nb * kb + 2 * m * n
+
+
+# ---- side operators (problems 038 and 029 of the reference repository) --------------------------------------
+# Seeded synthetic inputs, drawn on the CPU so that every machine sees the same bits.
+
+RMSNORM_SHAPES = {  # name -> (tokens, heads); head width is 128
+    "flux_128": (128, 48), "flux_2048": (2048, 48), "flux_4608": (4608, 48), "flux_16384": (16384, 48),
+}
+MAMBA_TAIL_SHAPES = {  # name -> (batch, sequence, channels, projected width)
+    "mamba_b1_l128": (1, 128, 16384, 32768), "mamba_b4_l2048": (4, 2048, 16384, 32768),
+}
+
+
+def make_rmsnorm_inputs(tokens: int, heads: int, seed: int = 0, device="cpu"):
+    """(query, key, weight_q, weight_k, eps): fp32 [1, tokens, heads, 128] x2, [heads, 128] x2."""
+    g = torch.Generator().manual_seed(seed)
+    query = torch.randn(1, tokens, heads, 128, generator=g) * 1.5
+    key = torch.randn(1, tokens, heads, 128, generator=g) * 0.7 + 0.1
+    weight_q = 1.0 + 0.1 * torch.randn(heads, 128, generator=g)
+    weight_k = 1.0 + 0.1 * torch.randn(heads, 128, generator=g)
+    return query.to(device), key.to(device), weight_q.to(device), weight_k.to(device), 1e-6
+
+
+def make_mamba_tail_inputs(batch: int, sequence: int, channels: int, width: int, seed: int = 0, device="cpu",
+                           padded: bool = True):
+    """(projected, attention_mask, conv1d_weight, conv1d_bias), all bf16.  With `padded`, every batch row but
+    the first has a run of masked positions at its start and a few inside (left padding plus holes)."""
+    g = torch.Generator().manual_seed(seed)
+    projected = (torch.randn(batch, sequence, width, generator=g) * 2.0).to(torch.bfloat16)
+    mask = torch.ones(batch, sequence)
+    if padded:
+        for b in range(1, batch):
+            mask[b, : (b * 37) % max(1, sequence // 2)] = 0.0
+        holes = torch.rand(batch, sequence, generator=g) < 0.02
+        mask[holes] = 0.0
+    conv_w = (torch.randn(channels, 1, 4, generator=g) * 0.5).to(torch.bfloat16)
+    conv_b = (torch.randn(channels, generator=g) * 0.5).to(torch.bfloat16)
+    return projected.to(device), mask.to(torch.bfloat16).to(device), conv_w.to(device), conv_b.to(device)

@@ -1,0 +1,144 @@
+"""Checks of the side operators (problems 038 and 029) that need no GPU: the library loads and exports what
+include/sideops.h declares, the host mirror rejects contract violations before any launch, and the CPU
+restatement agrees with the fixtures made from the reference's own kernels and with independent formulations."""
+import glob
+import json
+import os
+import re
+
+import pytest
+import torch
+
+from oracle import sideops_oracle as O
+from sol_execbench_b200_kernels_b200 import workloads as W
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+GOLDEN = os.path.join(ROOT, "tests", "golden")
+
+
+@pytest.fixture(scope="module")
+def so():
+    from sol_execbench_b200_kernels_b200 import build
+    build.build()
+    from sol_execbench_b200_kernels_b200 import _sideops_cabi
+    return _sideops_cabi
+
+
+def test_header_symbols_all_exported(so):
+    text = open(os.path.join(ROOT, "include", "sideops.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    declared = sorted(set(re.findall(r"\b(so_[a-z0-9_]+)\s*\(", text)))
+    assert declared == sorted(so.EXPORTS)
+    for name in declared:
+        assert hasattr(so.lib, name)
+    assert so.lib.so_version() >= 1
+    assert so.error_string(0) == "ok" and "null" in so.error_string(so.SO_EINVAL_NULL)
+
+
+def test_c_abi_rejects_bad_arguments_before_any_cuda_call(so):
+    f = so.lib.so_rmsnorm_qk
+    assert f(None, 16, 16, 16, 1e-6, 16, 16, 4, 48, None) == so.SO_EINVAL_NULL
+    assert f(16, 16, 16, 16, 1e-6, 16, 16, 4, 0, None) == so.SO_EINVAL_SHAPE
+    assert f(16, 16, 8, 16, 1e-6, 16, 16, 4, 48, None) == so.SO_EINVAL_ALIGN
+    assert f(16, 16, 16, 16, 1e-6, 16, 16, 0, 48, None) == so.SO_OK          # empty input: nothing to launch
+    g = so.lib.so_mamba_conv1d_tail
+    assert g(16, 16, 16, 16, None, 1, 8, 64, 64, None) == so.SO_EINVAL_NULL
+    assert g(16, 16, 16, 16, 16, 1, 8, 96, 128, None) == so.SO_EINVAL_SHAPE   # channels not a multiple of 64
+    assert g(16, 16, 16, 16, 16, 1, 8, 128, 64, None) == so.SO_EINVAL_SHAPE   # narrower than the channels
+    assert g(8, 16, 16, 16, 16, 1, 8, 64, 64, None) == so.SO_EINVAL_ALIGN
+    assert g(16, 16, 16, 16, 16, 0, 8, 64, 64, None) == so.SO_OK
+    assert so.lib.so_launch_count() == 0
+
+
+def test_host_mirror_validates_like_the_reference_binding(so):
+    from sol_execbench_b200_kernels_b200 import side_ops
+    q, k, wq, wk, eps = W.make_rmsnorm_inputs(4, 48)
+    with pytest.raises(ValueError, match="CUDA"):
+        side_ops.rmsnorm_qk(q, k, wq, wk, eps, torch.empty_like(q), torch.empty_like(k))
+    with pytest.raises(ValueError, match="shapes must match"):
+        side_ops.rmsnorm_qk(q, k[:, :2], wq, wk, eps, torch.empty_like(q), torch.empty_like(k))
+    with pytest.raises(ValueError, match="weight_q"):
+        side_ops.rmsnorm_qk(q, k, wq[:10], wk, eps, torch.empty_like(q), torch.empty_like(k))
+    with pytest.raises(ValueError, match="float32"):
+        side_ops.rmsnorm_qk(q.half(), k.half(), wq, wk, eps, torch.empty_like(q), torch.empty_like(k))
+    p, m, cw, cb = W.make_mamba_tail_inputs(1, 8, 64, 128)
+    out = torch.empty(1, 64, 8, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="CUDA"):
+        side_ops.mamba_conv1d_tail(p, m, cw, cb, out)
+    with pytest.raises(ValueError, match="attention_mask"):
+        side_ops.mamba_conv1d_tail(p, m[:, :4], cw, cb, out)
+    with pytest.raises(ValueError, match="output_hidden_states"):
+        side_ops.mamba_conv1d_tail(p, m, cw, cb, out.transpose(1, 2))
+    with pytest.raises(ValueError, match="bfloat16"):
+        side_ops.mamba_conv1d_tail(p.float(), m, cw, cb, out)
+
+
+def test_rmsnorm_oracle_properties():
+    q, k, wq, wk, eps = W.make_rmsnorm_inputs(9, 48, seed=2)
+    a, b = O.rmsnorm_qk(q, k, wq, wk, 0.0)
+    # with unit weights every row has unit mean square; scaling the input leaves the result unchanged
+    ones = torch.ones_like(wq)
+    u, _ = O.rmsnorm_qk(q, k, ones, ones, 0.0)
+    torch.testing.assert_close(u.pow(2).mean(-1), torch.ones(1, 9, 48), rtol=1e-5, atol=1e-5)
+    a4, _ = O.rmsnorm_qk(q * 4.0, k, wq, wk, 0.0)
+    torch.testing.assert_close(a4, a, rtol=1e-6, atol=1e-6)
+    d = q.double()
+    want = (d / d.pow(2).mean(-1, keepdim=True).sqrt() * wq.double()).float()
+    torch.testing.assert_close(a, want, rtol=2e-6, atol=2e-6)
+
+
+def test_mamba_tail_oracle_properties():
+    p, m, cw, cb = W.make_mamba_tail_inputs(3, 50, 64, 128, seed=4)
+    out = O.mamba_conv1d_tail(p, m, cw, cb)
+    assert out.shape == (3, 64, 50) and out.dtype == torch.bfloat16
+    masked = (m < 0.5)[:, None, :].expand_as(out)
+    assert masked.any() and bool((out[masked] == 0).all())
+    # causal: changing positions >= 30 leaves outputs < 30 untouched
+    p2 = p.clone()
+    p2[:, 30:] = 1.0
+    assert torch.equal(O.mamba_conv1d_tail(p2, m, cw, cb)[:, :, :30], out[:, :, :30])
+    # the gate half of the projection is never read
+    p3 = p.clone()
+    p3[:, :, 64:] = 7.0
+    assert torch.equal(O.mamba_conv1d_tail(p3, m, cw, cb), out)
+    # independent formulation: grouped conv1d in float64 on the masked input, same rounding boundaries
+    x = (p[:, :, :64].float() * m.float()[:, :, None]).bfloat16().double().transpose(1, 2)
+    conv = torch.nn.functional.conv1d(torch.nn.functional.pad(x, (3, 0)), cw.double(), cb.double(), groups=64)
+    conv = conv.float().bfloat16()
+    act = (conv.float() * torch.sigmoid(conv.float()).bfloat16().float()).bfloat16()
+    want = torch.where((m >= 0.5)[:, None, :], act, torch.zeros((), dtype=torch.bfloat16))
+    assert int((want != out).sum()) <= 2      # fp64 vs fp32 accumulation may flip a rounding, rarely
+
+
+def _fixtures(prefix):
+    return sorted(glob.glob(os.path.join(GOLDEN, prefix + "*.json")))
+
+
+def test_rmsnorm_oracle_against_reference_kernel_outputs():
+    files = _fixtures("ref038_")
+    assert files, "fixtures of problem 038 are missing"
+    for jf in files:
+        meta = json.load(open(jf))
+        ref = torch.load(jf[:-5] + ".pt")
+        q, k, wq, wk, eps = W.make_rmsnorm_inputs(meta["tokens"], meta["heads"], meta["seed"])
+        a, b = O.rmsnorm_qk(q, k, wq, wk, eps)
+        rs = meta["row_stride"]
+        # fp32, different sum order and an approximate rsqrt in the reference: relative 4e-6
+        torch.testing.assert_close(a[0, ::rs], ref["query_norm"], rtol=4e-6, atol=4e-6)
+        torch.testing.assert_close(b[0, ::rs], ref["key_norm"], rtol=4e-6, atol=4e-6)
+
+
+def test_mamba_tail_oracle_against_reference_kernel_outputs():
+    files = _fixtures("ref029_")
+    assert files, "fixtures of problem 029 are missing"
+    for jf in files:
+        ref = torch.load(jf[:-5] + ".pt")
+        want = ref["output"]
+        got = O.mamba_conv1d_tail(ref["projected_x"], ref["mask"], ref["conv_w"], ref["conv_b"])
+        assert got.shape == want.shape
+        diff = (got.float() - want.float()).abs()
+        bad = diff > 0
+        # the reference evaluates the sigmoid with fast-math exp and division: a rounding to bf16 may fall the
+        # other way on a few elements, by one bf16 step of the result
+        assert int(bad.sum()) <= max(2, 2e-3 * want.numel()), f"{jf}: {int(bad.sum())} mismatches"
+        assert bool((diff[bad] <= want.float().abs()[bad] * 2.0 ** -6 + 1e-30).all())
