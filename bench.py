@@ -508,6 +508,42 @@ def run_mlp(args):
     dist.destroy_process_group()
 
 
+def run_side(args):
+    """The two HBM-bound side operators (per-head RMSNorm of query / key; Mamba conv1d tail) on one GPU:
+    CUDA-event time per launch with L2 flushed, achieved algorithmic GB/s against the measured copy bandwidth.
+    A study line, not the headline metric."""
+    from sol_execbench_b200_kernels_b200 import side_ops
+    from sol_execbench_b200_kernels_b200 import workloads as W
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peaks = load_peaks()
+    flush = torch.empty(L2_FLUSH_BYTES // 4, dtype=torch.float32, device=dev)
+    rows = {}
+    for name, (tokens, heads) in W.RMSNORM_SHAPES.items():
+        if args.workload and args.workload != name:
+            continue
+        q, k, wq, wk, eps = W.make_rmsnorm_inputs(tokens, heads, 0, dev)
+        qn, kn = torch.empty_like(q), torch.empty_like(k)
+        total, _ = time_device_steps(lambda: side_ops.rmsnorm_qk(q, k, wq, wk, eps, qn, kn), args.steps, args.warmup, flush)
+        nbytes = 4 * q.numel() * 4          # two tensors, read and written once, fp32
+        rows[name] = (total / args.steps, nbytes)
+    for name, (b, l, c, w) in W.MAMBA_TAIL_SHAPES.items():
+        if args.workload and args.workload != name:
+            continue
+        p, mask, cw, cb = W.make_mamba_tail_inputs(b, l, c, w, 0, dev)
+        out = torch.empty(b, c, l, dtype=torch.bfloat16, device=dev)
+        total, _ = time_device_steps(lambda: side_ops.mamba_conv1d_tail(p, mask, cw, cb, out), args.steps, args.warmup, flush)
+        nbytes = 2 * b * l * c * 2          # the convolved half read once, the result written once, bf16
+        rows[name] = (total / args.steps, nbytes)
+    src = "of measured" if peaks["_source"] == "measured" else "of fallback"
+    print(json.dumps({
+        "study": "side operators", "steps": args.steps, "warmup": args.warmup, "peak_gbs": peaks["hbm_gbs"],
+        "peak_source": f"hbm_gbs, {src}", "gpu_launches": side_ops.launch_count(),
+        "rows": {k: {"us": round(ms * 1e3, 2), "algorithmic_bytes": nb, "gbs": round(nb / ms / 1e6, 1),
+                     "frac": round(nb / ms / 1e6 / peaks["hbm_gbs"], 4)} for k, (ms, nb) in rows.items()}}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -520,6 +556,8 @@ def main():
                     help="N>1: contiguous [M, N] output on every rank through peer stores in the kernel epilogue")
     ap.add_argument("--mlp", action="store_true",
                     help="N>1: tensor-parallel MLP block, NCCL all-reduce against the fused peer-store reduction")
+    ap.add_argument("--side", action="store_true",
+                    help="one GPU: the side operators (RMSNorm of query/key, Mamba conv1d tail) against the HBM roofline")
     ap.add_argument("--sweep", action="store_true", help="M sweep at K=4096, N=14336 on one GPU (plan crossover study)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -527,6 +565,8 @@ def main():
         run_reference(args)
     elif args.mlp:
         run_mlp(args)
+    elif args.side:
+        run_side(args)
     elif args.sweep:
         run_sweep(args)
     else:

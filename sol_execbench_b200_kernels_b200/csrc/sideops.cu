@@ -147,37 +147,23 @@ __device__ __noinline__ float sigmoid_wide(float x) {
   return x < 0.f ? e * r : r;
 }
 
-// bf16(sigmoid) of the four bf16 values in two packed words (channel pair at two positions).
-// Common case (all four arguments >= -20): sigmoid = 1 / (1 + 2^(-x log2 e)) directly; each denominator is
-// below 2^30, so the product of the four stays finite and ONE reciprocal of it serves all four (products of the
-// other three give each quotient back): 1.25 special-function operations per element instead of 2.  Below -20
-// the rounding of the exponent's argument would show in the bf16 result, and the product could overflow: those
-// (rare) blocks take sigmoid_wide.
+// bf16(sigmoid) of the four bf16 values in two packed words (channel pair at two positions), all four
+// arguments >= -20: sigmoid = 1 / (1 + 2^(-x log2 e)) directly; each denominator is below 2^30, so the product of
+// the four stays finite and ONE reciprocal of it serves all four (products of the other three give each quotient
+// back): 1.25 special-function operations per element instead of 2.
 __device__ __forceinline__ void sigmoid_2x2(uint32_t ca, uint32_t cb, uint32_t& sa, uint32_t& sb) {
   constexpr float kNegLog2e = -1.4426950408889634f;
-  const float2 xa = bf16x2_to_float2(ca);
-  const float2 xb = bf16x2_to_float2(cb);
-  const __nv_bfloat162 lowest = __hmin2(*reinterpret_cast<const __nv_bfloat162*>(&ca),
-                                        *reinterpret_cast<const __nv_bfloat162*>(&cb));
-  float2 ra, rb;
-  if (__hbge2(lowest, __floats2bfloat162_rn(-20.f, -20.f))) {
-    const float2 scale = make_float2(kNegLog2e, kNegLog2e);
-    const float2 ta = __fmul2_rn(xa, scale);
-    const float2 tb = __fmul2_rn(xb, scale);
-    const float2 one = make_float2(1.f, 1.f);
-    const float2 ya = __fadd2_rn(make_float2(ex2_approx(ta.x), ex2_approx(ta.y)), one);
-    const float2 yb = __fadd2_rn(make_float2(ex2_approx(tb.x), ex2_approx(tb.y)), one);
-    const float2 pab = __fmul2_rn(ya, yb);        // (ya.x*yb.x, ya.y*yb.y)
-    const float inv = rcp_approx(pab.x * pab.y);  // 1 / (all four)
-    const float2 rab = make_float2(inv * pab.y, inv * pab.x);  // 1/(ya.x*yb.x), 1/(ya.y*yb.y)
-    ra = __fmul2_rn(rab, yb);                     // 1/ya
-    rb = __fmul2_rn(rab, ya);                     // 1/yb
-  } else {  // also taken for a NaN
-    ra = make_float2(sigmoid_wide(xa.x), sigmoid_wide(xa.y));
-    rb = make_float2(sigmoid_wide(xb.x), sigmoid_wide(xb.y));
-  }
-  sa = float2_to_bf16x2(ra);
-  sb = float2_to_bf16x2(rb);
+  const float2 scale = make_float2(kNegLog2e, kNegLog2e);
+  const float2 ta = __fmul2_rn(bf16x2_to_float2(ca), scale);
+  const float2 tb = __fmul2_rn(bf16x2_to_float2(cb), scale);
+  const float2 one = make_float2(1.f, 1.f);
+  const float2 ya = __fadd2_rn(make_float2(ex2_approx(ta.x), ex2_approx(ta.y)), one);
+  const float2 yb = __fadd2_rn(make_float2(ex2_approx(tb.x), ex2_approx(tb.y)), one);
+  const float2 pab = __fmul2_rn(ya, yb);        // (ya.x*yb.x, ya.y*yb.y)
+  const float inv = rcp_approx(pab.x * pab.y);  // 1 / (all four)
+  const float2 rab = make_float2(inv * pab.y, inv * pab.x);  // 1/(ya.x*yb.x), 1/(ya.y*yb.y)
+  sa = float2_to_bf16x2(__fmul2_rn(rab, yb));   // 1/ya
+  sb = float2_to_bf16x2(__fmul2_rn(rab, ya));   // 1/yb
 }
 
 __global__ void __launch_bounds__(kConvThreads)
@@ -193,39 +179,42 @@ mamba_conv1d_tail_kernel(const __nv_bfloat16* __restrict__ projected, const __nv
   const int c0 = blockIdx.x * kConvChannels;
   const int l0 = blockIdx.y * kConvPositions;
   const long long token0 = static_cast<long long>(batch) * sequence;
-  const uint16_t* mask_bits = reinterpret_cast<const uint16_t*>(mask);
+  const uint16_t* mask_bits = reinterpret_cast<const uint16_t*>(mask) + token0;
 
-  // ---- load phase: 131 rows x 8 chunks of 16 bytes; all global loads of a thread are issued first ----
-  constexpr int kChunks = kConvRows * (kConvChannels / 8);                   // 1048
-  constexpr int kLoadsPerThread = (kChunks + kConvThreads - 1) / kConvThreads;  // 5
+  // ---- load phase: 131 rows x 8 chunks of 16 bytes.  Thread t owns chunk t % 8 of rows t / 8 + 32 i, so its
+  // addresses advance by a constant; all of its global loads are issued before the first use ----
+  constexpr int kLoadsPerThread = (kConvRows + 31) / 32;  // 5; the last round has 3 rows
+  const int l_first = l0 + (tid >> 3) - (kConvTaps - 1);
   uint4 raw[kLoadsPerThread];
   uint32_t m2[kLoadsPerThread];
+  {
+    const uint4* src = reinterpret_cast<const uint4*>(projected + token0 * width + c0) + (tid & 7);
+    const long long row_pitch = width >> 3;  // 16-byte words per token row
+    long long off = static_cast<long long>(l_first) * row_pitch;
 #pragma unroll
-  for (int i = 0; i < kLoadsPerThread; ++i) {
-    const int idx = tid + i * kConvThreads;
-    const int row = idx >> 3;
-    const int l = l0 + row - (kConvTaps - 1);
-    raw[i] = make_uint4(0u, 0u, 0u, 0u);
-    m2[i] = 0u;
-    if (idx < kChunks && l >= 0 && l < sequence) {
-      const long long token = token0 + l;
-      raw[i] = __ldcs(reinterpret_cast<const uint4*>(projected + token * width + c0) + (idx & 7));
-      const uint32_t mb = __ldg(mask_bits + token);
-      m2[i] = mb | (mb << 16);
+    for (int i = 0; i < kLoadsPerThread; ++i) {
+      const int l = l_first + 32 * i;
+      raw[i] = make_uint4(0u, 0u, 0u, 0u);
+      m2[i] = 0u;
+      if ((i < kLoadsPerThread - 1 || tid < 8 * (kConvRows - 32 * (kLoadsPerThread - 1))) && l >= 0 && l < sequence) {
+        raw[i] = __ldcs(src + off);
+        const uint32_t mb = __ldg(mask_bits + l);
+        m2[i] = mb | (mb << 16);
+      }
+      off += 32 * row_pitch;
     }
   }
   if (tid < kConvPositions / 2) {
     // the reference keeps an output only where the mask is at least one half (bf16 bits 0x3f00 .. 0x7f80)
     uint32_t keep = 0u;
     const int l = l0 + 2 * tid;
-    if (l < sequence && __ldg(mask_bits + token0 + l) - 0x3f00u <= 0x4080u) keep |= 0x0000ffffu;
-    if (l + 1 < sequence && __ldg(mask_bits + token0 + l + 1) - 0x3f00u <= 0x4080u) keep |= 0xffff0000u;
+    if (l < sequence && __ldg(mask_bits + l) - 0x3f00u <= 0x4080u) keep |= 0x0000ffffu;
+    if (l + 1 < sequence && __ldg(mask_bits + l + 1) - 0x3f00u <= 0x4080u) keep |= 0xffff0000u;
     s_keep[tid] = keep;
   }
 #pragma unroll
   for (int i = 0; i < kLoadsPerThread; ++i) {
-    const int idx = tid + i * kConvThreads;
-    if (idx < kChunks) {
+    if (i < kLoadsPerThread - 1 || tid < 8 * (kConvRows - 32 * (kLoadsPerThread - 1))) {
       uint4 v = raw[i];
       if (m2[i] != 0x3f803f80u) {  // a mask of exactly 1 leaves the values as they are
         v.x = mask_mul_bf16x2(v.x, m2[i]);
@@ -233,7 +222,7 @@ mamba_conv1d_tail_kernel(const __nv_bfloat16* __restrict__ projected, const __nv
         v.z = mask_mul_bf16x2(v.z, m2[i]);
         v.w = mask_mul_bf16x2(v.w, m2[i]);
       }
-      reinterpret_cast<uint4*>(s_in)[idx] = v;
+      reinterpret_cast<uint4*>(s_in)[tid + i * kConvThreads] = v;
     }
   }
 
@@ -254,33 +243,52 @@ mamba_conv1d_tail_kernel(const __nv_bfloat16* __restrict__ projected, const __nv
   }
   __syncthreads();
 
-  // ---- compute phase: this warp's 16 positions, two at a time ----
+  // ---- compute phase: this warp's 16 positions.  First all convolutions (sliding window), then one test
+  // whether every result allows the short sigmoid, then sigmoid and product two positions at a time ----
   {
     const int p0 = warp * kConvRun;
-    const uint32_t* col = s_in + lane;
-    float2 x0 = bf16x2_to_float2(col[(p0 + 0) * 32]);
-    float2 x1 = bf16x2_to_float2(col[(p0 + 1) * 32]);
-    float2 x2 = bf16x2_to_float2(col[(p0 + 2) * 32]);
+    const uint32_t* col = s_in + p0 * 32 + lane;
+    uint32_t conv[kConvRun];
+    float2 x0 = bf16x2_to_float2(col[0 * 32]);
+    float2 x1 = bf16x2_to_float2(col[1 * 32]);
+    float2 x2 = bf16x2_to_float2(col[2 * 32]);
+#pragma unroll
+    for (int j = 0; j < kConvRun; ++j) {
+      const float2 x3 = bf16x2_to_float2(col[(j + 3) * 32]);
+      conv[j] = conv_pair(x0, x1, x2, x3, w, bias);  // position p0 + j, channels (c, c + 1)
+      x0 = x1;
+      x1 = x2;
+      x2 = x3;
+    }
+    __nv_bfloat162 lowest = *reinterpret_cast<const __nv_bfloat162*>(&conv[0]);
+#pragma unroll
+    for (int j = 1; j < kConvRun; ++j) lowest = __hmin2(lowest, *reinterpret_cast<const __nv_bfloat162*>(&conv[j]));
     // tile row of channel c is (c & 1) * 32 + (c >> 1): both stores of a warp then hit 32 different banks
     uint32_t* dst_a = s_out + lane * kConvOutPitch + (p0 >> 1);
     uint32_t* dst_b = dst_a + 32 * kConvOutPitch;
+    const uint32_t* keep = s_keep + (p0 >> 1);
+    if (__hbge2(lowest, __floats2bfloat162_rn(-20.f, -20.f))) {
 #pragma unroll
-    for (int j = 0; j < kConvRun; j += 2) {
-      const int p = p0 + j;
-      const float2 x3 = bf16x2_to_float2(col[(p + 3) * 32]);
-      const float2 x4 = bf16x2_to_float2(col[(p + 4) * 32]);
-      const uint32_t ca = conv_pair(x0, x1, x2, x3, w, bias);  // position p, channels (c, c+1)
-      const uint32_t cb = conv_pair(x1, x2, x3, x4, w, bias);  // position p + 1
-      uint32_t sa, sb;
-      sigmoid_2x2(ca, cb, sa, sb);
-      const uint32_t ra = mul_bf16x2(ca, sa);
-      const uint32_t rb = mul_bf16x2(cb, sb);
-      const uint32_t keep = s_keep[p >> 1];
-      dst_a[j >> 1] = __byte_perm(ra, rb, 0x5410) & keep;  // channel c:     positions p, p + 1
-      dst_b[j >> 1] = __byte_perm(ra, rb, 0x7632) & keep;  // channel c + 1: positions p, p + 1
-      x0 = x2;
-      x1 = x3;
-      x2 = x4;
+      for (int j = 0; j < kConvRun; j += 2) {
+        uint32_t sa, sb;
+        sigmoid_2x2(conv[j], conv[j + 1], sa, sb);
+        const uint32_t ra = mul_bf16x2(conv[j], sa);
+        const uint32_t rb = mul_bf16x2(conv[j + 1], sb);
+        dst_a[j >> 1] = __byte_perm(ra, rb, 0x5410) & keep[j >> 1];  // channel c:     positions p, p + 1
+        dst_b[j >> 1] = __byte_perm(ra, rb, 0x7632) & keep[j >> 1];  // channel c + 1: positions p, p + 1
+      }
+    } else {  // some result below -20 (or a NaN): the wide-range sigmoid for the whole run, rare
+#pragma unroll  // unrolled although cold: a run-time index would move conv[] to local memory for both branches
+      for (int j = 0; j < kConvRun; j += 2) {
+        const float2 xa = bf16x2_to_float2(conv[j]);
+        const float2 xb = bf16x2_to_float2(conv[j + 1]);
+        const uint32_t sa = float2_to_bf16x2(make_float2(sigmoid_wide(xa.x), sigmoid_wide(xa.y)));
+        const uint32_t sb = float2_to_bf16x2(make_float2(sigmoid_wide(xb.x), sigmoid_wide(xb.y)));
+        const uint32_t ra = mul_bf16x2(conv[j], sa);
+        const uint32_t rb = mul_bf16x2(conv[j + 1], sb);
+        dst_a[j >> 1] = __byte_perm(ra, rb, 0x5410) & keep[j >> 1];
+        dst_b[j >> 1] = __byte_perm(ra, rb, 0x7632) & keep[j >> 1];
+      }
     }
   }
   __syncthreads();
@@ -288,14 +296,19 @@ mamba_conv1d_tail_kernel(const __nv_bfloat16* __restrict__ projected, const __nv
   // ---- store phase: rows of the transposed tile, 128 contiguous bytes per warp instruction ----
   const long long out_row0 = (static_cast<long long>(batch) * channels + c0) * sequence + l0;
   if ((sequence & 1) == 0) {
-#pragma unroll 4
-    for (int idx = tid; idx < kConvChannels * (kConvPositions / 2); idx += kConvThreads) {
-      const int r = idx >> 6;
-      const int c = ((r & 31) << 1) | (r >> 5);
-      const int wd = idx & 63;
-      if (l0 + 2 * wd < sequence)
-        __stcs(reinterpret_cast<uint32_t*>(output + out_row0 + static_cast<long long>(c) * sequence) + wd,
-               s_out[r * kConvOutPitch + wd]);
+    // thread t owns word t % 64 of tile rows t / 64 + 4 i: rows 0..31 are the even channels, 32..63 the odd ones
+    const int wd = tid & 63;
+    const int r0 = tid >> 6;
+    if (l0 + 2 * wd < sequence) {
+      const long long row_words = sequence >> 1;
+      uint32_t* dst = reinterpret_cast<uint32_t*>(output + out_row0) + 2 * r0 * row_words + wd;
+      const uint32_t* src = s_out + r0 * kConvOutPitch + wd;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        __stcs(dst, src[4 * i * kConvOutPitch]);                      // channel 2 (r0 + 4 i)
+        __stcs(dst + row_words, src[(32 + 4 * i) * kConvOutPitch]);   // channel 2 (r0 + 4 i) + 1
+        dst += 8 * row_words;
+      }
     }
   } else {  // odd row pitch: rows are only 2-byte aligned
     const uint16_t* s_out16 = reinterpret_cast<const uint16_t*>(s_out);

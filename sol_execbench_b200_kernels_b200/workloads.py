@@ -136,7 +136,8 @@ RMSNORM_SHAPES = {  # name -> (tokens, heads); head width is 128
     "flux_128": (128, 48), "flux_2048": (2048, 48), "flux_4608": (4608, 48), "flux_16384": (16384, 48),
 }
 MAMBA_TAIL_SHAPES = {  # name -> (batch, sequence, channels, projected width)
-    "mamba_b1_l128": (1, 128, 16384, 32768), "mamba_b4_l2048": (4, 2048, 16384, 32768),
+    "mamba_b1_l128": (1, 128, 16384, 32768), "mamba_b1_l2048": (1, 2048, 16384, 32768),
+    "mamba_b4_l2048": (4, 2048, 16384, 32768),
 }
 
 
