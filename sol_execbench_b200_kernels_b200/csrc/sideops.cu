@@ -44,7 +44,17 @@ rmsnorm_qk_kernel(const float4* __restrict__ query, const float4* __restrict__ k
 #pragma unroll
   for (int i = 0; i < kNormRowsPerWarp; ++i) {
     v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (row0 + i < rows) v[i] = __ldcs(in + (row0 + i) * 32 + lane);
+    if (row0 + i < rows) v[i] = __ldg(in + (row0 + i) * 32 + lane);
+  }
+  // the weight rows are fetched before the reduction so that their latency hides behind it
+  float4 wv[kNormRowsPerWarp];
+  {
+    int head = static_cast<int>(row0 % heads);
+#pragma unroll
+    for (int i = 0; i < kNormRowsPerWarp; ++i) {
+      wv[i] = __ldg(weight + head * 32 + lane);
+      if (++head == heads) head = 0;
+    }
   }
 #pragma unroll
   for (int i = 0; i < kNormRowsPerWarp; ++i)
@@ -54,20 +64,18 @@ rmsnorm_qk_kernel(const float4* __restrict__ query, const float4* __restrict__ k
 #pragma unroll
     for (int i = 0; i < kNormRowsPerWarp; ++i) sum[i] += __shfl_xor_sync(0xffffffffu, sum[i], offset);
   }
-  int head = static_cast<int>(row0 % heads);
 #pragma unroll
   for (int i = 0; i < kNormRowsPerWarp; ++i) {
     if (row0 + i < rows) {
-      const float4 w = __ldg(weight + head * 32 + lane);
+      const float4 w = wv[i];
       const float s = rsqrtf(fmaf(sum[i], 1.0f / 128.0f, eps));
       float4 r;
       r.x = (v[i].x * s) * w.x;
       r.y = (v[i].y * s) * w.y;
       r.z = (v[i].z * s) * w.z;
       r.w = (v[i].w * s) * w.w;
-      __stcs(out + (row0 + i) * 32 + lane, r);
+      out[(row0 + i) * 32 + lane] = r;  // default policy: the consumer of the normalised tensors reads them next
     }
-    if (++head == heads) head = 0;
   }
 }
 
@@ -166,7 +174,7 @@ __device__ __forceinline__ void sigmoid_2x2(uint32_t ca, uint32_t cb, uint32_t& 
   sb = float2_to_bf16x2(__fmul2_rn(rab, ya));   // 1/yb
 }
 
-__global__ void __launch_bounds__(kConvThreads)
+__global__ void __launch_bounds__(kConvThreads, 6)  // 6 CTAs of 33 KiB per SM: the phases of one overlap the others'
 mamba_conv1d_tail_kernel(const __nv_bfloat16* __restrict__ projected, const __nv_bfloat16* __restrict__ mask,
                          const __nv_bfloat16* __restrict__ conv_weight, const __nv_bfloat16* __restrict__ conv_bias,
                          __nv_bfloat16* __restrict__ output, int sequence, int channels, long long width) {
@@ -243,51 +251,57 @@ mamba_conv1d_tail_kernel(const __nv_bfloat16* __restrict__ projected, const __nv
   }
   __syncthreads();
 
-  // ---- compute phase: this warp's 16 positions.  First all convolutions (sliding window), then one test
-  // whether every result allows the short sigmoid, then sigmoid and product two positions at a time ----
+  // ---- compute phase: this warp's 16 positions in two halves.  Per half: all convolutions (sliding window),
+  // one test whether every result allows the short sigmoid, then sigmoid and product two positions at a time ----
   {
+    constexpr int kHalf = kConvRun / 2;
     const int p0 = warp * kConvRun;
     const uint32_t* col = s_in + p0 * 32 + lane;
-    uint32_t conv[kConvRun];
-    float2 x0 = bf16x2_to_float2(col[0 * 32]);
-    float2 x1 = bf16x2_to_float2(col[1 * 32]);
-    float2 x2 = bf16x2_to_float2(col[2 * 32]);
-#pragma unroll
-    for (int j = 0; j < kConvRun; ++j) {
-      const float2 x3 = bf16x2_to_float2(col[(j + 3) * 32]);
-      conv[j] = conv_pair(x0, x1, x2, x3, w, bias);  // position p0 + j, channels (c, c + 1)
-      x0 = x1;
-      x1 = x2;
-      x2 = x3;
-    }
-    __nv_bfloat162 lowest = *reinterpret_cast<const __nv_bfloat162*>(&conv[0]);
-#pragma unroll
-    for (int j = 1; j < kConvRun; ++j) lowest = __hmin2(lowest, *reinterpret_cast<const __nv_bfloat162*>(&conv[j]));
     // tile row of channel c is (c & 1) * 32 + (c >> 1): both stores of a warp then hit 32 different banks
     uint32_t* dst_a = s_out + lane * kConvOutPitch + (p0 >> 1);
     uint32_t* dst_b = dst_a + 32 * kConvOutPitch;
     const uint32_t* keep = s_keep + (p0 >> 1);
-    if (__hbge2(lowest, __floats2bfloat162_rn(-20.f, -20.f))) {
+    float2 x0 = bf16x2_to_float2(col[0 * 32]);
+    float2 x1 = bf16x2_to_float2(col[1 * 32]);
+    float2 x2 = bf16x2_to_float2(col[2 * 32]);
 #pragma unroll
-      for (int j = 0; j < kConvRun; j += 2) {
-        uint32_t sa, sb;
-        sigmoid_2x2(conv[j], conv[j + 1], sa, sb);
-        const uint32_t ra = mul_bf16x2(conv[j], sa);
-        const uint32_t rb = mul_bf16x2(conv[j + 1], sb);
-        dst_a[j >> 1] = __byte_perm(ra, rb, 0x5410) & keep[j >> 1];  // channel c:     positions p, p + 1
-        dst_b[j >> 1] = __byte_perm(ra, rb, 0x7632) & keep[j >> 1];  // channel c + 1: positions p, p + 1
+    for (int h = 0; h < kConvRun; h += kHalf) {
+      uint32_t conv[kHalf];
+#pragma unroll
+      for (int j = 0; j < kHalf; ++j) {
+        const float2 x3 = bf16x2_to_float2(col[(h + j + 3) * 32]);
+        conv[j] = conv_pair(x0, x1, x2, x3, w, bias);  // position p0 + h + j, channels (c, c + 1)
+        x0 = x1;
+        x1 = x2;
+        x2 = x3;
       }
-    } else {  // some result below -20 (or a NaN): the wide-range sigmoid for the whole run, rare
+      __nv_bfloat162 lowest = *reinterpret_cast<const __nv_bfloat162*>(&conv[0]);
+#pragma unroll
+      for (int j = 1; j < kHalf; ++j) lowest = __hmin2(lowest, *reinterpret_cast<const __nv_bfloat162*>(&conv[j]));
+      if (__hbge2(lowest, __floats2bfloat162_rn(-20.f, -20.f))) {
+#pragma unroll
+        for (int j = 0; j < kHalf; j += 2) {
+          uint32_t sa, sb;
+          sigmoid_2x2(conv[j], conv[j + 1], sa, sb);
+          const uint32_t ra = mul_bf16x2(conv[j], sa);
+          const uint32_t rb = mul_bf16x2(conv[j + 1], sb);
+          const uint32_t k2 = keep[(h + j) >> 1];
+          dst_a[(h + j) >> 1] = __byte_perm(ra, rb, 0x5410) & k2;  // channel c:     positions p, p + 1
+          dst_b[(h + j) >> 1] = __byte_perm(ra, rb, 0x7632) & k2;  // channel c + 1: positions p, p + 1
+        }
+      } else {  // some result below -20 (or a NaN): the wide-range sigmoid for this half, rare
 #pragma unroll  // unrolled although cold: a run-time index would move conv[] to local memory for both branches
-      for (int j = 0; j < kConvRun; j += 2) {
-        const float2 xa = bf16x2_to_float2(conv[j]);
-        const float2 xb = bf16x2_to_float2(conv[j + 1]);
-        const uint32_t sa = float2_to_bf16x2(make_float2(sigmoid_wide(xa.x), sigmoid_wide(xa.y)));
-        const uint32_t sb = float2_to_bf16x2(make_float2(sigmoid_wide(xb.x), sigmoid_wide(xb.y)));
-        const uint32_t ra = mul_bf16x2(conv[j], sa);
-        const uint32_t rb = mul_bf16x2(conv[j + 1], sb);
-        dst_a[j >> 1] = __byte_perm(ra, rb, 0x5410) & keep[j >> 1];
-        dst_b[j >> 1] = __byte_perm(ra, rb, 0x7632) & keep[j >> 1];
+        for (int j = 0; j < kHalf; j += 2) {
+          const float2 xa = bf16x2_to_float2(conv[j]);
+          const float2 xb = bf16x2_to_float2(conv[j + 1]);
+          const uint32_t sa = float2_to_bf16x2(make_float2(sigmoid_wide(xa.x), sigmoid_wide(xa.y)));
+          const uint32_t sb = float2_to_bf16x2(make_float2(sigmoid_wide(xb.x), sigmoid_wide(xb.y)));
+          const uint32_t ra = mul_bf16x2(conv[j], sa);
+          const uint32_t rb = mul_bf16x2(conv[j + 1], sb);
+          const uint32_t k2 = keep[(h + j) >> 1];
+          dst_a[(h + j) >> 1] = __byte_perm(ra, rb, 0x5410) & k2;
+          dst_b[(h + j) >> 1] = __byte_perm(ra, rb, 0x7632) & k2;
+        }
       }
     }
   }

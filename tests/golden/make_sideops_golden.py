@@ -95,6 +95,8 @@ def main():
                 q, k, wq, wk, eps = W.make_rmsnorm_inputs(tokens, heads, 0, dev)
                 qn, kn = torch.empty_like(q), torch.empty_like(k)
                 times["rmsnorm_qk/" + wl] = time_fn(lambda: ref038.run(q, k, wq, wk, eps, qn, kn))
+                from sol_execbench_b200_kernels_b200 import side_ops
+                times["rmsnorm_qk_this_package/" + wl] = time_fn(lambda: side_ops.rmsnorm_qk(q, k, wq, wk, eps, qn, kn))
     else:
         print("oracle/_ref/ref038_rmsnorm_qk missing: skipped")
 
@@ -123,6 +125,20 @@ def main():
                        "oracle_max_abs_err": float(diff.max()), "numel": out.numel()},
                       open(os.path.join(args.out, name + ".json"), "w"), indent=1)
             print(name, "oracle mismatches", nz, "of", out.numel(), "max", float(diff.max()))
+        if args.time:
+            # whole op (projection GEMM + tail) of the reference; run this script under a profiler's launch list
+            # to read the reference's tail kernel and this package's side by side on the same projection
+            from sol_execbench_b200_kernels_b200 import side_ops
+            batch, sequence = 4, 2048
+            g = torch.Generator().manual_seed(1)
+            hidden = (torch.randn(batch, sequence, 8192, generator=g) * 0.5).to(torch.bfloat16).to(dev)
+            in_w = (torch.randn(32768, 8192, generator=g) * 0.02).to(torch.bfloat16).to(dev)
+            in_b = (torch.randn(32768, generator=g) * 0.1).to(torch.bfloat16).to(dev)
+            _, mask, cw, cb = W.make_mamba_tail_inputs(batch, sequence, 16384, 64, 1, dev)
+            times["mamba_conv1d_with_gating/reference_whole_op_b4_l2048"] = time_fn(
+                lambda: ref029.run(hidden, mask, in_w, in_b, cw, cb), iters=5)
+            times["mamba_conv1d_with_gating/this_package_whole_op_b4_l2048"] = time_fn(
+                lambda: side_ops.mamba_conv1d_with_gating(hidden, mask, in_w, in_b, cw, cb), iters=5)
     else:
         print("oracle/_ref/ref029_mamba_conv1d missing: skipped")
 
