@@ -270,7 +270,7 @@ gateup_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_cons
               if (ctid == 0 && !ctx.aborted) {
                 unsigned long long t0 = 0;
                 for (uint32_t it = 1; ld_acquire_gpu(p.flags + rr) != p.epoch; ++it) {
-                  __nanosleep(64);
+                  spin_backoff_ns(64u);
                   if ((it & 255u) == 0u) {
                     const unsigned long long now = globaltimer_ns();
                     if (t0 == 0) {
@@ -314,7 +314,7 @@ gateup_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_cons
   tc_fence_after();
   if (*abort_gen) {
     const unsigned long long t0 = globaltimer_ns();
-    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    while (globaltimer_ns() - t0 < 200000ull) spin_backoff_ns(1000u);
   }
   if (warp == 1) tmem_dealloc(tmem_base, Cfg::kTmemCols);
 }

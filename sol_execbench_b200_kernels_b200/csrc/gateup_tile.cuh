@@ -556,7 +556,7 @@ __device__ __forceinline__ void tile_kernel_body(const CUtensorMap& tm_x, const 
             if (store_leader && !ctx.aborted) {
               unsigned long long t0 = 0;
               for (uint32_t it = 1; ld_acquire_gpu(p.flags + rr) != p.epoch; ++it) {
-                __nanosleep(64);
+                spin_backoff_ns(64u);
                 if ((it & 255u) == 0u) {
                   const unsigned long long now = globaltimer_ns();
                   if (t0 == 0) {
@@ -615,7 +615,7 @@ __device__ __forceinline__ void tile_kernel_body(const CUtensorMap& tm_x, const 
   if (*abort_gen) {
     // give copies that were already in flight time to land before shared memory goes away
     const unsigned long long t0 = globaltimer_ns();
-    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    while (globaltimer_ns() - t0 < 200000ull) spin_backoff_ns(1000u);
   }
   if (warp == 1) tmem_dealloc(tmem_base, kTileTmemCols);
 }

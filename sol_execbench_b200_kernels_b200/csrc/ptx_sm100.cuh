@@ -21,6 +21,9 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
+// back-off inside a bounded spin: lets the other warps of the SM issue while this one polls
+__device__ __forceinline__ void spin_backoff_ns(uint32_t ns) { asm volatile("nanosleep.u32 %0;" ::"r"(ns)); }
+
 __device__ __forceinline__ unsigned long long globaltimer_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
