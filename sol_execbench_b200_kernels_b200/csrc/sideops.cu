@@ -87,8 +87,9 @@ rmsnorm_qk_kernel(const float4* __restrict__ query, const float4* __restrict__ k
 // 16 bytes per thread, pre-masked.  Compute phase: a lane owns a channel PAIR (one 32-bit shared-memory word
 // per row, so a warp reads 128 contiguous bytes), a warp owns 16 positions and slides the 4-tap window along
 // them; the fp32 arithmetic is done on (channel, channel+1) pairs with the packed f32x2 instructions.  Two
-// positions of one channel are packed into one word of the transposed output tile (pitch 65 words).  Store
-// phase: 128 contiguous bytes per warp instruction.  Algorithmic traffic: 2 bytes read + 2 bytes written per
+// positions of one channel are packed into one word of the transposed output tile (pitch 66 words).  Store
+// phase: 256 contiguous bytes per warp instruction (8 bytes per lane) when the sequence length is a multiple
+// of 4, 128 when it is even, single elements when it is odd.  Algorithmic traffic: 2 bytes read + 2 bytes written per
 // (token, channel).
 //
 // The sigmoid costs 1.25 special-function operations per element instead of 2: e = 2^(-|x| log2 e) lies in
@@ -101,7 +102,7 @@ constexpr int kConvPositions = 128;
 constexpr int kConvTaps = 4;
 constexpr int kConvRows = kConvPositions + kConvTaps - 1;  // 131
 constexpr int kConvThreads = 256;
-constexpr int kConvOutPitch = kConvPositions / 2 + 1;  // words; odd, so lanes that differ in channel differ in bank
+constexpr int kConvOutPitch = kConvPositions / 2 + 2;  // words; even, so that rows stay 8-byte aligned for the 64-bit reads of the store phase
 constexpr int kConvRun = kConvPositions / (kConvThreads / 32);  // positions per warp = 16
 
 __device__ __forceinline__ float ex2_approx(float x) {
@@ -174,12 +175,12 @@ __device__ __forceinline__ void sigmoid_2x2(uint32_t ca, uint32_t cb, uint32_t& 
   sb = float2_to_bf16x2(__fmul2_rn(rab, ya));   // 1/yb
 }
 
-__global__ void __launch_bounds__(kConvThreads, 6)  // 6 CTAs of 33 KiB per SM: the phases of one overlap the others'
+__global__ void __launch_bounds__(kConvThreads)  // 48 registers: 5 CTAs per SM; forcing 6 (40 registers) measured 7 % slower
 mamba_conv1d_tail_kernel(const __nv_bfloat16* __restrict__ projected, const __nv_bfloat16* __restrict__ mask,
                          const __nv_bfloat16* __restrict__ conv_weight, const __nv_bfloat16* __restrict__ conv_bias,
                          __nv_bfloat16* __restrict__ output, int sequence, int channels, long long width) {
   __shared__ __align__(16) uint32_t s_in[kConvRows * (kConvChannels / 2)];  // [row][channel pair]
-  __shared__ uint32_t s_out[kConvChannels * kConvOutPitch];                 // [channel][position pair]
+  __shared__ __align__(8) uint32_t s_out[kConvChannels * kConvOutPitch];                 // [channel][position pair]
   __shared__ uint32_t s_keep[kConvPositions / 2];  // per position pair: 0xffff in the half of a kept position
 
   const int tid = threadIdx.x;
@@ -257,7 +258,8 @@ mamba_conv1d_tail_kernel(const __nv_bfloat16* __restrict__ projected, const __nv
     constexpr int kHalf = kConvRun / 2;
     const int p0 = warp * kConvRun;
     const uint32_t* col = s_in + p0 * 32 + lane;
-    // tile row of channel c is (c & 1) * 32 + (c >> 1): both stores of a warp then hit 32 different banks
+    // tile row of channel c is (c & 1) * 32 + (c >> 1): the lanes of a warp store to consecutive rows (a 2-way
+    // bank conflict at the even pitch, cheaper than a second pass of 32-bit global stores)
     uint32_t* dst_a = s_out + lane * kConvOutPitch + (p0 >> 1);
     uint32_t* dst_b = dst_a + 32 * kConvOutPitch;
     const uint32_t* keep = s_keep + (p0 >> 1);
@@ -307,9 +309,26 @@ mamba_conv1d_tail_kernel(const __nv_bfloat16* __restrict__ projected, const __nv
   }
   __syncthreads();
 
-  // ---- store phase: rows of the transposed tile, 128 contiguous bytes per warp instruction ----
+  // ---- store phase: rows of the transposed tile, whole 256- or 128-byte runs per warp instruction ----
   const long long out_row0 = (static_cast<long long>(batch) * channels + c0) * sequence + l0;
-  if ((sequence & 1) == 0) {
+  if ((sequence & 3) == 0) {
+    // thread t owns positions 4 (t % 32) .. +3 of tile rows t / 32 + 8 i: rows 0..31 even channels, 32..63 odd
+    const int pw = tid & 31;
+    const int r0 = tid >> 5;
+    if (l0 + 4 * pw < sequence) {
+      const long long row_words = sequence >> 2;  // 8-byte words per output row
+      uint2* dst = reinterpret_cast<uint2*>(output + out_row0) + 2 * r0 * row_words + pw;
+      const uint32_t* src = s_out + r0 * kConvOutPitch + 2 * pw;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t* a = src + 8 * i * kConvOutPitch;
+        const uint32_t* b = src + (32 + 8 * i) * kConvOutPitch;
+        __stcs(dst, *reinterpret_cast<const uint2*>(a));
+        __stcs(dst + row_words, *reinterpret_cast<const uint2*>(b));
+        dst += 16 * row_words;
+      }
+    }
+  } else if ((sequence & 1) == 0) {
     // thread t owns word t % 64 of tile rows t / 64 + 4 i: rows 0..31 are the even channels, 32..63 the odd ones
     const int wd = tid & 63;
     const int r0 = tid >> 6;
@@ -384,7 +403,7 @@ int so_mamba_conv1d_tail(const void* projected, const void* attention_mask, cons
       channels > (1ll << 30))
     return SO_EINVAL_SHAPE;
   if (!so::aligned16(projected) || !so::aligned16(conv_weight) || (reinterpret_cast<uintptr_t>(conv_bias) & 3u) ||
-      (reinterpret_cast<uintptr_t>(attention_mask) & 1u) || (reinterpret_cast<uintptr_t>(output) & 3u))
+      (reinterpret_cast<uintptr_t>(attention_mask) & 1u) || !so::aligned16(output))
     return SO_EINVAL_ALIGN;
   if (batch == 0 || sequence == 0) return SO_OK;
   const long long seq_tiles = (sequence + so::kConvPositions - 1) / so::kConvPositions;

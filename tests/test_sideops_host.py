@@ -46,6 +46,7 @@ def test_c_abi_rejects_bad_arguments_before_any_cuda_call(so):
     assert g(16, 16, 16, 16, 16, 1, 8, 96, 128, None) == so.SO_EINVAL_SHAPE   # channels not a multiple of 64
     assert g(16, 16, 16, 16, 16, 1, 8, 128, 64, None) == so.SO_EINVAL_SHAPE   # narrower than the channels
     assert g(8, 16, 16, 16, 16, 1, 8, 64, 64, None) == so.SO_EINVAL_ALIGN
+    assert g(16, 16, 16, 16, 8, 1, 8, 64, 64, None) == so.SO_EINVAL_ALIGN
     assert g(16, 16, 16, 16, 16, 0, 8, 64, 64, None) == so.SO_OK
     assert so.lib.so_launch_count() == 0
 
