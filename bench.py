@@ -288,7 +288,7 @@ def run_ours(args):
     x_host = local.x.cpu().view(torch.uint8).pin_memory().view(torch.float8_e4m3fn)
     sx_host = local.scale_x.cpu().pin_memory()
     out_host = torch.empty(m, n_local, dtype=torch.bfloat16).pin_memory()
-    pipe = HostPipeline(m, k, n_local, dev, chunks=4)
+    pipe = HostPipeline(m, k, n_local, dev, chunks=args.e2e_chunks)
 
     def e2e_step():
         pipe.run(x_host, sx_host, local.gate_proj_weight, local.scale_gate, local.up_proj_weight, local.scale_up,
@@ -314,7 +314,7 @@ def run_ours(args):
            "h2d_bytes_per_step": pipe.bytes_h2d, "d2h_bytes_per_step": pipe.bytes_d2h, "steps": e2e_steps,
            "matches_device_run": e2e_ok,
            "note": "HostPipeline.run: weights resident in HBM; x and scale_x copied from pinned host memory and the "
-                   "bf16 output copied back to pinned host memory every step, in 4 row chunks on three streams; "
+                   f"bf16 output copied back to pinned host memory every step, in {len(pipe.bounds)} row chunks on three streams; "
                    "wall clock"}
 
     result = None
@@ -554,6 +554,7 @@ def main():
     ap.add_argument("--gather", action="store_true", help="N>1: also all-gather the contiguous [M, N] output")
     ap.add_argument("--fused-gather", action="store_true",
                     help="N>1: contiguous [M, N] output on every rank through peer stores in the kernel epilogue")
+    ap.add_argument("--e2e-chunks", type=int, default=8, help="row chunks of the host-memory pipeline in the e2e leg")
     ap.add_argument("--mlp", action="store_true",
                     help="N>1: tensor-parallel MLP block, NCCL all-reduce against the fused peer-store reduction")
     ap.add_argument("--side", action="store_true",

@@ -190,6 +190,14 @@ bool shape_ok(int64_t m, int64_t k, int64_t n) {
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// CTAs of `threads` threads of `kernel` that one SM holds at once (at least 1), by the runtime's occupancy query
+template <typename Kernel>
+int resident_ctas(Kernel kernel, int threads) {
+  int n = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, 0) != cudaSuccess || n < 1) n = 1;
+  return n;
+}
+
 int check_problem(const gu_problem* pr) {
   if (!pr) return GU_EINVAL_NULL;
   if (!pr->x || !pr->scale_x || !pr->gate_w || !pr->scale_gate || !pr->up_w || !pr->scale_up || !pr->output)
@@ -692,7 +700,14 @@ int gu_quantize_activation(const void* x, int x_is_f32, int64_t ld_x, void* q, f
   if (blocks >= (1ll << 31)) return GU_EINVAL_SHAPE;  // the kernel counts 1x128 blocks in 32 bits
   const long long per_cta = (gu::kQuantThreads / 16) * (x_is_f32 ? gu::quant_unroll<float>() : gu::quant_unroll<__nv_bfloat16>());
   long long grid = (blocks + per_cta - 1) / per_cta;
-  const long long cap = static_cast<long long>(dev->sm_count) * 8;  // 8 resident CTAs of 256 threads per SM
+  // one wave: as many CTAs as are resident at once (the kernel's registers allow 4 of 256 threads per SM; a grid
+  // of 8 per SM ran as two waves and paid two ramps)
+  static const int resident[2][2] = {
+      {gu::resident_ctas(gu::quantize_act_kernel<__nv_bfloat16, false>, gu::kQuantThreads),
+       gu::resident_ctas(gu::quantize_act_kernel<__nv_bfloat16, true>, gu::kQuantThreads)},
+      {gu::resident_ctas(gu::quantize_act_kernel<float, false>, gu::kQuantThreads),
+       gu::resident_ctas(gu::quantize_act_kernel<float, true>, gu::kQuantThreads)}};
+  const long long cap = static_cast<long long>(dev->sm_count) * resident[x_is_f32 ? 1 : 0][ld_x != k ? 1 : 0];
   if (grid > cap) grid = cap;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   const int g = static_cast<int>(grid);

@@ -8,7 +8,8 @@
 // elements (one 16- or 32-byte load), sixteen lanes own one 128-wide block, so a warp instruction covers
 // two blocks; the block maximum is a four-step shuffle reduction inside the half-warp.  The quotient
 // x / scale is the correctly rounded one: one correctly rounded reciprocal per block, then per element a
-// product and the exact-residual correction (q0 = x*r; e = fma(-q0, s, x); q = fma(e, r, q0)), and the
+// product and the exact-residual correction (q0 = x*r; e = fma(-q0, s, x); q = fma(e, r, q0); two elements per
+// instruction with the packed fp32 forms), and the
 // conversion rounds to nearest even with saturation, so the bits equal those of
 // `clamp(x / scale, -448, 448).to(float8_e4m3fn)` in PyTorch at a fifth of the instructions of eight divisions.
 #pragma once
@@ -63,13 +64,34 @@ struct Raw8<float> {
   }
 };
 
+// a / 448, correctly rounded, without the division sequence: product with the rounded reciprocal, then the
+// exact-residual correction (the same scheme as the per-element quotient).  Equal to the IEEE quotient for every
+// fp32 input from 1e-12 up (checked on the CPU: all bf16-valued inputs, 10^8 random fp32 inputs).
+__device__ __forceinline__ float div_by_448(float a) {
+  constexpr float kInv448 = 0.0022321429569274187f;  // RN(1 / 448) = 0x3b124925
+  const float q0 = a * kInv448;
+  return fmaf(fmaf(-q0, 448.0f, a), kInv448, q0);
+}
+
+// 1 / s for a normal s whose reciprocal is normal (here 2e-15 <= s < 2^126): hardware approximation plus one
+// residual step, in place of the general routine with its special-case branch.
+__device__ __forceinline__ float reciprocal_normal(float s) {
+  float r0;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r0) : "f"(s));
+  return fmaf(fmaf(-s, r0, 1.0f), r0, r0);
+}
+
 // Blocks in flight per half-warp: enough 16-byte loads outstanding to cover HBM latency at full bandwidth
 template <typename T>
-__host__ __device__ constexpr int quant_unroll() { return sizeof(T) == 2 ? 8 : 4; }
+__host__ __device__ constexpr int quant_unroll() { return 4; }
+// Resident CTAs the compiler is asked to leave room for: measured on a B200 (bf16 input, 16384 x 7168, µs per launch,
+// unroll x CTAs per SM): 4x6 61.3, 6x5 62.6, 8x4 63.1, 4x8 64.7, 12x4 67.2, 8x5 (spills) 67.8.
+template <typename T>
+__host__ __device__ constexpr int quant_min_ctas() { return sizeof(T) == 2 ? 6 : 1; }
 
 // kPitched = false: rows are contiguous (ld_x == K), block b starts at element 128 * b and no division is needed.
 template <typename T, bool kPitched>
-__global__ void __launch_bounds__(kQuantThreads)
+__global__ void __launch_bounds__(kQuantThreads, quant_min_ctas<T>())
 quantize_act_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, float* __restrict__ scale, uint32_t blocks,
                     long long ld_x, uint32_t kb) {
   const int lane = threadIdx.x & 31;
@@ -102,11 +124,14 @@ quantize_act_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, float* __r
       float amax = raw[u].unpack(v);
 #pragma unroll
       for (int o = 8; o >= 1; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-      const float s = fmaxf(amax, 1e-12f) / 448.0f;
-      const float r = __frcp_rn(s);
-      auto quot = [&](float a) {
-        const float q0 = a * r;
-        return fmaf(fmaf(-q0, s, a), r, q0);
+      const float s = div_by_448(fmaxf(amax, 1e-12f));
+      const float r = reciprocal_normal(s);
+      // two quotients per instruction with the packed fp32 forms
+      const float2 r2 = make_float2(r, r), ns2 = make_float2(-s, -s);
+      auto quot2 = [&](float a, float c) {
+        const float2 x2 = make_float2(a, c);
+        const float2 q0 = __fmul2_rn(x2, r2);
+        return __ffma2_rn(__ffma2_rn(q0, ns2, x2), r2, q0);
       };
       if (live[u]) {
         const uint32_t bb = b + u * half_warps;
@@ -117,9 +142,8 @@ quantize_act_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, float* __r
 #pragma unroll
           for (int i = 0; i < 2; ++i) {
             // |x| <= amax, so |x / s| <= 448 up to one rounding; the saturating conversion does the clamp
-            const float a = quot(v[4 * w + 2 * i]);
-            const float c = quot(v[4 * w + 2 * i + 1]);
-            const __nv_fp8x2_storage_t pair = __nv_cvt_float2_to_fp8x2(make_float2(a, c), __NV_SATFINITE, __NV_E4M3);
+            const float2 ac = quot2(v[4 * w + 2 * i], v[4 * w + 2 * i + 1]);
+            const __nv_fp8x2_storage_t pair = __nv_cvt_float2_to_fp8x2(ac, __NV_SATFINITE, __NV_E4M3);
             word |= static_cast<uint32_t>(pair) << (16 * i);
           }
           packed[w] = word;
