@@ -544,6 +544,50 @@ def run_side(args):
                      "frac": round(nb / ms / 1e6 / peaks["hbm_gbs"], 4)} for k, (ms, nb) in rows.items()}}), flush=True)
 
 
+def run_graph(args):
+    """Decode-sized calls issued one after another, as a token loop does: eager calls through the Python entry point
+    against replays of one CUDA graph that recorded the call.  Wall clock per call over a few hundred calls (the GPU
+    is never flushed here: the point is the host cost per launch).  A study line, not the headline metric."""
+    import sol_execbench_b200_kernels_b200 as pkg
+    from sol_execbench_b200_kernels_b200 import workloads as W
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    rows = {}
+    calls = 300
+    for name, (m, k, n) in {"m1_k4096_n14336": (1, 4096, 14336), "m16_k4096_n14336": (16, 4096, 14336),
+                            "decode_70b": W.SHAPES["decode_70b"]}.items():
+        inp = W.make_inputs(m, k, n, seed=0, device=dev)
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+        for _ in range(5):
+            pkg.run(*inp.args(), out)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(calls):
+            pkg.run(*inp.args(), out)
+        torch.cuda.synchronize()
+        eager = (time.perf_counter() - t0) / calls
+        want = out.clone()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            pkg.run(*inp.args(), out)
+        for _ in range(5):
+            graph.replay()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(calls):
+            graph.replay()
+        torch.cuda.synchronize()
+        replay = (time.perf_counter() - t0) / calls
+        rows[name] = {"plan": pkg.select_plan(m, k, n), "eager_us_per_call": round(eager * 1e6, 2),
+                      "graph_replay_us_per_call": round(replay * 1e6, 2), "replay_equals_eager": bool(torch.equal(out, want))}
+    code, detail = pkg.last_status()
+    if code != 0:
+        raise SystemExit(f"bench.py: device status {code} detail {detail:#x}")
+    print(json.dumps({"study": "decode loop: eager calls against CUDA-graph replays", "calls": calls, "rows": rows,
+                      "gpu_launches": pkg.launch_count()}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -557,6 +601,8 @@ def main():
     ap.add_argument("--e2e-chunks", type=int, default=8, help="row chunks of the host-memory pipeline in the e2e leg")
     ap.add_argument("--mlp", action="store_true",
                     help="N>1: tensor-parallel MLP block, NCCL all-reduce against the fused peer-store reduction")
+    ap.add_argument("--graph", action="store_true",
+                    help="one GPU: decode-sized call loop, eager against CUDA-graph replay (host cost per launch)")
     ap.add_argument("--side", action="store_true",
                     help="one GPU: the side operators (RMSNorm of query/key, Mamba conv1d tail) against the HBM roofline")
     ap.add_argument("--sweep", action="store_true", help="M sweep at K=4096, N=14336 on one GPU (plan crossover study)")
@@ -568,6 +614,8 @@ def main():
         run_mlp(args)
     elif args.side:
         run_side(args)
+    elif args.graph:
+        run_graph(args)
     elif args.sweep:
         run_sweep(args)
     else:

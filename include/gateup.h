@@ -91,9 +91,9 @@ size_t gu_workspace_bytes(int64_t m, int64_t k, int64_t n, int plan);
 
 /*
  * Prepare freshly allocated scratch (zeroes the hand-off flags; enqueued on
- * `stream`).  Needed once per allocation, not per call: each call stamps the
- * flags with a new epoch.  Calls that share one workspace must not overlap on
- * the GPU.
+ * `stream`).  Needed once per allocation, not per call: each launch stamps the
+ * flags with a new epoch, taken from a launch counter inside the workspace.
+ * Calls that share one workspace must not overlap on the GPU.
  */
 int gu_workspace_init(void* workspace, size_t bytes, void* stream);
 
@@ -102,6 +102,10 @@ int gu_workspace_init(void* workspace, size_t bytes, void* stream);
  * of the reference `run`: two GEMM launches and the SwiGLU launch
  * (kernel.py:487-503), or `launch_fp8_mlp_gate_up` (cuda_cpp_v4/kernel.cu:271-341).
  * Asynchronous; returns after the launch with 0 or a negative code.
+ * With GU_PLAN_AUTO / TILE / TILE_DP / STREAM the launch keeps no host-side
+ * state, so a launch recorded in a CUDA graph may be replayed (the workspace
+ * must stay allocated and be used by nothing else meanwhile); GU_PLAN_TILE_SK,
+ * a study option, stamps its flags from a host counter and must not be replayed.
  */
 int gu_run(const gu_problem* problem, void* stream);
 

@@ -305,7 +305,6 @@ int launch_stream_t(const gu_problem* pr, const DeviceInfo& dev, cudaStream_t st
   p.stages = stages;
   p.flags = static_cast<unsigned int*>(pr->workspace);
   p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(pr->workspace) + kStreamFlagBytes);
-  p.epoch = next_epoch();
 
   const int64_t units = int64_t(p.nb) * p.kb;
   int64_t grid = dev.sm_count < kStreamMaxGrid ? dev.sm_count : kStreamMaxGrid;
@@ -512,14 +511,11 @@ int gu_run_decode_static(const gu_problem* pr, void* stream_v) {
   p.nb = static_cast<int>(n / 128);
   p.stages = stages;
   // The array keeps whatever the previous call left in it.  Nothing has to be cleared: a flag only
-  // counts when it equals this call's epoch, a value no earlier call has written (the array starts
-  // zeroed at module load and 0 is never an epoch), and partial slots are fully rewritten before
-  // their flag is stamped.
+  // counts when it equals this launch's epoch, a value no earlier launch has written (the array, with
+  // the launch counter that epochs come from, starts zeroed at module load and 0 is never an epoch), and
+  // partial slots are fully rewritten before their flag is stamped.
   p.flags = static_cast<unsigned int*>(scratch);
   p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) + gu::kStreamFlagBytes);
-  unsigned int e = gu::g_epoch.fetch_add(1, std::memory_order_relaxed) + 1;
-  if (e == 0) e = gu::g_epoch.fetch_add(1, std::memory_order_relaxed) + 1;
-  p.epoch = e;
 
   const int64_t units = int64_t(p.nb) * p.kb;
   int64_t grid = dev->sm_count < gu::kStreamMaxGrid ? dev->sm_count : gu::kStreamMaxGrid;

@@ -41,10 +41,18 @@ struct StreamParams {
   long long ld_out;
   int m, kb, nb;
   int stages;               // shared-memory ring depth (host: what fits)
-  unsigned int* flags;      // [gridDim.x], holds the epoch of the last call that filled slot i
+  unsigned int* flags;      // [gridDim.x], holds the epoch of the last launch that filled slot i; plus the two
+                            // words kStreamSyncLaunches / kStreamSyncTickets below
   float* partials;          // [gridDim.x][2][MPAD][128]
-  unsigned int epoch;       // this call's stamp, never 0
 };
+
+// The epoch of a launch is kept on the device, so that a launch recorded once (a CUDA graph) can be replayed: word
+// kStreamSyncLaunches of the flag area counts completed launches on this workspace, every CTA reads it when it starts
+// and stamps with that count + 1; at its end every CTA takes a ticket (word kStreamSyncTickets) and the last one
+// advances the count.  All CTAs have read the count before the last ticket is taken.
+constexpr int kStreamSyncLaunches = 1022;
+constexpr int kStreamSyncTickets = 1023;
+static_assert(kStreamMaxGrid <= kStreamSyncLaunches, "hand-off flags and the launch counters share the flag area");
 
 template <int MPAD>
 struct StreamCfg {
@@ -177,6 +185,11 @@ gateup_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_cons
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;  // weight row inside the tile = output column inside the block
     const int ctid = threadIdx.x - 64;    // 0..127
+    unsigned int epoch = 0;               // this launch's stamp, never 0; only thread ctid == 0 uses it
+    if (ctid == 0) {
+      epoch = ld_acquire_gpu(p.flags + kStreamSyncLaunches) + 1u;
+      if (epoch == 0u) epoch = 1u;
+    }
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
 
     // scale_x, transposed to [kb][MPAD] so one K block's token scales are contiguous
@@ -261,7 +274,7 @@ gateup_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_cons
           }
           __threadfence();
           named_bar_sync(1, 128);
-          if (ctid == 0 && !ctx.aborted) st_release_gpu(p.flags + my_range, p.epoch);
+          if (ctid == 0 && !ctx.aborted) st_release_gpu(p.flags + my_range, epoch);
         } else {
           if (!block_done) {
             // owner of the block's first K block: collect the later ranges' partials, in range order
@@ -269,7 +282,7 @@ gateup_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_cons
             for (int rr = my_range + 1; rr < ranges && stream_range_start(units, ranges, rr) < block_end; ++rr) {
               if (ctid == 0 && !ctx.aborted) {
                 unsigned long long t0 = 0;
-                for (uint32_t it = 1; ld_acquire_gpu(p.flags + rr) != p.epoch; ++it) {
+                for (uint32_t it = 1; ld_acquire_gpu(p.flags + rr) != epoch; ++it) {
                   spin_backoff_ns(64u);
                   if ((it & 255u) == 0u) {
                     const unsigned long long now = globaltimer_ns();
@@ -317,6 +330,15 @@ gateup_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_cons
     while (globaltimer_ns() - t0 < 200000ull) spin_backoff_ns(1000u);
   }
   if (warp == 1) tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  if (threadIdx.x == 0) {
+    // the last CTA to get here closes the launch: the next one (or a replay of this one) stamps with a new epoch
+    __threadfence();
+    if (atomicAdd(p.flags + kStreamSyncTickets, 1u) == gridDim.x - 1u) {
+      p.flags[kStreamSyncTickets] = 0u;
+      __threadfence();
+      atomicAdd(p.flags + kStreamSyncLaunches, 1u);
+    }
+  }
 }
 
 }  // namespace gu
