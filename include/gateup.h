@@ -168,7 +168,9 @@ int gu_blockwise_gemm_scatter(const void* a, const float* scale_a, const void* b
  * Second half: sums this rank's `world` slots ([world][M/world][H] bf16, filled by all ranks'
  * gu_blockwise_gemm_scatter) in rank order in fp32, rounds once to bf16 and writes the reduced rows into
  * every rank's full result rank_outputs[r] ([M][H] bf16, contiguous) at row rank*M/world, with 16-byte
- * stores (over NVLink for the peers).  After a second cross-rank barrier every rank holds the full sum.
+ * stores (over NVLink for the peers); a null rank_outputs[r] other than this rank's own is skipped, which with
+ * all peers null is the reduce-scatter form (each rank keeps only its own rows).  After a second cross-rank
+ * barrier every rank holds the full sum.
  * The summation order is fixed, so all ranks hold identical bits.  H a multiple of 8.  No counterpart in the
  * reference; it stands where an NCCL all-reduce would follow gu_blockwise_gemm.
  */

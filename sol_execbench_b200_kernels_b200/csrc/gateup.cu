@@ -665,9 +665,10 @@ int gu_reduce_gather(const void* slots, void* const* rank_outputs, int world, in
   gu::ReduceGatherParams p;
   std::memset(&p, 0, sizeof(p));
   p.slots = static_cast<const uint4*>(slots);
+  if (!rank_outputs[rank]) return GU_EINVAL_NULL;
   for (int r = 0; r < world; ++r) {
-    if (!rank_outputs[r]) return GU_EINVAL_NULL;
-    if (!gu::aligned16(rank_outputs[r])) return GU_EINVAL_ALIGN;
+    // a null entry other than this rank's own is a destination that does not want the rows (reduce-scatter form)
+    if (rank_outputs[r] && !gu::aligned16(rank_outputs[r])) return GU_EINVAL_ALIGN;
     p.outputs[r] = static_cast<uint4*>(rank_outputs[r]);
   }
   const int64_t slot_rows = m / world;

@@ -14,7 +14,7 @@ namespace gu {
 
 struct ReduceGatherParams {
   const uint4* slots;       // this rank's [world][slot_rows][h] bf16, as 16-byte words
-  uint4* outputs[8];        // every rank's [M][h] bf16 result buffer, as mapped into this process
+  uint4* outputs[8];        // every rank's [M][h] bf16 result buffer, as mapped into this process; null = skip
   long long words_per_slot; // slot_rows * h / 8
   long long out_word0;      // rank * slot_rows * h / 8: where this rank's rows start in a result buffer
   int world;
@@ -44,7 +44,7 @@ __global__ void __launch_bounds__(256) reduce_gather_kernel(const ReduceGatherPa
     for (int e = 0; e < 4; ++e) o[e] = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
 #pragma unroll
     for (int d = 0; d < 8; ++d)  // unrolled so that the pointer table stays in the parameter space
-      if (d < p.world) p.outputs[d][p.out_word0 + i] = r;
+      if (d < p.world && p.outputs[d] != nullptr) p.outputs[d][p.out_word0 + i] = r;
   }
 }
 

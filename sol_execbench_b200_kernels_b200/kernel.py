@@ -304,13 +304,14 @@ def blockwise_gemm_scatter(a: torch.Tensor, scale_a: torch.Tensor, b: torch.Tens
 @torch.no_grad()
 def reduce_gather(slots: torch.Tensor, rank_output_ptrs, rank: int, m: int, h: int) -> None:
     """Sum this rank's slots [world, M/world, H] (bf16, fp32 accumulation in rank order) and write the reduced
-    rows into every rank's [M, H] result (`rank_output_ptrs[r]`, mapped into this process).  Asynchronous."""
+    rows into every rank's [M, H] result (`rank_output_ptrs[r]`, mapped into this process; a peer entry of None is
+    skipped).  Asynchronous."""
     world = len(rank_output_ptrs)
     if slots.dtype != torch.bfloat16 or not slots.is_contiguous() or slots.numel() != m * h or m % world:
         raise ValueError("slots must be a contiguous bf16 [world, M/world, H] tensor")
     with torch.cuda.device(slots.device):
         stream_ptr = torch.cuda.current_stream(slots.device).cuda_stream
-        ptrs = (ctypes.c_void_p * world)(*[int(p) for p in rank_output_ptrs])
+        ptrs = (ctypes.c_void_p * world)(*[(int(p) if p else None) for p in rank_output_ptrs])
         code = _cabi.lib.gu_reduce_gather(slots.data_ptr(), ptrs, world, rank, m, h, stream_ptr)
     if code != _cabi.GU_OK:
         if code in (_cabi.GU_EINVAL_NULL, _cabi.GU_EINVAL_SHAPE, _cabi.GU_EINVAL_ALIGN):

@@ -183,13 +183,14 @@ class ReduceBuffers:
 @torch.no_grad()
 def mlp_block_sharded_fused(x: torch.Tensor, gate_shard: torch.Tensor, scale_gate_shard: torch.Tensor,
                             up_shard: torch.Tensor, scale_up_shard: torch.Tensor, down_shard: torch.Tensor,
-                            scale_down_shard: torch.Tensor, buffers: ReduceBuffers) -> torch.Tensor:
+                            scale_down_shard: torch.Tensor, buffers: ReduceBuffers, gather: bool = True) -> torch.Tensor:
     """`mlp_block_sharded` with the all-reduce done by the library's own kernels over peer memory.
 
     The down projection's epilogue TMA-stores each bf16 partial tile into the slot buffer of the rank that
     owns those token rows (reduce-scatter, overlapped with the math tile by tile); after a barrier each rank
     sums its slots in rank order and writes the reduced rows into every rank's [M, H] result (all-gather by
-    peer stores).  Two cross-rank barriers, no NCCL call.  All ranks return identical bits.  Consume the
+    peer stores).  Two cross-rank barriers, no NCCL call.  All ranks return identical bits.  With
+    `gather=False` each rank keeps only the rows it owns ([M/R, H], the reduce-scatter form) and nothing is sent back.  Consume the
     result on the stream this was called on (or synchronise with it) before the next call on `buffers`.
     """
     from .kernel import BLOCK as _B, blockwise_gemm_scatter, quantize_activation, reduce_gather, run_fp8_output
@@ -205,9 +206,17 @@ def mlp_block_sharded_fused(x: torch.Tensor, gate_shard: torch.Tensor, scale_gat
     # which every rank has enqueued (on this stream) whatever reads the previous result.
     blockwise_gemm_scatter(mid_q, mid_s, down_shard, scale_down_shard, buffers.slot_ptrs, buffers.rank)
     buffers.barrier()  # all partial tiles have landed in their owners' slots
-    reduce_gather(buffers.slots, buffers.out_ptrs, buffers.rank, m, h)
-    buffers.barrier()  # every rank's rows have landed in every result
-    return buffers.out
+    if gather:
+        reduce_gather(buffers.slots, buffers.out_ptrs, buffers.rank, m, h)
+        buffers.barrier()  # every rank's rows have landed in every result
+        return buffers.out
+    # reduce-scatter form (sequence-parallel consumers): only this rank's rows, written locally.  The closing barrier
+    # stays: it is what lets the next call's scatter overwrite the slots.
+    own = [p if r == buffers.rank else None for r, p in enumerate(buffers.out_ptrs)]
+    reduce_gather(buffers.slots, own, buffers.rank, m, h)
+    buffers.barrier()
+    rows = m // buffers.world
+    return buffers.out[buffers.rank * rows:(buffers.rank + 1) * rows]
 
 
 @torch.no_grad()

@@ -102,6 +102,10 @@ for _ in range(2):
     assert torch.equal(yf, want), f"rank {rank}: fused reduce differs from the fp32 sum of the bf16 partials"
     rel = float(torch.linalg.vector_norm(yf.float() - ref_y.float()) / torch.linalg.vector_norm(ref_y.float()))
     assert rel <= 1e-2, f"rank {rank}: fused sharded MLP rel-L2 {rel}"
+    rows = m // world
+    mine = pkg.mlp_block_sharded_fused(xb, gw, sg, uw, su, dw, ds, rb, gather=False)
+    torch.cuda.synchronize()
+    assert torch.equal(mine, want[rank * rows:(rank + 1) * rows]), f"rank {rank}: reduce-scatter form differs"
 dist.barrier()
 dist.destroy_process_group()
 print(f"rank {rank} ok")
@@ -139,6 +143,16 @@ def test_scatter_and_reduce_on_one_gpu_sum_the_partial_products(shape, world):
     want = want.to(torch.bfloat16)
     for r in range(world):
         assert torch.equal(outs[r], want), f"rank {r}"
+    # reduce-scatter form: peers' entries None, only the own rows are written
+    rows = m // world
+    for r in range(world):
+        outs[r].fill_(float("nan"))
+        pkg.reduce_gather(slots[r], [outs[d].data_ptr() if d == r else None for d in range(world)], r, m, h)
+    torch.cuda.synchronize()
+    for r in range(world):
+        assert torch.equal(outs[r][r * rows:(r + 1) * rows], want[r * rows:(r + 1) * rows])
+        rest = torch.cat([outs[r][:r * rows], outs[r][(r + 1) * rows:]])
+        assert bool(torch.isnan(rest.float()).all())
 
 
 def test_scatter_rejects_token_counts_that_do_not_split_into_whole_blocks():
