@@ -1,4 +1,4 @@
-"""Compiles the reference's own CUDA sources of problems 038 and 029, where they lie in a checkout of the
+"""Compiles the reference's own CUDA sources of problems 038 and 029 and of the C++ variant of problem 179, where they lie in a checkout of the
 reference repository, into torch extensions under oracle/_ref/ (git-ignored).  Test infrastructure only: the GPU
 parity tests load these libraries, when present, as a second check beside the CPU restatement; nothing in the
 package imports them.  Nothing is copied: the compiler reads the sources in place.
@@ -18,8 +18,12 @@ HERE = Path(__file__).resolve().parent
 OUT = HERE / "_ref"
 
 PROBLEMS = {
-    "ref038_rmsnorm_qk": ("kernels/038_flux_multi_head_rmsnorm_qk", ["binding.cpp", "kernel.cu"]),
-    "ref029_mamba_conv1d": ("kernels/029_mamba_conv1d_with_gating", ["binding.cpp", "kernel.cu"]),
+    "ref038_rmsnorm_qk": ("kernels/038_flux_multi_head_rmsnorm_qk", ["binding.cpp", "kernel.cu"], []),
+    "ref029_mamba_conv1d": ("kernels/029_mamba_conv1d_with_gating", ["binding.cpp", "kernel.cu"], []),
+    # the C++ variant of problem 179 (fixed K = 3584, N = 18944); the reference's tooling appends this define for
+    # B200 artifacts (tools/extra_kernels.py:411-418)
+    "ref179_cuda_cpp_v4": ("kernels/179_fp8_mlp_gate_up_projection/variants/cuda_cpp_v4", ["binding.cpp", "kernel.cu"],
+                           ["-DSOL_TARGET_SM100=1"]),
 }
 
 
@@ -37,7 +41,7 @@ def build(reference_root: str, only: str | None = None) -> dict:
     from torch.utils import cpp_extension
 
     results = {}
-    for name, (subdir, files) in PROBLEMS.items():
+    for name, (subdir, files, defines) in PROBLEMS.items():
         if only and only != name:
             continue
         src = Path(reference_root) / subdir
@@ -47,7 +51,7 @@ def build(reference_root: str, only: str | None = None) -> dict:
             cpp_extension.load(
                 name=name, sources=[str(src / f) for f in files], build_directory=str(build_dir),
                 extra_cflags=["-O3", "-std=c++17"],
-                extra_cuda_cflags=["-O3", "--use_fast_math", "-std=c++17"],
+                extra_cuda_cflags=["-O3", "--use_fast_math", "-std=c++17"] + defines,
                 extra_include_paths=[str(src)] + cutlass_include(), extra_ldflags=["-lcuda"],
                 is_python_module=False, verbose=False)
             results[name] = "built"

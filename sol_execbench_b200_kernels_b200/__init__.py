@@ -11,7 +11,7 @@ entry points without the built library raises: there is no fallback path.
 """
 from . import workloads  # noqa: F401  (pure torch, no native code)
 from .sharded import (GatherBuffers, ReduceBuffers, assemble_gathered, gather_columns, mlp_block_sharded,  # noqa: F401
-                      mlp_block_sharded_fused,
+                      mlp_block_sharded_fused, owned_rows,
                       run_sharded, run_sharded_fused, shard_bounds, shard_concat_weights, shard_down_weights,
                       shard_weights)
 
@@ -28,5 +28,5 @@ def __getattr__(name):
 
 
 __all__ = list(_NATIVE) + ["workloads", "run_sharded", "run_sharded_fused", "GatherBuffers", "shard_bounds",
-                           "shard_weights", "shard_concat_weights", "shard_down_weights", "mlp_block_sharded", "mlp_block_sharded_fused", "ReduceBuffers",
+                           "shard_weights", "shard_concat_weights", "shard_down_weights", "mlp_block_sharded", "mlp_block_sharded_fused", "ReduceBuffers", "owned_rows",
                            "gather_columns", "assemble_gathered"]

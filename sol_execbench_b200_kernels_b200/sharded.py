@@ -154,6 +154,17 @@ def mlp_block_sharded(x: torch.Tensor, gate_shard: torch.Tensor, scale_gate_shar
     return partial
 
 
+def owned_rows(m: int, rank: int, world: int) -> Tuple[int, int]:
+    """[start, stop) of the token rows whose reduced sum rank `rank` produces in the fused row-parallel GEMM +
+    all-reduce: equal runs of whole 128-row tiles, so that every output tile of the GEMM has one owner."""
+    if world < 1 or not 0 <= rank < world:
+        raise ValueError(f"bad rank/world {rank}/{world}")
+    if m % (BLOCK * world):
+        raise ValueError(f"M={m} must be a multiple of {BLOCK} * world ({world})")
+    rows = m // world
+    return rank * rows, (rank + 1) * rows
+
+
 class ReduceBuffers:
     """Symmetric buffers of the fused row-parallel GEMM + all-reduce: per rank a bf16 slot buffer
     [world, M/world, H] (one partial result per sending rank, for the token rows this rank owns) and a bf16
@@ -164,8 +175,7 @@ class ReduceBuffers:
 
         self.group = group if group is not None else dist.group.WORLD
         world = dist.get_world_size(self.group)
-        if m % (BLOCK * world):
-            raise ValueError(f"M={m} must be a multiple of {BLOCK} * world ({world})")
+        owned_rows(m, 0, world)  # raises when the rows do not split into whole tiles per rank
         self.slots = symm_mem.empty((world, m // world, h), dtype=torch.bfloat16, device=device)
         self.slots_handle = symm_mem.rendezvous(self.slots, self.group)
         self.out = symm_mem.empty((m, h), dtype=torch.bfloat16, device=device)

@@ -115,3 +115,67 @@ def test_row_parallel_down_projection_shards_sum_to_the_unsharded_result():
         acc += O._blockwise_gemm(mq.view(torch.uint8)[:, lo:hi].contiguous().view(torch.float8_e4m3fn),
                                  ms[:, lo // 128:hi // 128].contiguous(), dw, ds)
     assert torch.allclose(acc, full, rtol=1e-5, atol=1e-5)
+
+
+def _reduce_rank_main(rank, world, port, m, h, q):
+    """The exchange schedule of the fused row-parallel GEMM + all-reduce, with gloo standing in for the peer stores:
+    every rank's bf16 partial result is cut into the owners' row runs and delivered into the owners' slots
+    (slot = sending rank), each owner sums its slots in rank order in fp32 and rounds once, the reduced runs are
+    delivered to everybody."""
+    from sol_execbench_b200_kernels_b200.sharded import owned_rows
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        g = torch.Generator().manual_seed(100 + rank)
+        partial = torch.randn(m, h, generator=g).to(torch.bfloat16)
+        rows = m // world
+        send = [partial[slice(*owned_rows(m, d, world))].contiguous() for d in range(world)]
+        slots = [torch.empty(rows, h, dtype=torch.bfloat16) for _ in range(world)]
+        # slot s of this rank = rank s's partial of my rows (point to point: gloo has no all-to-all)
+        slots[rank].copy_(send[rank])
+        work = [dist.isend(send[d], d) for d in range(world) if d != rank]
+        work += [dist.irecv(slots[s], s) for s in range(world) if s != rank]
+        for w in work:
+            w.wait()
+        acc = torch.zeros(rows, h, dtype=torch.float32)
+        for s in range(world):
+            acc += slots[s].float()
+        mine = acc.to(torch.bfloat16)
+        full = [torch.empty(rows, h, dtype=torch.bfloat16) for _ in range(world)]
+        dist.all_gather(full, mine)
+        # by value (numpy), so that nothing refers to this process's shared memory after it exits
+        q.put((rank, partial.view(torch.int16).numpy().copy(), torch.cat(full).view(torch.int16).numpy().copy()))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_reduce_scatter_and_gather_schedule_gloo(world):
+    import torch.multiprocessing as mp
+    from sol_execbench_b200_kernels_b200.sharded import owned_rows
+
+    m, h = 128 * world * 2, 64
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_reduce_rank_main, args=(r, world, port, m, h, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = sorted((q.get(timeout=120) for _ in range(world)), key=lambda t: t[0])
+    got = [(r, torch.from_numpy(a).view(torch.bfloat16), torch.from_numpy(b).view(torch.bfloat16)) for r, a, b in got]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    want = torch.zeros(m, h, dtype=torch.float32)
+    for _, partial, _ in got:
+        want += partial.float()                            # rank order, fp32, one rounding
+    want = want.to(torch.bfloat16)
+    for rank, _, full in got:
+        assert torch.equal(full, want), f"rank {rank}"
+    edges = [owned_rows(m, r, world) for r in range(world)]
+    assert edges[0][0] == 0 and edges[-1][1] == m and all(a[1] == b[0] for a, b in zip(edges, edges[1:]))
+    with pytest.raises(ValueError):
+        owned_rows(128 * world + 128, 0, world) if world > 1 else owned_rows(100, 0, 1)
