@@ -1,4 +1,4 @@
-"""Compiles the reference's own CUDA sources of problems 038 and 029 and of the C++ variant of problem 179, where they lie in a checkout of the
+"""Compiles the reference's own CUDA sources of problems 038 and 029, where they lie in a checkout of the
 reference repository, into torch extensions under oracle/_ref/ (git-ignored).  Test infrastructure only: the GPU
 parity tests load these libraries, when present, as a second check beside the CPU restatement; nothing in the
 package imports them.  Nothing is copied: the compiler reads the sources in place.
@@ -20,10 +20,9 @@ OUT = HERE / "_ref"
 PROBLEMS = {
     "ref038_rmsnorm_qk": ("kernels/038_flux_multi_head_rmsnorm_qk", ["binding.cpp", "kernel.cu"], []),
     "ref029_mamba_conv1d": ("kernels/029_mamba_conv1d_with_gating", ["binding.cpp", "kernel.cu"], []),
-    # the C++ variant of problem 179 (fixed K = 3584, N = 18944); the reference's tooling appends this define for
-    # B200 artifacts (tools/extra_kernels.py:411-418)
-    "ref179_cuda_cpp_v4": ("kernels/179_fp8_mlp_gate_up_projection/variants/cuda_cpp_v4", ["binding.cpp", "kernel.cu"],
-                           ["-DSOL_TARGET_SM100=1"]),
+    # Not built: the C++ variant of problem 179 (variants/cuda_cpp_v4).  It compiles against the CUTLASS tree of
+    # this image, but its first launch returns "invalid configuration argument" from CUTLASS's cluster launch (the
+    # variant was written against another CUTLASS release), so it cannot serve as a checker here.
 }
 
 
