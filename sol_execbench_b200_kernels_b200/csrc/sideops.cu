@@ -92,10 +92,10 @@ rmsnorm_qk_kernel(const float4* __restrict__ query, const float4* __restrict__ k
 // of 4, 128 when it is even, single elements when it is odd.  Algorithmic traffic: 2 bytes read + 2 bytes written per
 // (token, channel).
 //
-// The sigmoid costs 1.25 special-function operations per element instead of 2: e = 2^(-|x| log2 e) lies in
-// (0, 1], so the four denominators 1 + e of a 2 x 2 block lie in (1, 2] and are inverted with ONE reciprocal
-// of their product (products of the other three give each quotient back); sigmoid = 1/(1+e) for x >= 0 and
-// e/(1+e) for x < 0, which keeps full relative accuracy in the negative tail.
+// The sigmoid costs 1.25 special-function operations per element instead of 2 (see sigmoid_2x2): for arguments
+// >= -20 it is 1 / (1 + 2^(-x log2 e)) with ONE reciprocal of the product of the four denominators of a 2 x 2
+// block; a run that holds an argument below -20 takes the wide-range form sigmoid_wide, which keeps full relative
+// accuracy in the negative tail.
 // ------------------------------------------------------------------------------------------------------------
 constexpr int kConvChannels = 64;
 constexpr int kConvPositions = 128;
