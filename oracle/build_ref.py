@@ -60,6 +60,8 @@ def build(reference_root: str, only: str | None = None) -> dict:
 
 
 if __name__ == "__main__":
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit(__doc__)
+    root = sys.argv[1]
     for k, v in build(root, sys.argv[2] if len(sys.argv) > 2 else None).items():
         print(k, "->", v)
