@@ -39,6 +39,16 @@ def select_plan(m: int, k: int, n: int) -> str:
     return _cabi.PLAN_NAMES[code]
 
 
+def _raise_for(code: int) -> None:
+    """0 returns; a contract violation the library found itself becomes ValueError, like the Python-side checks; any
+    other code (workspace, CUDA, device, time-out) GateUpError."""
+    if code == _cabi.GU_OK:
+        return
+    if code in (_cabi.GU_EINVAL_NULL, _cabi.GU_EINVAL_SHAPE, _cabi.GU_EINVAL_ALIGN, _cabi.GU_EINVAL_PLAN):
+        raise ValueError(f"libgateup: {_cabi.error_string(code)} (code {code})")
+    raise _cabi.GateUpError(code, _cabi.error_string(code))
+
+
 def _expected_inputs(x, scale_x, gate_w, scale_gate, up_w, scale_up, m_expected=None, n_expected=None):
     """(m, k, n) and the contract's (tensor, shape, dtype) per input name; raises on an unsupported M, K, N."""
     if x.dim() != 2 or gate_w.dim() != 2 or up_w.dim() != 2:
@@ -120,10 +130,7 @@ def _launch(x, scale_x, gate_w, scale_gate, up_w, scale_up, output, plan: str) -
             m, k, n, output.stride(0),
             ws.data_ptr() if ws is not None else None, nbytes, plan_id, 0)
         code = _cabi.lib.gu_run(ctypes.byref(pr), stream_ptr)
-    if code != _cabi.GU_OK:
-        if code in (_cabi.GU_EINVAL_NULL, _cabi.GU_EINVAL_SHAPE, _cabi.GU_EINVAL_ALIGN, _cabi.GU_EINVAL_PLAN):
-            raise ValueError(f"libgateup: {_cabi.error_string(code)} (code {code})")
-        raise _cabi.GateUpError(code, _cabi.error_string(code))
+    _raise_for(code)
 
 
 @torch.no_grad()
@@ -186,10 +193,7 @@ def run_gather(x: torch.Tensor, scale_x: torch.Tensor, gate_shard: torch.Tensor,
             up_shard.data_ptr(), scale_up_shard.data_ptr(), int(rank_output_ptrs[rank]),
             m, k, n_local, ld_full, None, 0, PLAN_TILE, 0)
         code = _cabi.lib.gu_run_gather(ctypes.byref(pr), ptrs, world, rank, ld_full, stream_ptr)
-    if code != _cabi.GU_OK:
-        if code in (_cabi.GU_EINVAL_NULL, _cabi.GU_EINVAL_SHAPE, _cabi.GU_EINVAL_ALIGN, _cabi.GU_EINVAL_PLAN):
-            raise ValueError(f"libgateup: {_cabi.error_string(code)} (code {code})")
-        raise _cabi.GateUpError(code, _cabi.error_string(code))
+    _raise_for(code)
 
 
 @torch.no_grad()
@@ -210,10 +214,7 @@ def run_fp8_output(x: torch.Tensor, scale_x: torch.Tensor, gate_proj_weight: tor
             x.data_ptr(), scale_x.data_ptr(), gate_proj_weight.data_ptr(), scale_gate.data_ptr(),
             up_proj_weight.data_ptr(), scale_up.data_ptr(), None, m, k, n, n, None, 0, PLAN_TILE, 0)
         code = _cabi.lib.gu_run_fp8out(ctypes.byref(pr), out_q.data_ptr(), out_scale.data_ptr(), stream_ptr)
-    if code != _cabi.GU_OK:
-        if code in (_cabi.GU_EINVAL_NULL, _cabi.GU_EINVAL_SHAPE, _cabi.GU_EINVAL_ALIGN):
-            raise ValueError(f"libgateup: {_cabi.error_string(code)} (code {code})")
-        raise _cabi.GateUpError(code, _cabi.error_string(code))
+    _raise_for(code)
 
 
 @torch.no_grad()
@@ -264,10 +265,7 @@ def blockwise_gemm(a: torch.Tensor, scale_a: torch.Tensor, b: torch.Tensor, scal
         stream_ptr = torch.cuda.current_stream(a.device).cuda_stream
         code = _cabi.lib.gu_blockwise_gemm(a.data_ptr(), scale_a.data_ptr(), b.data_ptr(), scale_b.data_ptr(),
                                            output.data_ptr(), m, k, n, output.stride(0), stream_ptr)
-    if code != _cabi.GU_OK:
-        if code in (_cabi.GU_EINVAL_NULL, _cabi.GU_EINVAL_SHAPE, _cabi.GU_EINVAL_ALIGN):
-            raise ValueError(f"libgateup: {_cabi.error_string(code)} (code {code})")
-        raise _cabi.GateUpError(code, _cabi.error_string(code))
+    _raise_for(code)
 
 
 @torch.no_grad()
@@ -295,10 +293,7 @@ def blockwise_gemm_scatter(a: torch.Tensor, scale_a: torch.Tensor, b: torch.Tens
         ptrs = (ctypes.c_void_p * world)(*[int(p) for p in rank_slot_ptrs])
         code = _cabi.lib.gu_blockwise_gemm_scatter(a.data_ptr(), scale_a.data_ptr(), b.data_ptr(),
                                                    scale_b.data_ptr(), ptrs, world, rank, m, k, n, stream_ptr)
-    if code != _cabi.GU_OK:
-        if code in (_cabi.GU_EINVAL_NULL, _cabi.GU_EINVAL_SHAPE, _cabi.GU_EINVAL_ALIGN):
-            raise ValueError(f"libgateup: {_cabi.error_string(code)} (code {code})")
-        raise _cabi.GateUpError(code, _cabi.error_string(code))
+    _raise_for(code)
 
 
 @torch.no_grad()
@@ -313,10 +308,7 @@ def reduce_gather(slots: torch.Tensor, rank_output_ptrs, rank: int, m: int, h: i
         stream_ptr = torch.cuda.current_stream(slots.device).cuda_stream
         ptrs = (ctypes.c_void_p * world)(*[(int(p) if p else None) for p in rank_output_ptrs])
         code = _cabi.lib.gu_reduce_gather(slots.data_ptr(), ptrs, world, rank, m, h, stream_ptr)
-    if code != _cabi.GU_OK:
-        if code in (_cabi.GU_EINVAL_NULL, _cabi.GU_EINVAL_SHAPE, _cabi.GU_EINVAL_ALIGN):
-            raise ValueError(f"libgateup: {_cabi.error_string(code)} (code {code})")
-        raise _cabi.GateUpError(code, _cabi.error_string(code))
+    _raise_for(code)
 
 
 @torch.no_grad()
@@ -347,10 +339,7 @@ def quantize_activation(x: torch.Tensor, q: Optional[torch.Tensor] = None,
         stream_ptr = torch.cuda.current_stream(x.device).cuda_stream
         code = _cabi.lib.gu_quantize_activation(x.data_ptr(), 1 if x.dtype == torch.float32 else 0, x.stride(0),
                                                 q.data_ptr(), scale.data_ptr(), m, k, stream_ptr)
-    if code != _cabi.GU_OK:
-        if code in (_cabi.GU_EINVAL_NULL, _cabi.GU_EINVAL_SHAPE, _cabi.GU_EINVAL_ALIGN):
-            raise ValueError(f"libgateup: {_cabi.error_string(code)} (code {code})")
-        raise _cabi.GateUpError(code, _cabi.error_string(code))
+    _raise_for(code)
     return q, scale
 
 
