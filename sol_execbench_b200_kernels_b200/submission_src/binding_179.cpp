@@ -45,6 +45,7 @@ torch::Tensor workspace_for(const torch::Tensor& like, cudaStream_t stream, size
 void run(const torch::Tensor& x, const torch::Tensor& scale_x, const torch::Tensor& gate_proj_weight,
          const torch::Tensor& scale_gate, const torch::Tensor& up_proj_weight, const torch::Tensor& scale_up,
          torch::Tensor output) {
+  TORCH_CHECK(x.is_cuda(), "x must be a CUDA tensor");
   c10::cuda::CUDAGuard guard(x.device());
   check_cuda_contiguous(x, "x", torch::kFloat8_e4m3fn, "float8_e4m3fn");
   check_cuda_contiguous(gate_proj_weight, "gate_proj_weight", torch::kFloat8_e4m3fn, "float8_e4m3fn");

@@ -144,3 +144,29 @@ def test_cli_package_and_summarize(tmp_path, capsys):
     assert summary.read_bytes() == open(os.path.join(GOLDEN, "trace_summary_expected.json"), "rb").read()
     assert S.main(["lint", str(tmp_path)]) == 1      # no manifest there
     capsys.readouterr()
+
+
+@pytest.mark.parametrize("problem,module", [("179", "submission_003_fp8_mlp_gate_up_projection"),
+                                            ("38", "submission_038_flux_multi_head_rmsnorm_qk"),
+                                            ("29", "submission_029_mamba_conv1d_with_gating")])
+def test_built_extensions_load_and_reject_host_tensors(problem, module):
+    """The torch extensions that `submission.build_extension` makes of the emitted directories (built beside the
+    tests by the repository's build entry point) import without a GPU and refuse CPU tensors before any CUDA call."""
+    import torch
+
+    so = os.path.join(ROOT, "tests", "_built_submissions", f"build_{problem}", module + ".so")
+    if not os.path.exists(so):
+        pytest.skip("the submission extensions are not built")
+    ext = S.load_extension(so)
+    bf = torch.bfloat16
+    if problem == "179":
+        x = torch.zeros(128, 128).to(torch.float8_e4m3fn)
+        args = (x, torch.zeros(128, 1), x, torch.zeros(1, 1), x, torch.zeros(1, 1), torch.zeros(128, 128, dtype=bf))
+    elif problem == "38":
+        q = torch.zeros(1, 2, 48, 128)
+        args = (q, q, torch.zeros(48, 128), torch.zeros(48, 128), 1e-6, q.clone(), q.clone())
+    else:
+        args = (torch.zeros(1, 4, 128, dtype=bf), torch.zeros(1, 4, dtype=bf), torch.zeros(128, 128, dtype=bf),
+                torch.zeros(128, dtype=bf), torch.zeros(64, 1, 4, dtype=bf), torch.zeros(64, dtype=bf))
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        ext.run(*args)
