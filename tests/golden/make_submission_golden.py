@@ -1,7 +1,7 @@
 """Generates the packaging fixtures in this directory with the reference's own tooling
 (tools/extra_kernels.py of a checkout of the reference repository, imported, not copied):
 
-* `toy_submission/solution.json` — a manifest in the reference's canonical byte form;
+* `toy_submission/manifest.compact.json` — a manifest (compact form; its canonical form is what gets packaged);
 * `toy_submission_artifact.sha256` — sha256 of the artifact the reference's `build_artifact` makes of it;
 * `traces_trial{1,2,3}.jsonl` + `trace_summary_expected.json` — seeded synthetic evaluator traces (16 workloads, the count the
   reference's lock file gives problem 29) and the summary the reference's `command_summarize` writes for them.
@@ -27,16 +27,30 @@ def main(reference_root: str) -> None:
     spec.loader.exec_module(ref)
 
     manifest = {
-        "author": "fixture", "definition": "000_toy_scale", "description": "Packaging fixture — not a kernel.",
-        "name": "toy_scale_v1", "sources": [{"path": "binding.cpp"}, {"path": "kernel.cu"}],
+        "author": "fixture", "definition": "000_toy_scale",
+        "description": "Packaging fixture — not a kernel. It exists so that the manifest rules, the forbidden-API audit, "
+                       "the embedding of several sources (two of them headers, one plain text, one with non-ASCII "
+                       "characters) and the canonical byte form can be checked against the reference's own packager "
+                       "without depending on any real kernel source, which changes from commit to commit.",
+        "name": "toy_scale_v1",
+        "sources": [{"path": "binding.cpp"}, {"path": "kernel.cu"}, {"path": "scale.h"}, {"path": "config.h"},
+                    {"path": "notes.txt"}],
         "spec": {"binding": "torch",
                  "compile_options": {"cflags": ["-O3"], "cuda_cflags": ["-O3", "-std=c++17"], "ld_flags": ["-lcuda"]},
                  "dependencies": [], "destination_passing_style": True, "entry_point": "binding.cpp::run",
                  "languages": ["cuda_cpp"], "target_hardware": ["B200", "LOCAL"]},
     }
-    (TOY / "solution.json").write_bytes(ref.canonical_json_bytes(manifest))
-    ref.ROOT = HERE
-    ref.variant_dir = lambda config, variant=None: TOY
+    # the manifest is kept in compact form beside the toy sources; the canonical `solution.json` the packager wants is
+    # written into a scratch copy (the tests do the same)
+    (TOY / "manifest.compact.json").write_text(json.dumps(manifest, separators=(",", ":"), ensure_ascii=False) + "\n",
+                                                encoding="utf-8")
+    import shutil
+    import tempfile
+    scratch = Path(tempfile.mkdtemp()) / "toy_submission"
+    shutil.copytree(TOY, scratch)
+    (scratch / "solution.json").write_bytes(ref.canonical_json_bytes(manifest))
+    ref.ROOT = scratch.parent
+    ref.variant_dir = lambda config, variant=None: scratch
     config = {"name": "000_toy_scale", "directory": "toy_submission"}
     ref.load_source_manifest(config)
     artifact = ref.build_artifact(config, "B200", None, ["-DFIXTURE=1"])

@@ -13,7 +13,18 @@ GOLDEN = os.path.join(ROOT, "tests", "golden")
 TOY = os.path.join(GOLDEN, "toy_submission")
 
 
-def test_toy_manifest_is_valid_and_packages_to_the_reference_artifact_bytes():
+@pytest.fixture()
+def toy(tmp_path):
+    """A scratch copy of the toy submission with its manifest written in canonical form as `solution.json`."""
+    d = tmp_path / "toy_submission"
+    shutil.copytree(TOY, d)
+    manifest = json.load(open(d / "manifest.compact.json", encoding="utf-8"))
+    (d / "solution.json").write_bytes(S.canonical_json_bytes(manifest))
+    return d
+
+
+def test_toy_manifest_is_valid_and_packages_to_the_reference_artifact_bytes(toy):
+    TOY = toy  # noqa: N806 - shadows the module constant on purpose
     manifest = S.validate(TOY, definition="000_toy_scale")
     assert manifest["spec"]["entry_point"] == "binding.cpp::run"
     data = S.package(TOY, "B200", ["-DFIXTURE=1"])
@@ -23,6 +34,7 @@ def test_toy_manifest_is_valid_and_packages_to_the_reference_artifact_bytes():
     assert art["spec"]["target_hardware"] == ["B200"]
     assert art["spec"]["compile_options"]["cuda_cflags"][-1] == "-DFIXTURE=1"
     assert all("content" in s for s in art["sources"]) and "µs → ok" in art["sources"][1]["content"]
+    assert [s["path"] for s in art["sources"]] == ["binding.cpp", "kernel.cu", "scale.h", "config.h", "notes.txt"]
     assert S.canonical_json_bytes(art) == data
 
 
@@ -73,6 +85,8 @@ def test_emitted_submissions_pass_the_manifest_rules(tmp_path, problem):
 def _toy_copy(tmp_path):
     d = tmp_path / "toy"
     shutil.copytree(TOY, d)
+    manifest = json.load(open(d / "manifest.compact.json", encoding="utf-8"))
+    (d / "solution.json").write_bytes(S.canonical_json_bytes(manifest))
     return d
 
 
@@ -117,8 +131,8 @@ def test_non_canonical_bytes_wrong_definition_and_forbidden_sources(tmp_path):
     (d / "solution.json").write_text(text.replace("  ", "    ", 1))
     with pytest.raises(S.SubmissionError, match="not canonical"):
         S.validate(d)
-    d2 = tmp_path / "second"
-    shutil.copytree(TOY, d2)
+    (tmp_path / "second_parent").mkdir()
+    d2 = _toy_copy(tmp_path / "second_parent")
     for fragment, category in (("cudaEventRecord(e, s);", "timing"), ("std::getenv(\"X\")", "process"),
                                ("usleep(5);", "delay"), ("cudaStreamCreate(&s);", "stream"),
                                ("std::thread t;", "thread"), ("#include <cupti.h>", "profiler")):
@@ -133,9 +147,9 @@ def test_package_sources_of_this_repository_are_audit_clean():
             S.audit_source(open(path).read(), f"{problem}:{name}")
 
 
-def test_cli_package_and_summarize(tmp_path, capsys):
+def test_cli_package_and_summarize(tmp_path, capsys, toy):
     out = tmp_path / "artifact.json"
-    assert S.main(["package", TOY, str(out), "--cuda-cflag=-DFIXTURE=1"]) == 0
+    assert S.main(["package", str(toy), str(out), "--cuda-cflag=-DFIXTURE=1"]) == 0
     assert S.sha256_bytes(out.read_bytes()) == open(os.path.join(GOLDEN, "toy_submission_artifact.sha256")).read().strip()
     summary = tmp_path / "summary.json"
     traces = [os.path.join(GOLDEN, f"traces_trial{t}.jsonl") for t in (1, 2, 3)]
