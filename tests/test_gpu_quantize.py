@@ -18,6 +18,10 @@ def _compare(x_cpu):
     assert q.dtype == torch.float8_e4m3fn and s.dtype == torch.float32
     assert torch.equal(s.cpu(), s_ref)
     assert torch.equal(q.cpu().view(torch.uint8), q_ref.view(torch.uint8))
+    # third statement of the same bytes: the integer restatement of the e4m3 rounding (numpy)
+    from oracle import quantize_oracle as Q
+    q_np, s_np = Q.quantize_activation_1x128(x_cpu.float().numpy())
+    assert (q.cpu().view(torch.uint8).numpy() == q_np).all() and (s.cpu().numpy() == s_np).all()
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])

@@ -123,3 +123,60 @@ def test_golden_fixtures(meta_path):
         st = O.error_stats(got, data["out"])
         assert st["rel_l2"] <= 1e-2, (name, st)
         assert st["frac_over_atol"] <= 1e-4, (name, st)
+
+
+# ---------------------------------------------------------------------------------------------
+# the quantiser's integer / byte restatement (numpy) against torch's cast and the torch quantiser
+# ---------------------------------------------------------------------------------------------
+def _torch_e4m3_bytes(values):
+    import numpy as np
+    return torch.from_numpy(np.asarray(values, dtype=np.float32)).to(torch.float8_e4m3fn).view(torch.uint8).numpy()
+
+
+def test_e4m3_encoding_restatement_equals_the_library_cast():
+    import numpy as np
+    from oracle import quantize_oracle as Q
+
+    # every bf16 value in range (both signs, zeros, subnormals of the target)
+    v = (np.arange(0, 1 << 16, dtype=np.uint32) << 16).view(np.float32)
+    v = v[np.isfinite(v) & (np.abs(v) <= 448)]
+    assert np.array_equal(Q.encode_e4m3fn(v), _torch_e4m3_bytes(v))
+    # all 256 bytes decode like the library type and encode back to themselves
+    codes = np.arange(256, dtype=np.uint8)
+    dec = Q.decode_e4m3fn(codes)
+    lib = torch.from_numpy(codes).view(torch.float8_e4m3fn).float().numpy()
+    assert np.array_equal(np.isnan(dec), np.isnan(lib)) and np.array_equal(dec[~np.isnan(dec)], lib[~np.isnan(lib)])
+    fin = ~np.isnan(dec)
+    assert np.array_equal(Q.encode_e4m3fn(dec[fin]), codes[fin])
+    # exact ties between neighbouring codes go to the even code
+    mag = dec[:0x7F].astype(np.float64)
+    ties = ((mag[:-1] + mag[1:]) / 2).astype(np.float32)
+    assert np.array_equal(Q.encode_e4m3fn(ties), _torch_e4m3_bytes(ties))
+    assert np.array_equal(Q.encode_e4m3fn(-ties), _torch_e4m3_bytes(-ties))
+    # random magnitudes over the whole range, NaN, saturation
+    rng = np.random.default_rng(0)
+    r = (rng.standard_normal(400_000) * rng.choice([1e-3, 0.02, 1.0, 50.0, 300.0], 400_000)).astype(np.float32)
+    r = np.clip(r, -448, 448)
+    assert np.array_equal(Q.encode_e4m3fn(r), _torch_e4m3_bytes(r))
+    special = np.array([np.nan, 1e9, -1e9, 463.9, 464.0, 448.0, -448.0], dtype=np.float32)
+    assert list(Q.encode_e4m3fn(special)) == [0x7F, 0x7E, 0xFE, 0x7E, 0x7E, 0x7E, 0xFE]
+
+
+@pytest.mark.parametrize("m,k", [(3, 128), (17, 384), (64, 1024)])
+def test_quantiser_restatement_equals_the_torch_quantiser(m, k):
+    import numpy as np
+    from oracle import quantize_oracle as Q
+
+    g = torch.Generator().manual_seed(m * k)
+    x = torch.randn(m, k, generator=g) * torch.rand(m, 1, generator=g) * 8
+    x[0, :128] = 0.0                                   # an all-zero block: scale = 1e-12 / 448
+    x[-1, 5] = 3e4
+    want_q, want_s = W.quantize_activation_1x128(x)
+    got_q, got_s = Q.quantize_activation_1x128(x.numpy())
+    assert np.array_equal(got_s, want_s.numpy())
+    assert np.array_equal(got_q, want_q.view(torch.uint8).numpy())
+    # bf16 activations are quantised from their exact fp32 values
+    xb = x.to(torch.bfloat16)
+    want_q, want_s = W.quantize_activation_1x128(xb.float())
+    got_q, got_s = Q.quantize_activation_1x128(xb.float().numpy())
+    assert np.array_equal(got_s, want_s.numpy()) and np.array_equal(got_q, want_q.view(torch.uint8).numpy())
