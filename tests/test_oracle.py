@@ -180,3 +180,63 @@ def test_quantiser_restatement_equals_the_torch_quantiser(m, k):
     want_q, want_s = W.quantize_activation_1x128(xb.float())
     got_q, got_s = Q.quantize_activation_1x128(xb.float().numpy())
     assert np.array_equal(got_s, want_s.numpy()) and np.array_equal(got_q, want_q.view(torch.uint8).numpy())
+
+
+# ---------------------------------------------------------------------------------------------
+# the plain C restatement (oracle/gateup_oracle.c): no tensor library underneath
+# ---------------------------------------------------------------------------------------------
+@pytest.fixture(scope="module")
+def c_oracle():
+    from oracle import build_c
+    return build_c.load()
+
+
+def _run_c(lib, inp):
+    m, k = inp.x.shape
+    n = inp.gate_proj_weight.shape[0]
+    out = torch.empty(m, n, dtype=torch.int16)
+    keep = [t.contiguous() for t in (inp.x.view(torch.uint8), inp.scale_x, inp.gate_proj_weight.view(torch.uint8),
+                                     inp.scale_gate, inp.up_proj_weight.view(torch.uint8), inp.scale_up)]
+    assert lib.gateup_oracle_c(*[t.data_ptr() for t in keep], out.data_ptr(), m, k, n) == 0
+    return out.view(torch.bfloat16)
+
+
+@pytest.mark.parametrize("shape", [(1, 128, 128), (16, 256, 256), (40, 512, 384), (129, 384, 256)])
+def test_c_restatement_equals_the_block_ordered_oracle(c_oracle, shape):
+    inp = W.make_inputs(*shape, seed=3)
+    got = _run_c(c_oracle, inp)
+    want = O.gateup_blockwise(*inp.args())
+    # same order, same rounding boundaries; the sigmoid comes from libm here and from torch there, so a rounding
+    # to bf16 may, rarely, fall the other way
+    diff = (got.float() - want.float()).abs()
+    assert int((diff > 0).sum()) <= max(1, 1e-4 * got.numel())
+    assert O.error_stats(got, want)["rel_l2"] <= 1e-4
+    st = O.error_stats(got, O.gateup_dequant(*inp.args()))
+    assert st["rel_l2"] <= 1e-2 and st["frac_over_atol"] <= 1e-4
+
+
+def test_c_restatement_of_the_single_gemm(c_oracle):
+    inp = W.make_inputs(24, 384, 256, seed=8)
+    out = torch.empty(24, 256, dtype=torch.int16)
+    keep = [inp.x.view(torch.uint8).contiguous(), inp.scale_x, inp.gate_proj_weight.view(torch.uint8).contiguous(),
+            inp.scale_gate]
+    assert c_oracle.gemm_oracle_c(*[t.data_ptr() for t in keep], out.data_ptr(), 24, 384, 256) == 0
+    want = O.gemm_blockwise(inp.x, inp.scale_x, inp.gate_proj_weight, inp.scale_gate)
+    assert torch.equal(out.view(torch.bfloat16), want)
+    assert c_oracle.gemm_oracle_c(*[t.data_ptr() for t in keep], out.data_ptr(), 24, 100, 256) == -1
+
+
+@pytest.mark.parametrize("name", ["ref_square_128x512x512", "ref_256x1024x1024"])
+def test_c_restatement_against_reference_kernel_outputs(c_oracle, name):
+    """The same fixtures as above (outputs of the reference's own GPU kernel), against the C statement."""
+    meta_path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", name + ".json")
+    if not os.path.exists(meta_path):
+        pytest.skip("fixture not committed")
+    with open(meta_path) as f:
+        meta = json.load(f)
+    data = torch.load(meta_path[:-5] + ".pt", weights_only=True)
+    m, k, n = meta["shape"]
+    inp = W.make_inputs(m, k, n, seed=meta["seed"])
+    got = _run_c(c_oracle, inp.rows(data["rows"]))[:, data["cols"]]
+    st = O.error_stats(got, data["out"])
+    assert st["rel_l2"] <= 1e-4 and st["frac_over_atol"] <= 1e-4, st
