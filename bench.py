@@ -44,9 +44,23 @@ def flush_l2(buf: torch.Tensor) -> None:
     buf.zero_()
     buf.sum()
 
-# Measured DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum from the ncu
-# captures summarised under profiles/), keyed by workload; None until a capture exists.
-NCU_TRAFFIC_BYTES = {"prefill_8b": 227_744_256, "decode_70b": 477_501_184}
+def ncu_traffic_bytes(workload: str):
+    """DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernel on `workload`,
+    as recorded by the ncu summary committed under profiles/ (a line `traffic_bytes[<workload>] = <integer>`);
+    None when no capture of that workload is on record."""
+    import glob
+    import re
+
+    pat = re.compile(r"traffic_bytes\[" + re.escape(workload) + r"\]\s*=\s*(\d+)")
+    for path in sorted(glob.glob(os.path.join(ROOT, "profiles", "*.md"))):
+        try:
+            with open(path) as f:
+                hit = pat.search(f.read())
+        except OSError:
+            continue
+        if hit:
+            return int(hit.group(1))
+    return None
 
 
 def load_peaks():
@@ -176,6 +190,79 @@ def cpu_baseline(inp_cpu, oracle, max_flops: float = 2.0e12):
     }
 
 
+def parity_of(out, inp, W, oracle, label):
+    """Sampled parity of a device result against both CPU restatements (16 token rows x 3 column blocks of 128):
+    the numbers the tolerance of the path is stated in (max-abs 2e-2, relative L2 1e-2 on the bf16 output)."""
+    m, k, n = inp.shape
+    dev = out.device
+    rows = torch.arange(0, m, max(1, m // 16), device=dev)[:16]
+    nb = n // 128
+    blocks = torch.tensor(sorted({0, nb // 2, nb - 1}), device=dev)
+    sub = inp.rows(rows).column_blocks(blocks).to("cpu")
+    cols = (blocks[:, None] * 128 + torch.arange(128, device=dev)[None]).reshape(-1)
+    got = out[rows][:, cols].cpu()
+    res = {"config": label, "sample": f"{len(rows)} token rows x {len(blocks)} column blocks of 128", "atol": 2e-2}
+    for name, fn in (("gateup_dequant", oracle.gateup_dequant), ("gateup_blockwise", oracle.gateup_blockwise)):
+        st = oracle.error_stats(got, fn(*sub.args()))
+        entry = {"max_abs": round(st["max_abs"], 6), "rel_l2": float(f"{st['rel_l2']:.3e}"),
+                 "n_over_atol": st["n_over_atol"], "frac_over_atol": st["frac_over_atol"],
+                 "max_ulp_over": st["max_ulp_over"]}
+        if name == "gateup_dequant":
+            res.update(entry)
+            res["vs"] = name
+        else:
+            entry["bit_equal"] = bool(torch.equal(got, fn(*sub.args()).to(torch.bfloat16)))
+            res["vs_" + name] = entry
+    return res
+
+
+def sustained_leg(fn, flops, peaks, gpu_index, seconds=2.5):
+    """The same launch back to back for `seconds` (no flush: the operands exceed L2), CUDA events around the whole
+    run, against twice the measured SUSTAINED bf16 rate; the median SM clock under load is sampled beside it."""
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(20):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    count = max(50, int(seconds * 1e3 / max(a.elapsed_time(b) / 20, 1e-3)))
+    with ClockSampler(gpu_index) as clocks:
+        a.record()
+        for _ in range(count):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / count
+    peak = 2.0 * peaks.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"])
+    ach = flops / (ms * 1e-3) / 1e12
+    c = clocks.summary()
+    return {"launches": count, "seconds": round(ms * count * 1e-3, 3), "ms_per_step": round(ms, 5),
+            "tflops": round(ach, 2), "peak": round(peak, 1), "frac": round(ach / peak, 4),
+            "peak_source": "2 x bf16_tflops_sustained, " + ("of measured" if peaks["_source"] == "measured" else "of fallback"),
+            "clocks": c, "ms_x_mhz": round(ms * c["sm_mhz"], 2) if c.get("sm_mhz") else None}
+
+
+def pcie_rates(dev, nbytes=64 << 20):
+    """Pinned-host copy bandwidth each way (GB/s), the ceiling of the end-to-end leg."""
+    host = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+    devb = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    res = {}
+    for name, (dst, src) in {"h2d_gbs": (devb, host), "d2h_gbs": (host, devb)}.items():
+        dst.copy_(src, non_blocking=True)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(3):
+            dst.copy_(src, non_blocking=True)
+        b.record()
+        torch.cuda.synchronize()
+        res[name] = round(3 * nbytes / (a.elapsed_time(b) * 1e-3) / 1e9, 1)
+    return res
+
+
 def run_sweep(args):
     """M sweep at K=4096, N=14336: every plan that can run each M, the heuristic's pick and the roofline fraction."""
     import sol_execbench_b200_kernels_b200 as pkg
@@ -191,7 +278,8 @@ def run_sweep(args):
         inp = W.make_inputs(m, k, n, seed=0, device=dev)
         out = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
         entry = {"m": m, "auto_plan": pkg.select_plan(m, k, n), "plans": {}}
-        for plan in (("stream", "tile") if m <= 64 else ("tile",)):
+        # "tile" is the heuristic's tile kernel (CTA pairs above 128 tokens), "tile_dp" the lone-CTA kernel forced
+        for plan in (("stream", "tile") if m <= 64 else (("tile",) if m <= 128 else ("tile", "tile_dp"))):
             ms, _ = time_device_steps(lambda: pkg.run_with_plan(*inp.args(), out, plan), args.steps, args.warmup, flush)
             ms /= args.steps
             roof = roofline_for(m, k, n, ms, peaks, W)
@@ -299,7 +387,7 @@ def run_ours(args):
     torch.cuda.synchronize()
     if barrier:
         barrier()
-    e2e_steps = max(3, min(args.steps, 10))
+    e2e_steps = max(30, args.steps)
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
         e2e_step()
@@ -310,17 +398,46 @@ def run_ours(args):
     if n_gpus > 1:
         dist.all_reduce(te, op=dist.ReduceOp.MAX)
     e2e_s = float(te.item())
+    pcie = pcie_rates(dev)
+    # what the copies alone allow: both directions run at once, so the slower of the two bounds a step
+    copy_s = max(pipe.bytes_h2d / (pcie["h2d_gbs"] * 1e9), pipe.bytes_d2h / (pcie["d2h_gbs"] * 1e9))
     e2e = {"value": round(flops_job / (e2e_s / e2e_steps) / 1e12, 3), "unit": "TFLOP/s",
            "h2d_bytes_per_step": pipe.bytes_h2d, "d2h_bytes_per_step": pipe.bytes_d2h, "steps": e2e_steps,
-           "matches_device_run": e2e_ok,
+           "ms_per_step": round(e2e_s / e2e_steps * 1e3, 4), "matches_device_run": e2e_ok,
+           "pcie": {**pcie, "copy_bound_ms": round(copy_s * 1e3, 4),
+                    "ceiling": round(flops_job / max(copy_s, ms_per_step * 1e-3) / 1e12, 1),
+                    "note": "ceiling = the metric if a step took only the slower of its host copies (or the kernel)"},
            "note": "HostPipeline.run: weights resident in HBM; x and scale_x copied from pinned host memory and the "
                    f"bf16 output copied back to pinned host memory every step, in {len(pipe.bounds)} row chunks on three streams; "
                    "wall clock"}
 
     result = None
+    parity = None
+    if rank == 0 and buffers is None:
+        from oracle import gateup_oracle as oracle  # checker only: parity of the timed configuration
+
+        step()
+        torch.cuda.synchronize()
+        parity = parity_of(out, local, W, oracle, f"{workload}" + (f", rank 0 shard of {n_gpus}" if n_gpus > 1 else ""))
+    scaling_base = None
+    if n_gpus > 1 and not (args.gather or args.fused_gather):
+        # the same workload, unsharded, on rank 0's GPU in this very run: the base the N-GPU value is compared with
+        if rank == 0:
+            whole = W.make_inputs(m, k, n, seed=0, device=dev)
+            wout = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+            bsteps = 5
+            bms, _ = time_device_steps(lambda: pkg.run(*whole.args(), wout), bsteps, 3, flush)
+            base_ms = bms / bsteps
+            base_tf = flops_job / (base_ms * 1e-3) / 1e12
+            scaling_base = {"workload": f"{workload}: M={m} K={k} N={n}, unsharded on one GPU (rank 0, same run)",
+                            "one_gpu_ms": round(base_ms, 5), "one_gpu_tflops": round(base_tf, 2), "steps": bsteps,
+                            "efficiency": round(value / (n_gpus * base_tf), 4)}
+            del whole, wout
+            torch.cuda.empty_cache()
+        dist.barrier()
     if rank == 0:
         roof = roofline_for(m, k, n_local, ms_per_step, peaks, W)
-        roof["traffic"] = NCU_TRAFFIC_BYTES.get(workload)
+        roof["traffic"] = ncu_traffic_bytes(workload)
         result = {
             "metric": METRIC, "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": n_gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 5),
@@ -331,11 +448,17 @@ def run_ours(args):
                        "gather": "fused peer stores" if buffers is not None else ("nccl" if gathered is not None else False),
                        "l2": f"flushed before every timed step by writing, then reading back, a {L2_FLUSH_BYTES >> 20} MiB buffer"},
             "roofline": roof, "e2e": e2e, "gpu_launches": launches_timed,
-            "clocks": clocks.summary(),
+            "clocks": clocks.summary(), "parity": parity,
         }
+        if scaling_base is not None:
+            result["scaling_base"] = scaling_base
 
     # ---- decode shape (HBM-bound) and CPU baseline: rank 0, single-GPU runs only ----
     if n_gpus == 1 and not args.workload:
+        from oracle import gateup_oracle as oracle  # checker and CPU baseline legs: the only uses of it here
+
+        result["also"] = [{"workload": f"{workload} back to back (sustained)",
+                           **sustained_leg(step, flops_job, peaks, local_rank)}]
         dm, dk, dn = W.SHAPES["decode_70b"]
         del local, out, pipe
         torch.cuda.empty_cache()
@@ -344,12 +467,12 @@ def run_ours(args):
         dsteps = max(args.steps, 20)
         dms, _ = time_device_steps(lambda: pkg.run(*dec.args(), dout), dsteps, max(args.warmup, 3), flush)
         droof = roofline_for(dm, dk, dn, dms / dsteps, peaks, W)
-        droof["traffic"] = NCU_TRAFFIC_BYTES.get("decode_70b")
-        result["also"] = [{
+        droof["traffic"] = ncu_traffic_bytes("decode_70b")
+        result["also"].append({
             "workload": f"decode_70b: M={dm} K={dk} N={dn}", "plan": pkg.select_plan(dm, dk, dn),
             "ms_per_step": round(dms / dsteps, 5), "steps": dsteps,
             "tflops": round(W.algorithmic_flops(dm, dk, dn) / (dms / dsteps * 1e-3) / 1e12, 2),
-            "roofline": droof}]
+            "roofline": droof, "parity": parity_of(dout, dec, W, oracle, "decode_70b")})
         del dec, dout
         torch.cuda.empty_cache()
         sm_, sk_, sn_ = W.SHAPES["prefill_sharded"]
@@ -409,8 +532,6 @@ def run_ours(args):
             "tflops": round(bfl / (bms / gsteps * 1e-3) / 1e12, 2)})
         del blk, dq, dsc, mid_q, mid_s, yout, xb
         torch.cuda.empty_cache()
-        from oracle import gateup_oracle as oracle  # CPU baseline leg: the only use of the checker here
-
         cpu_inp = W.make_inputs(m, k, n, seed=0, device="cpu")
         result["cpu_baseline"] = cpu_baseline(cpu_inp, oracle)
     if rank == 0:
@@ -430,6 +551,8 @@ def run_reference(args):
     from oracle import gateup_oracle as oracle
     from sol_execbench_b200_kernels_b200 import workloads as W
 
+    # a launcher for several ranks pins every rank to one OpenMP thread; this arm is the host cores' number
+    torch.set_num_threads(os.cpu_count() or 1)
     n_gpus = max(world, args.gpus)
     workload = args.workload or ("prefill_8b" if n_gpus == 1 else "prefill_sharded")
     m, k, n = W.SHAPES[workload]
@@ -445,6 +568,20 @@ def run_reference(args):
     value = 4.0 * rows * k * n / dt / 1e12
     sample = (f"{rows} token rows of {workload} (M={m}, K={k}, N={n}) per step; weights dequantised inside every "
               f"step as the CPU definition does; throughput is per-row-proportional for the matmul part")
+    # The reference itself has no CPU code for this path (its CPU definition lives in a dataset that is fetched at
+    # set-up); what it does ship is a single-GPU kernel.  Where that kernel can run (one GPU, the reference copy
+    # present) its time on this box is reported beside the CPU number, measured in a child process.
+    reference_gpu = {"unavailable": "the reference is single-GPU"}
+    if n_gpus == 1:
+        if not torch.cuda.is_available():
+            reference_gpu = {"unavailable": "no CUDA device"}
+        elif not os.path.exists(os.path.join(REF_KERNEL_DIR, "kernel.py")):
+            reference_gpu = {"unavailable": "no copy of the reference's kernel directory on this machine"}
+        else:
+            rows, failures = ref_gpu_groups(["prefill_8b"] if workload == "prefill_8b" else [], 10, 3, timeout_s=420)
+            reference_gpu = rows[0] if rows else {"unavailable": "; ".join(failures) or f"no group for {workload}"}
+            reference_gpu["what"] = ("the reference's kernel.py::run (two CuTe-DSL GEMMs + Triton SwiGLU) and this "
+                                     "library timed alternately on the same operands, CUDA events, L2 flushed")
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": round(value, 4), "unit": "TFLOP/s", "n_gpus": n_gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True,
@@ -453,8 +590,161 @@ def run_reference(args):
         "cpu_baseline": {"value": round(value, 4), "unit": "TFLOP/s", "cores": torch.get_num_threads(),
                          "host_cpus": os.cpu_count(), "kind": "port", "sample": sample},
         "e2e": {"value": round(value, 4), "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "gpu_launches": 0,
+        "gpu_launches": 0, "reference_gpu": reference_gpu,
     }), flush=True)
+
+
+# --------------------------------------------------------------------------------------
+# same-harness GPU comparison with the reference's own default variant (one GPU only)
+# --------------------------------------------------------------------------------------
+REF_KERNEL_DIR = os.path.join(ROOT, "baseline", "_ref", "179_fp8_mlp_gate_up_projection")
+# the M values of the reference's own micro-benchmark at its native K = 3584, N = 18944 (tools/bench_179_epilogue.py:15-16)
+REF_NATIVE_M = (384, 512, 768, 1152, 1280, 1792, 2048, 2304, 2816, 3072, 3584, 3840, 5120, 5632, 6144, 8704)
+REF_GPU_GROUPS = {"prefill_8b": (4096, 14336, (4096,)), "reference_native": (3584, 18944, REF_NATIVE_M)}
+
+
+def _load_reference_kernel():
+    """The unmodified kernels/179_fp8_mlp_gate_up_projection/kernel.py of the reference, from the git-ignored copy
+    under baseline/_ref (it loads NVIDIA's CuTe-DSL blockwise GEMM example from $CUTLASS_DIR: the image's tree)."""
+    import importlib.util
+
+    path = os.path.join(REF_KERNEL_DIR, "kernel.py")
+    if not os.path.exists(path):
+        raise FileNotFoundError(f"{os.path.relpath(path, ROOT)} is not on this machine")
+    fi = importlib.util.find_spec("flashinfer")
+    if fi is None:
+        raise FileNotFoundError("no CUTLASS tree on this machine (flashinfer's vendored copy)")
+    os.environ.setdefault("CUTLASS_DIR", os.path.join(os.path.dirname(fi.origin), "data", "cutlass"))
+    spec = importlib.util.spec_from_file_location("_reference_179_kernel", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def run_ref_gpu_one(args):
+    """Child of --ref-gpu: one (K, N) per process, because the reference caches its compiled kernel under a key
+    that omits K and N (kernel.py:263).  Times the reference's `run` (kernel.py:398-503: two CuTe-DSL GEMMs + a
+    Triton SwiGLU) and this library's `run` alternately on the same operands, same L2 flush, same CUDA events."""
+    import sol_execbench_b200_kernels_b200 as pkg
+    from sol_execbench_b200_kernels_b200 import workloads as W
+
+    k, n, ms_list = args.ref_gpu_one.split(",")
+    k, n = int(k), int(n)
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    ref = _load_reference_kernel()
+    flush = torch.empty(L2_FLUSH_BYTES // 4, dtype=torch.float32, device=dev)
+    rows = []
+    for m in (int(v) for v in ms_list.split(":")):
+        inp = W.make_inputs(m, k, n, seed=0, device=dev)
+        out_ref = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+        out_own = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+        fns = {"reference": lambda: ref.run(*inp.args(), out_ref), "this_library": lambda: pkg.run(*inp.args(), out_own)}
+        for fn in fns.values():
+            for _ in range(max(3, args.warmup)):
+                fn()
+        torch.cuda.synchronize()
+        times = {name: [] for name in fns}
+        for _ in range(args.steps):
+            for name, fn in fns.items():
+                flush_l2(flush)
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                fn()
+                b.record()
+                torch.cuda.synchronize()
+                times[name].append(a.elapsed_time(b))
+        med = {name: sorted(t)[len(t) // 2] for name, t in times.items()}
+        diff = (out_ref.float() - out_own.float()).abs()
+        flops = W.algorithmic_flops(m, k, n)
+        rows.append({"m": m, "k": k, "n": n, "reference_ms": round(med["reference"], 5),
+                     "this_library_ms": round(med["this_library"], 5),
+                     "reference_tflops": round(flops / (med["reference"] * 1e-3) / 1e12, 1),
+                     "this_library_tflops": round(flops / (med["this_library"] * 1e-3) / 1e12, 1),
+                     "speedup": round(med["reference"] / med["this_library"], 3),
+                     "max_abs_between": float(diff.max()), "frac_bit_equal": float((out_ref == out_own).float().mean())})
+        del inp, out_ref, out_own
+        torch.cuda.empty_cache()
+    code, detail = pkg.last_status()
+    print(json.dumps({"k": k, "n": n, "rows": rows, "device_status": code}), flush=True)
+
+
+def ref_gpu_groups(groups, steps, warmup, timeout_s=900):
+    """Runs run_ref_gpu_one in a child process per (K, N); returns (rows, failures)."""
+    rows, failures = [], []
+    for name in groups:
+        k, n, ms = REF_GPU_GROUPS[name]
+        cmd = [sys.executable, os.path.abspath(__file__), "--ref-gpu-one", f"{k},{n},{':'.join(map(str, ms))}",
+               "--steps", str(steps), "--warmup", str(warmup)]
+        try:
+            proc = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout_s)
+            line = [l for l in proc.stdout.splitlines() if l.startswith("{")]
+            if proc.returncode != 0 or not line:
+                tail = (proc.stderr or proc.stdout).strip().splitlines()[-1:] or ["no output"]
+                failures.append(f"{name}: exit {proc.returncode}: {tail[0][:200]}")
+                continue
+            rows += json.loads(line[-1])["rows"]
+        except subprocess.TimeoutExpired:
+            failures.append(f"{name}: no result within {timeout_s} s")
+    return rows, failures
+
+
+def run_ref_gpu(args):
+    """Study line: the reference's default variant against this library on one B200, same harness, on prefill_8b
+    and on the reference's native shape over its own list of M."""
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1 or args.gpus > 1:
+        raise SystemExit("bench.py --ref-gpu: one GPU only (the reference is single-GPU)")
+    rows, failures = ref_gpu_groups(list(REF_GPU_GROUPS), max(5, min(args.steps, 10)), args.warmup)
+    print(json.dumps({"study": "reference default variant (kernel.py::run) against this library, one B200, CUDA events, "
+                               f"L2 flushed (write then read of {L2_FLUSH_BYTES >> 20} MiB) before every timed call, medians",
+                      "rows": rows, "failures": failures}), flush=True)
+
+
+def run_trace(args):
+    """Study line: where the roles of the CTA-pair kernel spend their time.  Needs the library built with
+    -DGU_TRACE (`python -m sol_execbench_b200_kernels_b200.build --trace`, or --lib for another study build);
+    prints, per K block and for the first CTA pair, the cycles each role waited for the others, and the time
+    stamps of sixteen consecutive K blocks of the first tile (issuer and one consumer warp)."""
+    import ctypes
+
+    import sol_execbench_b200_kernels_b200 as pkg
+    from sol_execbench_b200_kernels_b200 import _cabi
+    from sol_execbench_b200_kernels_b200 import workloads as W
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    workload = args.workload or "prefill_8b"
+    m, k, n = W.SHAPES[workload]
+    inp = W.make_inputs(m, k, n, seed=0, device=dev)
+    out = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+    flush = torch.empty(L2_FLUSH_BYTES // 4, dtype=torch.float32, device=dev)
+    buf = (ctypes.c_uint64 * 288)()
+    for _ in range(3):
+        pkg.run_with_plan(*inp.args(), out, "tile_pair")
+    torch.cuda.synchronize()
+    _cabi.lib.gu_trace_read(buf, 288, 1)
+    total_ms, _ = time_device_steps(lambda: pkg.run_with_plan(*inp.args(), out, "tile_pair"), args.steps, 0, flush)
+    words = _cabi.lib.gu_trace_read(buf, 288, 1)
+    if words < 288:
+        raise SystemExit("bench.py --trace: this library was built without -DGU_TRACE (see --lib)")
+    names = ["producer_wait_slot", "issuer_wait_operands_and_stage", None, "consumer_wait_partial", None, "consumer_k_loop",
+             "consumer_hand_over", "epilogue_busy", "epilogue_wait", "cta_total", "k_blocks"]
+    roles = {}
+    for r in range(2):
+        v = [int(buf[16 * r + i]) for i in range(11)]
+        kbn = max(v[10], 1)
+        roles[f"cta{r}"] = {nm: round(x / kbn, 1) for nm, x in zip(names, v) if nm and nm != "k_blocks"}
+    ev = lambda r, role, i: int(buf[32 + (r * 2 + role) * 64 + i])
+    base = ev(0, 0, 0)
+    stamps = [{"k_block": 8 + i,
+               "issuer_polls_passed": ev(0, 0, 4 * i) - base, "issuer_mmas_issued": ev(0, 0, 4 * i + 2) - base,
+               "issuer_commits_issued": ev(0, 0, 4 * i + 3) - base, "consumer_partial_seen": ev(0, 1, 4 * i) - base,
+               "consumer_stage_handed_back": ev(0, 1, 4 * i + 3) - base} for i in range(16)]
+    print(json.dumps({"study": "CTA-pair kernel: cycles per K block each role of the first pair spent (trace build; the "
+                               "counters cost the traced threads some cycles themselves)",
+                      "workload": f"{workload}: M={m} K={k} N={n}", "ms_per_step": round(total_ms / args.steps, 5),
+                      "steps": args.steps, "cycles_per_k_block": roles,
+                      "time_stamps_even_cta_cycles": stamps}), flush=True)
 
 
 def run_mlp(args):
@@ -606,9 +896,27 @@ def main():
     ap.add_argument("--side", action="store_true",
                     help="one GPU: the side operators (RMSNorm of query/key, Mamba conv1d tail) against the HBM roofline")
     ap.add_argument("--sweep", action="store_true", help="M sweep at K=4096, N=14336 on one GPU (plan crossover study)")
+    ap.add_argument("--ref-gpu", action="store_true",
+                    help="one GPU: the reference's default variant against this library, same harness (needs baseline/_ref)")
+    ap.add_argument("--ref-gpu-one", default=None, help=argparse.SUPPRESS)
+    ap.add_argument("--trace", action="store_true", help="one GPU: role counters of the CTA-pair kernel (trace build)")
+    ap.add_argument("--lib", default=None,
+                    help="study runs: load this build of the library (e.g. libgateup_trace.so) instead of libgateup.so")
     args = ap.parse_args()
+    if args.lib or args.trace:
+        from pathlib import Path
+
+        import sol_execbench_b200_kernels_b200.build as _build
+
+        _build.LIB_PATH = Path(args.lib).resolve() if args.lib else _build.TRACE_LIB_PATH
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
-    if args.impl == "reference":
+    if args.trace:
+        run_trace(args)
+    elif args.ref_gpu_one:
+        run_ref_gpu_one(args)
+    elif args.ref_gpu:
+        run_ref_gpu(args)
+    elif args.impl == "reference":
         run_reference(args)
     elif args.mlp:
         run_mlp(args)

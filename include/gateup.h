@@ -41,10 +41,11 @@ extern "C" {
 
 /* plans */
 #define GU_PLAN_AUTO 0    /* shape heuristic (gu_select_plan)                                      */
-#define GU_PLAN_TILE 1    /* persistent 128 x (128 gate + 128 up) tiles; any M; schedule by tile count */
+#define GU_PLAN_TILE 1    /* persistent tiles of both projections; any M; CTA pairs above 128 tokens    */
 #define GU_PLAN_STREAM 2  /* weight-streaming, tokens on the MMA N side, stream-K over (N-block, K-block); M <= 64 */
-#define GU_PLAN_TILE_DP 3 /* tile kernel, data-parallel schedule forced (whole tiles per CTA, no scratch)    */
-#define GU_PLAN_TILE_SK 4 /* tile kernel, stream-K schedule forced (needs scratch)                           */
+#define GU_PLAN_TILE_DP 3 /* lone-CTA tile kernel, data-parallel schedule forced (whole tiles per CTA, no scratch) */
+#define GU_PLAN_TILE_SK 4 /* lone-CTA tile kernel, stream-K schedule forced (needs scratch)                  */
+#define GU_PLAN_TILE_PAIR 5      /* CTA-pair tile kernel forced (256-token tiles, cta_group::2), any M        */
 
 /*
  * One call's operands.  Replaces the seven tensors of the reference `run`
@@ -227,6 +228,34 @@ int gu_run_decode_static(const gu_problem* problem, void* stream);
 
 /* Kernel launches issued by this library in this process so far. */
 int64_t gu_launch_count(void);
+
+/*
+ * Time limit of every bounded device-side wait on the current device, in nanoseconds (default 2 s; 0 restores
+ * the default).  A wait that runs out records (wait id, block) for gu_last_status, the kernel's roles skip the
+ * rest of their device work and the launch returns; nothing traps.  The reference has no counterpart: its
+ * cluster wait spins without bound (variants/cute_fused_v1/blockwise_gemm_fused.py:85-91).  Synchronous copy of
+ * one word to the device; set it while no launch of this library is in flight.
+ */
+int gu_set_wait_limit_ns(uint64_t ns);
+
+/*
+ * Self-test of the bounded-wait protocol: launches one CTA whose only wait is on a barrier nothing ever arrives
+ * on.  It returns after the wait limit (lower it first with gu_set_wait_limit_ns: the default is 2 s); afterwards
+ * gu_last_status reports GU_ETIMEOUT with wait id 31, and the context stays usable.  Nothing traps or faults, no
+ * copy or MMA is in flight.  No counterpart in the reference.
+ */
+int gu_wait_probe(void* stream);
+
+/*
+ * Cycle counters of the CTA-pair kernel's roles (what each role of the first CTA pair spent waiting for the
+ * others, summed over the launches since the last clear).  Only a library built with -DGU_TRACE fills them;
+ * the regular build returns 0 and writes nothing.  Copies up to `capacity` 64-bit words to `out` (layout:
+ * [2 CTAs][16 slots] of summed cycles, then [2 CTAs][2 roles][64] time stamps of sixteen K blocks of the first
+ * tile; all named in csrc/gateup_pair.cuh), returns the number of words written (at most 288) or a negative
+ * code; `clear` != 0 zeroes the counters afterwards.  Synchronises the device.  Profiling aid with no
+ * counterpart in the reference.
+ */
+int gu_trace_read(uint64_t* out, int capacity, int clear);
 
 #ifdef __cplusplus
 }

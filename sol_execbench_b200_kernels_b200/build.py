@@ -15,8 +15,10 @@ PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 LIB_PATH = PKG_DIR / "libgateup.so"
 SOURCES = [CSRC / "gateup.cu"]
-HEADERS = [CSRC / "ptx_sm100.cuh", CSRC / "gateup_tile.cuh", CSRC / "gateup_stream.cuh", CSRC / "quantize_act.cuh", CSRC / "reduce_gather.cuh",
-           PKG_DIR.parent / "include" / "gateup.h"]
+HEADERS = [CSRC / "ptx_sm100.cuh", CSRC / "gateup_tile.cuh", CSRC / "gateup_pair.cuh", CSRC / "gateup_stream.cuh",
+           CSRC / "quantize_act.cuh", CSRC / "reduce_gather.cuh", PKG_DIR.parent / "include" / "gateup.h"]
+# the same library with the pair kernel's per-role cycle counters compiled in (gu_trace_read); a profiling aid
+TRACE_LIB_PATH = PKG_DIR / "libgateup_trace.so"
 
 SIDE_LIB_PATH = PKG_DIR / "libsideops.so"
 SIDE_SOURCES = [CSRC / "sideops.cu"]
@@ -48,8 +50,8 @@ def is_stale() -> bool:
     return _stale(LIB_PATH, SOURCES + HEADERS) or _stale(SIDE_LIB_PATH, SIDE_SOURCES + SIDE_HEADERS)
 
 
-def _compile(lib: Path, sources, verbose: bool) -> None:
-    cmd = [find_nvcc(), *NVCC_FLAGS]
+def _compile(lib: Path, sources, verbose: bool, defines=()) -> None:
+    cmd = [find_nvcc(), *NVCC_FLAGS, *[f"-D{d}" for d in defines]]
     if verbose:
         cmd += ["-Xptxas", "-v"]
     cmd += ["-o", str(lib), *map(str, sources)]
@@ -69,5 +71,25 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     return LIB_PATH
 
 
+def build_trace(force: bool = False, verbose: bool = False) -> Path:
+    """Compile libgateup_trace.so (-DGU_TRACE): same entry points, cycle counters of the pair kernel's roles."""
+    if force or _stale(TRACE_LIB_PATH, SOURCES + HEADERS):
+        _compile(TRACE_LIB_PATH, SOURCES, verbose, defines=("GU_TRACE",))
+    return TRACE_LIB_PATH
+
+
+def build_study(name: str, defines, verbose: bool = False) -> Path:
+    """Compile libgateup_<name>.so with extra -D switches (the study builds listed in csrc/gateup_pair.cuh)."""
+    lib = PKG_DIR / f"libgateup_{name}.so"
+    _compile(lib, SOURCES, verbose, defines=tuple(defines))
+    return lib
+
+
 if __name__ == "__main__":
+    # python -m sol_execbench_b200_kernels_b200.build [--force] [-v] [--trace] [--study NAME DEFINE[,DEFINE...]]
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    if "--trace" in sys.argv:
+        print(build_trace(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    if "--study" in sys.argv:
+        at = sys.argv.index("--study")
+        print(build_study(sys.argv[at + 1], sys.argv[at + 2].split(","), verbose="-v" in sys.argv))

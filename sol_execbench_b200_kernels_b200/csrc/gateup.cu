@@ -12,6 +12,7 @@
 
 #include "../../include/gateup.h"
 #include "gateup_stream.cuh"
+#include "gateup_pair.cuh"
 #include "gateup_tile.cuh"
 #include "quantize_act.cuh"
 #include "reduce_gather.cuh"
@@ -95,6 +96,7 @@ struct DeviceInfo {
   int sm_count = 0;
   int cc_major = 0;
   int max_smem_optin = 0;
+  int pair_clusters = 0;  // CTA pairs of the pair kernel that are resident at once (0: pairs cannot be launched)
   bool attrs_set = false;
 };
 DeviceInfo g_dev[64];
@@ -131,14 +133,55 @@ int device_info(DeviceInfo** out) {
         cudaFuncSetAttribute(gateup_stream_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
             cudaSuccess ||
         cudaFuncSetAttribute(gateup_stream_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
-            cudaSuccess) {
+            cudaSuccess ||
+        cudaFuncSetAttribute(gateup_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
       cudaGetLastError();
       return GU_ECUDA;
+    }
+    {
+      // how many two-CTA clusters of the pair kernel the device holds at once (one CTA per SM)
+      cudaLaunchConfig_t cfg;
+      std::memset(&cfg, 0, sizeof(cfg));
+      cfg.gridDim = dim3(2 * static_cast<unsigned>(d.sm_count), 1, 1);
+      cfg.blockDim = dim3(kPairThreads, 1, 1);
+      cfg.dynamicSmemBytes = kPairSmemBytes;
+      cudaLaunchAttribute attr;
+      attr.id = cudaLaunchAttributeClusterDimension;
+      attr.val.clusterDim.x = 2;
+      attr.val.clusterDim.y = 1;
+      attr.val.clusterDim.z = 1;
+      cfg.attrs = &attr;
+      cfg.numAttrs = 1;
+      int clusters = 0;
+      if (cudaOccupancyMaxActiveClusters(&clusters, gateup_pair_kernel, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        clusters = 0;
+      }
+      d.pair_clusters = clusters;
     }
     d.attrs_set = true;
   }
   *out = &d;
   return GU_OK;
+}
+
+// One CTA whose only wait is on a barrier that nothing ever arrives on: the bounded-wait protocol of the real
+// kernels (mbar_wait, WaitCtx::fail, the CTA abort flag) run to its time limit, with no copy or MMA in flight.
+constexpr unsigned kWaitProbe = 31;
+__global__ void wait_probe_kernel() {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bar), 1);
+    abort_flag = 0;
+    fence_mbar_init();
+  }
+  __syncthreads();
+  WaitCtx ctx{smem_u32(&abort_flag), false, false};
+  if (threadIdx.x == 0) mbar_wait(ctx, smem_u32(&bar), 0u, kWaitProbe);  // gives up after the wait limit
+  __syncthreads();
+  // every other thread finds the CTA aborting and returns at once, as the roles of the real kernels do
+  if (threadIdx.x != 0) mbar_wait(ctx, smem_u32(&bar), 0u, kWaitProbe);
 }
 
 std::atomic<unsigned int> g_epoch{0};
@@ -284,6 +327,49 @@ int launch_tile(const gu_problem* pr, const DeviceInfo& dev, cudaStream_t stream
   return GU_OK;
 }
 
+// CTA-pair kernel: 256-token x 128-column tiles, one per two-CTA cluster.
+int launch_pair(const gu_problem* pr, const DeviceInfo& dev, cudaStream_t stream) {
+  const int64_t m = pr->m, k = pr->k, n = pr->n;
+  if (dev.pair_clusters < 1) return GU_EINVAL_PLAN;
+  CUtensorMap tm_x, tm_g, tm_u, tm_o;
+  int rc;
+  if ((rc = get_map(&tm_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, pr->x, k, m, k, 128, 128)) != GU_OK) return rc;
+  if ((rc = get_map(&tm_g, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, pr->gate_w, k, n, k, 128, 128)) != GU_OK) return rc;
+  if ((rc = get_map(&tm_u, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, pr->up_w, k, n, k, 128, 128)) != GU_OK) return rc;
+  if ((rc = get_map(&tm_o, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, pr->output, n, m, pr->ld_output * 2, 64, 128)) !=
+      GU_OK)
+    return rc;
+
+  TileParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.scale_x = pr->scale_x;
+  p.scale_gate = pr->scale_gate;
+  p.scale_up = pr->scale_up;
+  p.m = static_cast<int>(m);
+  p.kb = static_cast<int>(k / 128);
+  p.num_m_blocks = static_cast<int>((m + 2 * kTileM - 1) / (2 * kTileM));  // 256-token pair blocks
+  p.num_n_blocks = static_cast<int>(n / kTileN);
+  const int64_t tiles = int64_t(p.num_m_blocks) * p.num_n_blocks;
+  if (tiles * (k / 128) >= (1ll << 31)) return GU_EINVAL_SHAPE;
+  p.num_tiles = static_cast<int>(tiles);
+  // raster group: as many pair blocks as keep the group's X rows (256 x K bytes each) within ~24 MiB of L2
+  int64_t gm = (24ll << 20) / (256 * k);
+  if (gm < 1) gm = 1;
+  if (gm > p.num_m_blocks) gm = p.num_m_blocks;
+  p.group_m = static_cast<int>(gm);
+  p.out_count = 1;
+  p.blocks_per_owner = 1;
+
+  const int clusters = p.num_tiles < dev.pair_clusters ? p.num_tiles : dev.pair_clusters;
+  gateup_pair_kernel<<<2 * clusters, kPairThreads, kPairSmemBytes, stream>>>(tm_x, tm_g, tm_u, tm_o, p);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError() == cudaSuccess ? GU_OK : GU_ECUDA;
+}
+
+// The tile plan's kernel for a shape: CTA pairs once there is more than one 128-token block (a lone block would
+// leave the second CTA of every pair without rows), the lone-CTA kernel otherwise.
+bool tile_prefers_pairs(int64_t m, const DeviceInfo& dev) { return m > kTileM && dev.pair_clusters >= 1; }
+
 template <int MPAD>
 int launch_stream_t(const gu_problem* pr, const DeviceInfo& dev, cudaStream_t stream, int stages) {
   const int64_t m = pr->m, k = pr->k, n = pr->n;
@@ -383,7 +469,7 @@ const char* gu_error_string(int code) {
     case GU_EINVAL_NULL: return "a required pointer is null";
     case GU_EINVAL_SHAPE: return "unsupported shape: need M >= 1, K and N positive multiples of 128, ld_output >= N";
     case GU_EINVAL_ALIGN: return "pointers must be 16-byte aligned and ld_output a multiple of 8";
-    case GU_EINVAL_PLAN: return "unknown plan, or the plan cannot run this shape";
+    case GU_EINVAL_PLAN: return "unknown plan, or the plan cannot run this shape on this device";
     case GU_EWORKSPACE: return "workspace missing or too small (see gu_workspace_bytes)";
     case GU_ECUDA: return "a CUDA call failed";
     case GU_EDEVICE: return "the current device is not compute capability 10.x";
@@ -428,11 +514,14 @@ int gu_run(const gu_problem* pr, void* stream_v) {
   if (rc != GU_OK) return rc;
   int plan = pr->plan;
   if (plan == GU_PLAN_AUTO) plan = gu_select_plan(pr->m, pr->k, pr->n);
-  if (plan != GU_PLAN_TILE && plan != GU_PLAN_STREAM && plan != GU_PLAN_TILE_DP && plan != GU_PLAN_TILE_SK)
+  if (plan != GU_PLAN_TILE && plan != GU_PLAN_STREAM && plan != GU_PLAN_TILE_DP && plan != GU_PLAN_TILE_SK &&
+      plan != GU_PLAN_TILE_PAIR)
     return GU_EINVAL_PLAN;
   gu::DeviceInfo* dev = nullptr;
   if ((rc = gu::device_info(&dev)) != GU_OK) return rc;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  if (plan == GU_PLAN_TILE_PAIR) return gu::launch_pair(pr, *dev, stream);
+  if (plan == GU_PLAN_TILE && gu::tile_prefers_pairs(pr->m, *dev)) return gu::launch_pair(pr, *dev, stream);
   if (plan != GU_PLAN_STREAM) {
     const bool have_ws = pr->workspace && pr->workspace_bytes >= gu::tile_stream_k_bytes() && gu::aligned16(pr->workspace);
     bool sk = false;
@@ -837,5 +926,39 @@ int gu_last_status(int* detail, int clear) {
 }
 
 int64_t gu_launch_count(void) { return gu::g_launches.load(std::memory_order_relaxed); }
+
+int gu_set_wait_limit_ns(uint64_t ns) {
+  const unsigned long long v = ns ? ns : 2000000000ull;
+  if (cudaDeviceSynchronize() != cudaSuccess) return GU_ECUDA;
+  return cudaMemcpyToSymbol(gu::g_wait_limit_ns, &v, sizeof(v)) == cudaSuccess ? GU_OK : GU_ECUDA;
+}
+
+int gu_wait_probe(void* stream_v) {
+  gu::wait_probe_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream_v)>>>();
+  gu::g_launches.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError() == cudaSuccess ? GU_OK : GU_ECUDA;
+}
+
+int gu_trace_read(uint64_t* out, int capacity, int clear) {
+#ifdef GU_TRACE
+  if (!out || capacity < 0) return GU_EINVAL_NULL;
+  unsigned long long host[32 + 256];
+  if (cudaDeviceSynchronize() != cudaSuccess) return GU_ECUDA;
+  if (cudaMemcpyFromSymbol(host, gu::g_trace, 32 * sizeof(host[0])) != cudaSuccess) return GU_ECUDA;
+  if (cudaMemcpyFromSymbol(host + 32, gu::g_events, 256 * sizeof(host[0])) != cudaSuccess) return GU_ECUDA;
+  const int n = capacity < 288 ? capacity : 288;
+  for (int i = 0; i < n; ++i) out[i] = host[i];
+  if (clear) {
+    std::memset(host, 0, sizeof(host));
+    if (cudaMemcpyToSymbol(gu::g_trace, host, 32 * sizeof(host[0])) != cudaSuccess) return GU_ECUDA;
+  }
+  return n;
+#else
+  (void)out;
+  (void)capacity;
+  (void)clear;
+  return 0;
+#endif
+}
 
 }  // extern "C"

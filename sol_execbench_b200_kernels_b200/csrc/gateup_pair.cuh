@@ -1,0 +1,516 @@
+// Persistent tile kernel for CTA pairs: the gate/up projection with fused SwiGLU
+// for everything but decode-sized and single-block M.
+//
+// Two CTAs on neighbouring SMs (a cluster of two) own a 256-token x 128-column
+// output tile of BOTH projections.  Each CTA stages its own 128 token rows of X
+// and HALF of the weight rows of a K block (the even CTA the gate block, the odd
+// CTA the up block: 32 KiB per CTA and K block instead of the 48 KiB a lone CTA
+// needs), the even CTA issues one tcgen05.mma stream with cta_group::2 (M = 256,
+// N = 256) for both, and each CTA finds the 128 x 256 fp32 partial of its own
+// tokens in its own TMEM: gate in columns [0,128), up in [128,256) of a
+// two-stage accumulator.  Per MAC that is two thirds of the shared-memory traffic
+// (TMA writes and MMA operand reads) of the lone-CTA kernel.
+//
+// What bounds a kernel of this kind is the round trip of an accumulator stage —
+// MMA, completion seen by the consumers, the partial read out of TMEM, the stage
+// handed back, the next MMA issued — because the fp32 per-128 scales force every
+// K block's partial through registers and TMEM holds only two 128 x 256 stages.
+// So every hop of that loop is kept short:
+//   * the issuer and the producer are whole warps in uniform control flow with one
+//     elected lane doing the work (descriptors and addresses stay in uniform
+//     registers), and the polls a step needs are issued together;
+//   * exactly one lane per warp polls a barrier (the other 31 wait at a warp or
+//     CTA barrier), so polling does not load the shared-memory pipeline that the
+//     barriers themselves go through;
+//   * arrivals that cross to the other CTA are relaxed (what they order lives in
+//     TMEM) and one commit per CTA and K block serves both the ring slot and the
+//     accumulator;
+//   * warps 4-7 promote the gate half and warps 8-11 the up half (a thread owns
+//     one token row and all 128 columns of one projection), reading the partial
+//     in pieces through two alternating buffers so that the tcgen05.ld of a
+//     piece is in flight while the piece before it is multiplied by
+//     scale_x[m, kb] * scale_w[n/128, kb] and added to the fp32 running sums
+//     (block order ascending, as the reference's promotion loop does:
+//     variants/cute_fused_v1/blockwise_gemm_fused.py:1817-1823); the stage goes
+//     back as soon as the last piece is in registers;
+//   * at the end of a tile the consumers only round gate and up to bf16 into a
+//     64 KiB shared-memory hand-over tile and go on with the next tile; separate
+//     epilogue warps apply SiLU, the product and the last rounding in place and
+//     issue the TMA store.
+//
+// Warp roles:
+//   warp 0        TMA producer: own X tile + own 128 weight rows (gate or up)
+//   warp 1        TMEM allocation; in the even CTA it issues every MMA of the pair
+//   warps 4-11    consumers (promotion); warp w reads TMEM lanes 32*(w%4)..+31
+//   epilogue      warps 2-3 (12 warps per CTA, the default) or warps 12-15 (16)
+//
+// Cross-CTA signalling: every wait is on a barrier of the waiting CTA and is
+// bounded; the other CTA reaches it with shared::cluster addresses (remote
+// mbarrier.arrive, TMA completion bytes, tcgen05.commit).  No multicast form.
+#pragma once
+
+#include "gateup_tile.cuh"
+
+namespace gu {
+
+#ifndef GU_PAIR_THREADS
+#define GU_PAIR_THREADS 384
+#endif
+#ifndef GU_PIECE
+#define GU_PIECE 16
+#endif
+#ifndef GU_INFLIGHT
+#define GU_INFLIGHT 2
+#endif
+constexpr int kPairThreads = GU_PAIR_THREADS;                    // 384: epilogue on warps 2-3; 512: on warps 12-15
+constexpr int kPairEpiWarp0 = kPairThreads == 512 ? 12 : 2;
+constexpr int kPairEpiThreads = kPairThreads == 512 ? 128 : 64;
+constexpr int kPairConsumerRegs = kPairThreads == 512 ? 216 : 232;  // the other warpgroups keep 40
+#ifndef GU_PAIR_STAGES
+#define GU_PAIR_STAGES 4
+#endif
+constexpr int kPairStages = GU_PAIR_STAGES;                      // shared-memory ring depth
+constexpr uint32_t kPairStageBytes = 2 * kOperandTileBytes;      // X tile + this CTA's half of the weight rows
+constexpr uint32_t kPairHandBytes = 4 * kTileOutHalfBytes;       // bf16 gate tile + bf16 up tile (two half tiles each)
+constexpr uint32_t kPairSmemBytes = kPairStages * kPairStageBytes + kPairHandBytes + 256 /*barriers*/ + 1024 /*alignment*/;
+constexpr int kPairPiece = GU_PIECE;                             // accumulator columns per tcgen05.ld of a consumer
+constexpr int kPairInFlight = GU_INFLIGHT;                       // loads a consumer keeps in flight (1 or 2)
+constexpr int kPairRounds = kTileN / (kPairPiece * kPairInFlight);  // rounds of loads per 128-column half
+
+enum : unsigned {
+  kWaitPairSlot = 11, kWaitPairFull = 12, kWaitPairStageFree = 13, kWaitPairDone = 14,
+  kWaitPairHandEmpty = 15, kWaitPairHandFull = 16,
+};
+
+// Study builds (never the shipped library; see build.py):
+//   -DGU_TRACE   per-role cycle counters and time stamps of the first CTA pair, read with gu_trace_read
+//   -DGU_EXP=n   results are wrong on purpose; what is left bounds a part of the kernel from above:
+//                1 consumers read the partial but skip the promotion arithmetic
+//                2 consumers neither read nor add: only the hand-shake with the issuer is left
+//                3 the issuer waits for each K block's completion before going on (issue-to-completion latency)
+//                4 as 2, and the issuer never waits for the consumers: MMA + TMA + issuer alone
+//                5 as 3 and 4 together: one K block in flight on an otherwise idle SM
+//   -DGU_PAIR_THREADS=512, -DGU_PIECE=32, -DGU_INFLIGHT=1, -DGU_PAIR_STAGES=5   layout variants that were measured
+#ifdef GU_TRACE
+// Cycle counters of cluster 0 (both CTAs), summed over the launch: [rank][slot]
+//  0 producer: waiting for a free ring slot     1 issuer: waiting for operands   2 issuer: waiting for a free unit
+//  3 consumer warp 4: waiting for a partial     4 consumer warp 4: in tcgen05.wait::ld
+//  5 consumer warp 4: K loop, all tiles         6 consumer warp 4: hand-over (incl. waiting for the tile to be free)
+//  7 first epilogue warp: SwiGLU + store       8 first epilogue warp: waiting for a hand-over
+//  9 whole CTA (thread 0)                      10 K blocks walked by consumer warp 4
+__device__ unsigned long long g_trace[2][16];
+// Time stamps (clock64 of the CTA's SM) of K blocks 8..23 of cluster 0's first tile, four per K block: [rank][role][64]
+//  role 0, issuer (even CTA): operands and stage seen / - / MMAs issued / commits issued
+//  role 1, consumer warp 4:   partial seen / - / last load issued / stage handed back
+__device__ unsigned long long g_events[2][2][64];
+#define GU_EV(role, j, e) do { if (tr_me && tr_first && (j) >= 8 && (j) < 24) g_events[blockIdx.x & 1][role][4 * ((j) - 8) + (e)] = clock64(); } while (0)
+// one reporting thread per role: the elected lane of the producer and issuer warps, lane 0 of consumer warp 4 and of the
+// first epilogue warp
+#define GU_TR_DECL                                                                                               \
+  unsigned long long tr_t0 = 0;                                                                                  \
+  bool tr_me = blockIdx.x < 2 && (threadIdx.x == 128 || threadIdx.x == 32 * kPairEpiWarp0)
+#define GU_TR_BEGIN() do { if (tr_me) tr_t0 = clock64(); } while (0)
+// (reductions whose result is not used: the thread does not wait for them)
+#define GU_TR_END(slot) do { if (tr_me) atomicAdd(&g_trace[blockIdx.x & 1][slot], (unsigned long long)(clock64() - tr_t0)); } while (0)
+#else
+#define GU_TR_DECL
+#define GU_TR_BEGIN() do {} while (0)
+#define GU_TR_END(slot) do {} while (0)
+#define GU_EV(role, j, e) do {} while (0)
+#endif
+
+
+// packed FMAs over one piece: sums[i] += piece[2i, 2i+1] * scale
+__device__ __forceinline__ void pair_fma(float2* sums, const float* piece, float2 scale) {
+#if defined(GU_EXP) && (GU_EXP == 1 || GU_EXP == 2 || GU_EXP == 4 || GU_EXP == 5)
+  sums[0].x += piece[0] * scale.x;  // experiment: no promotion arithmetic
+  return;
+#endif
+#pragma unroll
+  for (int i = 0; i < kPairPiece / 2; ++i)
+    sums[i] = __ffma2_rn(make_float2(piece[2 * i], piece[2 * i + 1]), scale, sums[i]);
+}
+
+__device__ __forceinline__ void pair_ld(uint32_t taddr, float* v) {
+#if defined(GU_EXP) && (GU_EXP == 2 || GU_EXP == 4 || GU_EXP == 5)
+  (void)taddr;  // experiment: the partial is not read at all
+  (void)v;
+#else
+  if constexpr (kPairPiece == 32) tmem_ld32(taddr, v);
+  else tmem_ld16(taddr, v);
+#endif
+}
+
+// One lane of a converged warp polls; every lane gets the outcome.  Keeps the warp's control flow uniform (so the
+// addresses and descriptors around it stay in uniform registers) and the polling traffic at one thread per warp.
+__device__ __forceinline__ bool mbar_wait_elected(WaitCtx& ctx, bool elected, uint32_t bar, uint32_t parity, unsigned code) {
+  bool ok = true;
+  if (elected) ok = mbar_wait(ctx, bar, parity, code);
+  ok = __all_sync(0xffffffffu, ok);
+  __syncwarp();  // what the polling lane acquired is ordered before the other lanes' accesses
+  return ok;
+}
+// Same for waiters that do not branch on the outcome (after a time-out they read stale data, which is discarded).
+__device__ __forceinline__ void mbar_wait_lane(WaitCtx& ctx, bool elected, uint32_t bar, uint32_t parity, unsigned code) {
+  if (elected) (void)mbar_wait(ctx, bar, parity, code);
+  __syncwarp();
+}
+
+// TileParams as used here: num_m_blocks / group_m count 256-token pair blocks, num_tiles pair tiles.
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
+gateup_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_gate,
+                   const __grid_constant__ CUtensorMap tm_up, const __grid_constant__ CUtensorMap tm_out,
+                   const TileParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  // operand tiles need 1024-byte alignment for the 128-byte swizzle pattern; both CTAs of a pair get the same offsets
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+
+  const uint32_t ring = smem_base;
+  const uint32_t hand = smem_base + kPairStages * kPairStageBytes;  // gate tile (later the output tile), then up tile
+  const uint32_t bars = hand + kPairHandBytes;
+  const uint32_t bar_full = bars;                           // [stages] even CTA's are used: 2 producer arrivals + both CTAs' bytes
+  const uint32_t bar_done = bar_full + 8 * kPairStages;     // [stages] the K block's MMAs have completed (one commit):
+                                                            // its partial is in TMEM and its ring slot may be refilled
+  const uint32_t bar_stage_free = bar_done + 8 * kPairStages;  // [2] even CTA's are used: 8 consumer warps x 2 CTAs
+  const uint32_t bar_hand_full = bar_stage_free + 16;       // 8 consumer warps
+  const uint32_t bar_hand_empty = bar_hand_full + 8;        // the storing epilogue thread
+  const uint32_t tmem_slot = bar_hand_empty + 8;
+  const uint32_t abort_slot = tmem_slot + 4;
+  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + (tmem_slot - smem_base));
+  volatile int* abort_gen = reinterpret_cast<volatile int*>(smem_gen + (abort_slot - smem_base));
+
+  // the warp index through a shuffle, so that the compiler knows it is the same in every lane
+  const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0: the CTA that issues the MMAs
+  const int cluster_id = blockIdx.x >> 1;
+  const int clusters = gridDim.x >> 1;
+  GU_TR_DECL;
+#ifdef GU_TRACE
+  const unsigned long long tr_cta0 = clock64();
+#endif
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPairStages; ++s) {
+      mbar_init(bar_full + 8 * s, 2);
+      mbar_init(bar_done + 8 * s, 1);
+    }
+    for (int q = 0; q < 2; ++q) mbar_init(bar_stage_free + 8 * q, 16);
+    mbar_init(bar_hand_full, 8);
+    mbar_init(bar_hand_empty, 1);
+    *abort_gen = 0;
+    fence_mbar_init();
+    fence_proxy_async_smem();
+    tma_prefetch_desc(&tm_x);
+    tma_prefetch_desc(&tm_gate);
+    tma_prefetch_desc(&tm_up);
+    tma_prefetch_desc(&tm_out);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, kTileTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  cluster_sync_all();  // barriers and the abort flag of both CTAs exist before anything reaches across
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_gen;
+
+  WaitCtx ctx{abort_slot, false, true};
+  const bool is_consumer = warp >= 4 && warp < 12;
+  const bool is_epilogue = warp >= kPairEpiWarp0 && warp < kPairEpiWarp0 + kPairEpiThreads / 32;
+
+  if (!is_consumer) {
+    reg_dealloc<40>();
+    if (warp == 0) {
+      // ---------------- TMA producer: the whole warp walks the loop, one elected lane waits and issues ----------------
+      const bool elected = elect_one() != 0u;
+#ifdef GU_TRACE
+      tr_me = blockIdx.x < 2 && elected;
+#endif
+      const uint32_t full_even = mapa_shared(bar_full, 0);
+      uint32_t slots = 0;  // ring slots filled so far: stage = low bits, barrier phase = the next bit
+      for (int tile = cluster_id; tile < p.num_tiles; tile += clusters) {
+        int pm, nb;
+        tile_coords(p, tile, pm, nb);
+        const int row0 = (2 * pm + static_cast<int>(rank)) * kTileM;
+        for (int j = 0; j < p.kb; ++j, ++slots) {
+          const uint32_t stage = slots % kPairStages, phase = (slots / kPairStages) & 1u;
+          GU_TR_BEGIN();
+          const bool ok = mbar_wait_elected(ctx, elected, bar_done + 8 * stage, phase ^ 1u, kWaitPairSlot);
+          GU_TR_END(0);
+          const uint32_t full = full_even + 8 * stage;
+          const uint32_t dst = ring + stage * kPairStageBytes;
+          if (ok && elected) {
+            mbar_arrive_expect_tx_cluster(full, kPairStageBytes);
+            tma_load_2d_pair(dst, &tm_x, full, j * kBlockK, row0);  // rows past M read as zero
+            // B rows [0, 128) of the MMA = the gate block (even CTA), [128, 256) = the up block (odd CTA)
+            tma_load_2d_pair(dst + kOperandTileBytes, rank == 0 ? &tm_gate : &tm_up, full, j * kBlockK, nb * kTileN);
+          }
+          __syncwarp();
+        }
+      }
+      // the last commits into this CTA's ring barriers must have landed before the CTA may go away
+      for (int s = 0; s < kPairStages; ++s, ++slots)
+        mbar_wait_elected(ctx, elected, bar_done + 8 * (slots % kPairStages), ((slots / kPairStages) & 1u) ^ 1u,
+                          kWaitPairSlot);
+    } else if (warp == 1 && rank == 0) {
+      // ---------------- MMA issuer of the pair: the whole warp walks the loop, one elected lane waits and issues ------
+      const bool elected = elect_one() != 0u;
+#ifdef GU_TRACE
+      tr_me = blockIdx.x < 2 && elected;
+#endif
+      constexpr uint32_t idesc = umma_idesc_e4m3_f32(2 * kTileM, 2 * kTileN);
+      const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
+      const uint32_t done_odd = mapa_shared(bar_done, 1);
+      // descriptors of ring stage 0; a stage further on adds its byte offset >> 4 to the address field (low word)
+      const uint64_t adesc0 = umma_desc_k_sw128(ring);
+      const uint64_t bdesc0 = umma_desc_k_sw128(ring + kOperandTileBytes);
+      uint32_t blocks = 0;  // K blocks issued so far
+      for (int tile = cluster_id; tile < p.num_tiles; tile += clusters) {
+#ifdef GU_TRACE
+        const bool tr_first = tile == cluster_id;
+#endif
+        for (int j = 0; j < p.kb; ++j, ++blocks) {
+          const uint32_t stage = blocks % kPairStages, phase = (blocks / kPairStages) & 1u;
+          const uint32_t acc = blocks & 1u, acc_phase = (blocks >> 1) & 1u;
+          const uint64_t adesc = adesc0 + stage * (kPairStageBytes >> 4);
+          const uint64_t bdesc = bdesc0 + stage * (kPairStageBytes >> 4);
+          const uint32_t d = tmem_u + acc * (2 * kTileN);
+          const uint32_t full = bar_full + 8 * stage;
+          const uint32_t stage_free = bar_stage_free + 8 * acc;
+          // The two polls are issued back to back (a poll of shared memory takes a hundred cycles or more while TMA
+          // writes and MMA operand reads keep it busy); only a poll that fails turns into a wait.
+          bool ok = true;
+          GU_TR_BEGIN();
+          if (elected) {
+            const uint32_t hit_full = mbar_try_wait(full, phase);
+            const uint32_t hit_free = mbar_try_wait(stage_free, acc_phase ^ 1u);
+            ok = hit_full || mbar_wait(ctx, full, phase, kWaitPairFull);
+#if !(defined(GU_EXP) && (GU_EXP == 4 || GU_EXP == 5))  // (experiments 4, 5: the issuer never waits for the consumers)
+            ok = (hit_free || mbar_wait(ctx, stage_free, acc_phase ^ 1u, kWaitPairStageFree)) && ok;
+#endif
+          }
+          ok = __all_sync(0xffffffffu, ok);
+          GU_TR_END(1);
+          GU_EV(0, j, 0);
+          if (ok && elected) {
+            tc_fence_after();
+#pragma unroll
+            for (int kk = 0; kk < kBlockK / 32; ++kk)  // 32 e4m3 along K inside the swizzle span: +2 in the address field
+              umma_f8_pair(d, adesc + 2 * kk, bdesc + 2 * kk, idesc, kk > 0 ? 1u : 0u);
+            GU_EV(0, j, 2);
+            umma_commit_pair(bar_done + 8 * stage);  // to both CTAs: partial in TMEM, operands read
+            umma_commit_pair(done_odd + 8 * stage);
+            GU_EV(0, j, 3);
+#if defined(GU_EXP) && (GU_EXP == 3 || GU_EXP == 5)
+            mbar_wait(ctx, bar_done + 8 * stage, phase, kWaitPairDone);  // experiment: issue-to-completion latency
+            GU_EV(0, j, 1);
+#endif
+          }
+          __syncwarp();
+        }
+      }
+      // the odd CTA's last hand-backs must have landed here before this CTA may go away
+      for (uint32_t b = blocks; b < blocks + 2; ++b)
+        mbar_wait_elected(ctx, elected, bar_stage_free + 8 * (b & 1u), ((b >> 1) & 1u) ^ 1u, kWaitPairStageFree);
+    } else if (is_epilogue) {
+      // -------------------------------- epilogue ---------------------------------
+      const int et = static_cast<int>(threadIdx.x) - 32 * kPairEpiWarp0;  // 0 .. kPairEpiThreads-1
+      uint8_t* hand_gen = smem_gen + (hand - smem_base);
+      uint32_t hand_phase = 0;
+      for (int tile = cluster_id; tile < p.num_tiles; tile += clusters) {
+        int pm, nb;
+        tile_coords(p, tile, pm, nb);
+        const int row0 = (2 * pm + static_cast<int>(rank)) * kTileM;
+        GU_TR_BEGIN();
+        // one thread polls; the others sleep at a hardware barrier instead of polling shared memory for a whole tile
+        bool ok = true;
+        if (et == 0) ok = mbar_wait(ctx, bar_hand_full, hand_phase, kWaitPairHandFull);
+        named_bar_sync(2, kPairEpiThreads);
+        GU_TR_END(8);
+        GU_TR_BEGIN();
+        // gate and up tiles have the same layout, so chunk q of one meets chunk q of the other whatever it holds
+#pragma unroll 4
+        for (int i = 0; i < 2048 / kPairEpiThreads; ++i) {
+          uint4* gq = reinterpret_cast<uint4*>(hand_gen + (et + kPairEpiThreads * i) * 16);
+          const uint4 a = *gq;
+          const uint4 b = *reinterpret_cast<const uint4*>(hand_gen + 2 * kTileOutHalfBytes + (et + kPairEpiThreads * i) * 16);
+          uint4 o;
+          o.x = swiglu_packed_bf16x2(a.x, b.x);
+          o.y = swiglu_packed_bf16x2(a.y, b.y);
+          o.z = swiglu_packed_bf16x2(a.z, b.z);
+          o.w = swiglu_packed_bf16x2(a.w, b.w);
+          *gq = o;
+        }
+        fence_proxy_async_smem();
+        named_bar_sync(1, kPairEpiThreads);
+        if (et == 0) {
+          if (ok && !ctx.aborted && row0 < p.m) {
+            tma_store_2d(&tm_out, hand, nb * kTileN, row0);
+            tma_store_2d(&tm_out, hand + kTileOutHalfBytes, nb * kTileN + 64, row0);
+            tma_store_commit();
+            tma_store_wait_read0();  // the tile may be overwritten once the stores have read it
+          }
+          mbar_arrive(bar_hand_empty);
+        }
+        GU_TR_END(7);
+        hand_phase ^= 1u;
+      }
+      if (et == 0) tma_store_wait_all0();
+    }
+  } else {
+    reg_alloc<kPairConsumerRegs>();
+    // ------------------------------- consumers --------------------------------
+    // Warps 4-7 promote the gate half of every K block, warps 8-11 the up half: a thread owns one token row and all
+    // 128 columns of one projection.
+    const int quarter = warp & 3;          // TMEM lane quarter this warp may read
+    const uint32_t proj = static_cast<uint32_t>(warp - 4) >> 2;  // 0: gate, 1: up
+    const int row = quarter * 32 + lane;   // token row inside this CTA's 128
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + proj * kTileN;
+    const uint32_t stage_free_even = mapa_shared(bar_stage_free, 0);
+    const float* scale_w = proj ? p.scale_up : p.scale_gate;
+    uint32_t blocks_done = 0;  // K blocks walked so far: accumulator stage = bit 0, ring stage = low bits, phases above
+    uint32_t hand_phase = 0;
+
+    int tile = cluster_id;
+    // element offsets of this thread's scale rows (the host keeps M * K/128 and N/128 * K/128 below 2^31)
+    uint32_t sx_off = 0, sw_off = 0;
+    float sx0 = 0.f, sw0 = 0.f;
+    // first K block's scales of a tile (fetched before the previous tile is handed over)
+    auto start_tile = [&](int t) {
+      int pm, nb;
+      tile_coords(p, t, pm, nb);
+      const int m_global = min((2 * pm + static_cast<int>(rank)) * kTileM + row, p.m - 1);
+      sx_off = static_cast<uint32_t>(m_global) * static_cast<uint32_t>(p.kb);
+      sw_off = static_cast<uint32_t>(nb) * static_cast<uint32_t>(p.kb);
+      sx0 = __ldg(p.scale_x + sx_off);
+      sw0 = __ldg(scale_w + sw_off);
+    };
+    if (tile < p.num_tiles) start_tile(tile);
+
+    while (tile < p.num_tiles) {
+#ifdef GU_TRACE
+      const bool tr_first = tile == cluster_id;
+#endif
+      float2 sums[64];       // this row's 128 running sums of one projection
+      // piece buffers: one round (kPairInFlight pieces) is being added while the next round's loads are in flight
+      float va[kPairPiece], vb[kPairPiece], vc[kPairInFlight == 2 ? kPairPiece : 1], vd[kPairInFlight == 2 ? kPairPiece : 1];
+#pragma unroll
+      for (int i = 0; i < 64; ++i) sums[i] = make_float2(0.f, 0.f);
+#ifdef GU_TRACE
+      const unsigned long long tr_loop0 = clock64();
+#endif
+      for (int j = 0; j < p.kb; ++j) {
+        // the next K block's scales are fetched one block ahead of their use
+        float sx1 = 0.f, sw1 = 0.f;
+        if (j + 1 < p.kb) {
+          sx1 = __ldg(p.scale_x + sx_off + j + 1);
+          sw1 = __ldg(scale_w + sw_off + j + 1);
+        }
+        const float sc = sx0 * sw0;
+        const float2 scv = make_float2(sc, sc);
+        const uint32_t acc = blocks_done & 1u;
+        const uint32_t stage = blocks_done % kPairStages, phase = (blocks_done / kPairStages) & 1u;
+        const uint32_t t = lane_addr + acc * (2 * kTileN);
+
+        // This half's 128 columns come in rounds of kPairInFlight pieces of kPairPiece columns through two alternating
+        // sets of buffers: the loads of a round are in flight while the round before it is added; the stage goes back
+        // to the issuer as soon as the last round is in registers.  (Two loads of 16 columns instead of one of 32:
+        // same registers, but the allocator places four 16-register blocks without spilling, two 32-register ones not.)
+        GU_TR_BEGIN();
+        mbar_wait_lane(ctx, lane == 0, bar_done + 8 * stage, phase, kWaitPairDone);
+        GU_TR_END(3);
+        GU_EV(1, j, 0);
+        tc_fence_after();
+        pair_ld(t, va);
+        if constexpr (kPairInFlight == 2) pair_ld(t + kPairPiece, vb);
+#pragma unroll
+        for (int q = 0; q < kPairRounds; ++q) {
+          // buffers of this round and of the next (one or two pieces each)
+          float* c0 = (kPairInFlight == 2) ? ((q & 1) ? vc : va) : ((q & 1) ? vb : va);
+          float* c1 = (q & 1) ? vd : vb;
+          float* n0 = (kPairInFlight == 2) ? ((q & 1) ? va : vc) : ((q & 1) ? va : vb);
+          float* n1 = (q & 1) ? vb : vd;
+          tmem_ld_wait_pin<kPairPiece>(c0);
+          if constexpr (kPairInFlight == 2) tmem_ld_wait_pin<kPairPiece>(c1);
+          if (q + 1 < kPairRounds) {
+            pair_ld(t + (q + 1) * kPairInFlight * kPairPiece, n0);
+            if constexpr (kPairInFlight == 2) pair_ld(t + ((q + 1) * 2 + 1) * kPairPiece, n1);
+          } else {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(stage_free_even + 8 * acc);  // the half is in registers: hand it back
+            GU_EV(1, j, 3);
+          }
+          // The round before the last is not added until the last round is in registers too, so that the stage goes
+          // back one round of arithmetic earlier (both rounds sit in the two buffer sets meanwhile).
+          if (q + 2 != kPairRounds) {
+            pair_fma(sums + q * kPairInFlight * (kPairPiece / 2), c0, scv);
+            if constexpr (kPairInFlight == 2) pair_fma(sums + (q * 2 + 1) * (kPairPiece / 2), c1, scv);
+          }
+          if (q + 1 == kPairRounds) {
+            pair_fma(sums + (q - 1) * kPairInFlight * (kPairPiece / 2), n0, scv);
+            if constexpr (kPairInFlight == 2) pair_fma(sums + ((q - 1) * 2 + 1) * (kPairPiece / 2), n1, scv);
+          }
+        }
+
+        ++blocks_done;
+        sx0 = sx1;
+        sw0 = sw1;
+      }
+#ifdef GU_TRACE
+      if (tr_me) {
+        atomicAdd(&g_trace[blockIdx.x & 1][5], (unsigned long long)(clock64() - tr_loop0));
+        atomicAdd(&g_trace[blockIdx.x & 1][10], (unsigned long long)p.kb);
+      }
+#endif
+
+      // next tile's coordinates and first scales, so their latency hides under the hand-over
+      const int next = tile + clusters;
+      if (next < p.num_tiles) start_tile(next);
+
+      // -------- hand-over: this projection's bf16 tile in the output staging layout (two 64-column half tiles of
+      // 128-byte rows, 16-byte chunks swizzled by the row) --------
+      GU_TR_BEGIN();
+      mbar_wait_lane(ctx, lane == 0, bar_hand_empty, hand_phase ^ 1u, kWaitPairHandEmpty);
+      {
+        uint8_t* tile_row = smem_gen + (hand - smem_base) + proj * (2 * kTileOutHalfBytes) + row * 128;
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {  // 16 chunks of 8 bf16 = 16 bytes
+          uint4 q;
+          q.x = pack_bf16x2(sums[4 * c + 0].x, sums[4 * c + 0].y);
+          q.y = pack_bf16x2(sums[4 * c + 1].x, sums[4 * c + 1].y);
+          q.z = pack_bf16x2(sums[4 * c + 2].x, sums[4 * c + 2].y);
+          q.w = pack_bf16x2(sums[4 * c + 3].x, sums[4 * c + 3].y);
+          *reinterpret_cast<uint4*>(tile_row + (c >> 3) * kTileOutHalfBytes + (((c & 7) ^ (row & 7)) << 4)) = q;
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_hand_full);
+      GU_TR_END(6);
+      hand_phase ^= 1u;
+      tile = next;
+    }
+  }
+
+  // ------------------------------- teardown --------------------------------
+  if (*abort_gen) {
+    // give copies that were already in flight time to land before shared memory goes away
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) spin_backoff_ns(1000u);
+  }
+  tc_fence_before();
+  __syncwarp();
+  cluster_sync_all();  // neither CTA leaves while the other may still reach into it
+  tc_fence_after();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc_pair(tmem_base, kTileTmemCols);
+  }
+#ifdef GU_TRACE
+  if (blockIdx.x < 2 && threadIdx.x == 0) atomicAdd(&g_trace[blockIdx.x & 1][9], (unsigned long long)(clock64() - tr_cta0));
+#endif
+}
+
+}  // namespace gu

@@ -127,7 +127,7 @@ gateup_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_cons
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_gen;
 
-  WaitCtx ctx{abort_gen, false};
+  WaitCtx ctx{abort_slot, false, false};
 
   if (warp == 0) {
     if (lane == 0) {
@@ -288,7 +288,7 @@ gateup_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_cons
                     const unsigned long long now = globaltimer_ns();
                     if (t0 == 0) {
                       t0 = now;
-                    } else if (now - t0 > kWaitTimeoutNs || *ctx.cta_abort) {
+                    } else if (now - t0 > g_wait_limit_ns || ctx.raised()) {
                       ctx.fail(kWaitStreamFlag, (kWaitStreamFlag << 24) | (blockIdx.x & 0xffffffu));
                       break;
                     }
@@ -296,7 +296,7 @@ gateup_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_cons
                 }
               }
               named_bar_sync(1, 128);
-              if (!*ctx.cta_abort) {
+              if (!ctx.raised()) {
                 const float* slot = p.partials + static_cast<size_t>(rr) * (2 * MPAD * 128);
 #pragma unroll
                 for (int t = 0; t < MPAD; ++t) {

@@ -211,7 +211,7 @@ __device__ __forceinline__ void tile_kernel_body(const CUtensorMap& tm_x, const 
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_gen;
 
-  WaitCtx ctx{abort_gen, false};
+  WaitCtx ctx{abort_slot, false, false};
 
   if (warp < 4) {
     reg_dealloc<64>();
@@ -561,7 +561,7 @@ __device__ __forceinline__ void tile_kernel_body(const CUtensorMap& tm_x, const 
                   const unsigned long long now = globaltimer_ns();
                   if (t0 == 0) {
                     t0 = now;
-                  } else if (now - t0 > kWaitTimeoutNs || *ctx.cta_abort) {
+                  } else if (now - t0 > g_wait_limit_ns || ctx.raised()) {
                     ctx.fail(kWaitTileFlag, (kWaitTileFlag << 24) | (blockIdx.x & 0xffffffu));
                     break;
                   }
@@ -569,7 +569,7 @@ __device__ __forceinline__ void tile_kernel_body(const CUtensorMap& tm_x, const 
               }
             }
             named_bar_sync(1 + half, 128);
-            if (!*ctx.cta_abort) {
+            if (!ctx.raised()) {
               const float4* slot =
                   reinterpret_cast<const float4*>(p.partials + static_cast<size_t>(rr) * kTilePartialFloats) + ctid;
 #pragma unroll

@@ -15,7 +15,8 @@ namespace gu {
 // ---------------------------------------------------------------------------
 __device__ unsigned int g_status[4];
 
-constexpr unsigned long long kWaitTimeoutNs = 2000000000ull;  // every device-side wait gives up after 2 s
+// Every device-side wait gives up after this many nanoseconds (2 s unless gu_set_wait_limit_ns changed it).
+__device__ unsigned long long g_wait_limit_ns = 2000000000ull;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -47,11 +48,27 @@ __device__ __forceinline__ uint32_t elect_one() {
 // structure, so all warps still meet at the same barriers and the CTA exits.
 // ---------------------------------------------------------------------------
 struct WaitCtx {
-  volatile int* cta_abort;  // shared memory flag
+  uint32_t abort_addr;  // shared::cta address of the CTA's abort flag
   bool aborted;
+  bool pair;            // CTA pair: a failing wait raises the other CTA's flag too (same offset, other rank)
+  __device__ __forceinline__ bool raised() const {
+    uint32_t v;
+    asm volatile("ld.volatile.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(abort_addr) : "memory");
+    return v != 0u;
+  }
   __device__ __forceinline__ void fail(unsigned code, unsigned detail) {
     aborted = true;
-    *cta_abort = 1;
+    asm volatile("st.volatile.shared::cta.u32 [%0], %1;" ::"r"(abort_addr), "r"(1u) : "memory");
+    if (pair) {
+      asm volatile(
+          "{\n\t.reg .b32 r, a;\n\t"
+          "mov.u32 r, %%cluster_ctarank;\n\t"
+          "xor.b32 r, r, 1;\n\t"
+          "mapa.shared::cluster.u32 a, %0, r;\n\t"
+          "st.shared::cluster.u32 [a], %1;\n\t}"
+          ::"r"(abort_addr), "r"(1u)
+          : "memory");
+    }
     if (atomicCAS(&g_status[0], 0u, code) == 0u) g_status[1] = detail;
   }
 };
@@ -94,7 +111,7 @@ __device__ __forceinline__ bool mbar_wait(WaitCtx& ctx, uint32_t bar, uint32_t p
   for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 63u) == 0u) {
-      if (*ctx.cta_abort) {
+      if (ctx.raised()) {
         ctx.aborted = true;
         return false;
       }
@@ -102,7 +119,7 @@ __device__ __forceinline__ bool mbar_wait(WaitCtx& ctx, uint32_t bar, uint32_t p
         unsigned long long now = globaltimer_ns();
         if (t0 == 0) {
           t0 = now;
-        } else if (now - t0 > kWaitTimeoutNs) {
+        } else if (now - t0 > g_wait_limit_ns) {
           ctx.fail(code, (code << 24) | (blockIdx.x & 0xffffffu));
           return false;
         }
@@ -239,6 +256,78 @@ __device__ __forceinline__ void tmem_ld_wait_pin(float* v) {
 }
 
 // ---------------------------------------------------------------------------
+// CTA pairs (cluster of two CTAs, tcgen05 with cta_group::2).  The even CTA of a
+// pair issues the MMAs for both; each CTA keeps its own 128 accumulator lanes in
+// its own TMEM and stages its own token rows plus HALF of the weight rows.
+// Barriers are always waited on locally; the signalling side reaches into the
+// other CTA with shared::cluster addresses (mapa).  No multicast form is used.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of `smem_addr` (a shared::cta address of this CTA) in the CTA of rank `rank`
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+// hardware barrier over all threads of the cluster (cannot time out: only placed where every thread arrives)
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+}
+// Arrivals on a barrier of either CTA of the pair.  Relaxed: what they hand over lives in TMEM or is written by
+// the async proxy (ordered by the tcgen05 fences and the barrier's transaction count), not in memory this thread
+// wrote, and a release at cluster scope would make the thread wait for every load it still has in flight.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx_cluster(uint32_t cluster_bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.relaxed.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_bar),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void st_shared_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+// Plain (non-multicast) tiled load into THIS CTA's shared memory whose completion bytes are counted on a barrier
+// that may live in the other CTA of the pair (`cluster_bar` is a shared::cluster address).
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const CUtensorMap* m, uint32_t cluster_bar, int x,
+                                                 int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(cluster_bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_result, uint32_t ncols) {  // same warp id in both CTAs
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_result), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {  // same warp id in both CTAs
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// D[tmem of both CTAs] (+)= A[256 rows: 128 per CTA] * B[N rows: N/2 per CTA]^T; issued by one thread of the even CTA.
+__device__ __forceinline__ void umma_f8_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// `cluster_bar` (either CTA's barrier, shared::cluster address) gets one arrival once every pair MMA issued before
+// by this thread has completed.
+__device__ __forceinline__ void umma_commit_pair(uint32_t cluster_bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar)
+               : "memory");
+}
+
+// ---------------------------------------------------------------------------
 // misc
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
@@ -280,9 +369,8 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 // bf16 rounding done by the packed two-value conversion (half the conversion
 // instructions) and the widening back to fp32 by shifts.  Returns the two bf16
 // outputs packed (.x in the low half).
-__device__ __forceinline__ uint32_t swiglu_bf16x2(float2 gate_acc, float2 up_acc) {
-  const uint32_t gp = pack_bf16x2(gate_acc.x, gate_acc.y);
-  const uint32_t up = pack_bf16x2(up_acc.x, up_acc.y);
+// `gp` / `up`: two bf16-rounded gate / up values, packed (.x in the low half).
+__device__ __forceinline__ uint32_t swiglu_packed_bf16x2(uint32_t gp, uint32_t up) {
   const float g0 = __uint_as_float(gp << 16), g1 = __uint_as_float(gp & 0xffff0000u);
   const float u0 = __uint_as_float(up << 16), u1 = __uint_as_float(up & 0xffff0000u);
   const float a0 = __fdividef(g0, 1.0f + __expf(-g0));
@@ -290,6 +378,9 @@ __device__ __forceinline__ uint32_t swiglu_bf16x2(float2 gate_acc, float2 up_acc
   const uint32_t ap = pack_bf16x2(a0, a1);
   const float r0 = __uint_as_float(ap << 16), r1 = __uint_as_float(ap & 0xffff0000u);
   return pack_bf16x2(r0 * u0, r1 * u1);
+}
+__device__ __forceinline__ uint32_t swiglu_bf16x2(float2 gate_acc, float2 up_acc) {
+  return swiglu_packed_bf16x2(pack_bf16x2(gate_acc.x, gate_acc.y), pack_bf16x2(up_acc.x, up_acc.y));
 }
 
 }  // namespace gu

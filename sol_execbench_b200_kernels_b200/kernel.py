@@ -18,10 +18,11 @@ from typing import Dict, Optional, Tuple
 import torch
 
 from . import _cabi
-from ._cabi import PLAN_AUTO, PLAN_STREAM, PLAN_TILE, PLAN_TILE_DP, PLAN_TILE_SK, GuProblem
+from ._cabi import PLAN_AUTO, PLAN_STREAM, PLAN_TILE, PLAN_TILE_DP, PLAN_TILE_PAIR, PLAN_TILE_SK, GuProblem
 
 BLOCK = 128
-_PLANS = {"auto": PLAN_AUTO, "tile": PLAN_TILE, "stream": PLAN_STREAM, "tile_dp": PLAN_TILE_DP, "tile_sk": PLAN_TILE_SK}
+_PLANS = {"auto": PLAN_AUTO, "tile": PLAN_TILE, "stream": PLAN_STREAM, "tile_dp": PLAN_TILE_DP, "tile_sk": PLAN_TILE_SK,
+          "tile_pair": PLAN_TILE_PAIR}
 
 # Scratch for the stream-K hand-off, one buffer per (device, stream): it is
 # written and consumed inside a single call and carries no result across calls.

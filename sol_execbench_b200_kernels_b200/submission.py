@@ -3,9 +3,10 @@
 The reference repository ships each kernel as a directory with a `solution.json` manifest and its sources, checks
 it (`tools/extra_kernels.py:291-393`, `load_source_manifest`), embeds the sources into one JSON artifact for the
 evaluator (`:396-486`, `build_artifact`) and condenses three evaluator traces into a summary (`:699-746`,
-`command_summarize`).  This module does the same for this package's kernels: `emit` writes a flat submission
-directory (a torch binding + the CUDA sources + manifest, language `cuda_cpp`, binding `torch`), `validate` applies
-the manifest rules and the forbidden-API audit, `package` produces the artifact bytes, `summarize` the trace summary.
+`command_summarize`).  This module serves the same file formats for this package's kernels: `emit` writes a flat
+submission directory (a torch binding + the CUDA sources + manifest, language `cuda_cpp`, binding `torch`), `validate`
+evaluates a table of manifest rules plus the forbidden-API audit and reports every broken rule at once, `package`
+produces the artifact bytes, `summarize` the trace summary.
 Pure Python, no GPU and no network; the evaluator itself is not part of this repository.
 
     python -m sol_execbench_b200_kernels_b200.submission emit 179 <dir>
@@ -71,7 +72,8 @@ PROBLEMS: Dict[str, Dict[str, Any]] = {
                        "after both GEMMs, SiLU and the product; weight-streaming stream-K plan for M <= 32.",
         "destination_passing_style": True,
         "sources": [("binding.cpp", BINDINGS / "binding_179.cpp"), ("gateup.cu", CSRC / "gateup.cu"),
-                    ("gateup_tile.cuh", CSRC / "gateup_tile.cuh"), ("gateup_stream.cuh", CSRC / "gateup_stream.cuh"),
+                    ("gateup_tile.cuh", CSRC / "gateup_tile.cuh"), ("gateup_pair.cuh", CSRC / "gateup_pair.cuh"),
+                    ("gateup_stream.cuh", CSRC / "gateup_stream.cuh"),
                     ("quantize_act.cuh", CSRC / "quantize_act.cuh"), ("reduce_gather.cuh", CSRC / "reduce_gather.cuh"),
                     ("ptx_sm100.cuh", CSRC / "ptx_sm100.cuh"), ("gateup.h", INCLUDE / "gateup.h")],
     },
@@ -153,138 +155,266 @@ def emit(problem: str, out_dir, author: str = "sol-execbench-b200-kernels") -> P
     return out
 
 
-def _need(cond: bool, message: str) -> None:
-    if not cond:
-        raise SubmissionError(message)
-
-
 def audit_source(text: str, where: str = "source") -> None:
+    """Raise if `text` names an API a submission may not use (FORBIDDEN_FRAGMENTS); `where` labels the complaint."""
     lowered = text.lower()
-    for category, fragments in FORBIDDEN_FRAGMENTS.items():
-        for fragment in fragments:
-            if fragment in lowered:
-                raise SubmissionError(f"forbidden {category} API {fragment!r} in {where}")
+    hits = [(category, fragment) for category, fragments in FORBIDDEN_FRAGMENTS.items()
+            for fragment in fragments if fragment in lowered]
+    if hits:
+        raise SubmissionError("; ".join(f"{where} uses {fragment!r} ({category})" for category, fragment in hits))
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Manifest rules.  The format is the reference's (tools/extra_kernels.py:291-393 checks the same manifest); here the
+# rules are data: each entry looks at a parsed view of the manifest and returns a complaint or nothing, every rule is
+# evaluated, and one exception carries all complaints, so a broken manifest is fixed in one pass instead of rule by rule.
+# ---------------------------------------------------------------------------------------------------------------
+class _ManifestView:
+    """What the rules look at: the manifest, its `spec` (an empty dict when it is not an object), the directory and
+    the language family the manifest declares."""
+
+    def __init__(self, manifest: Dict[str, Any], directory: Path, expected_definition: Optional[str]):
+        self.manifest = manifest
+        self.directory = directory
+        self.expected_definition = expected_definition
+        spec = manifest.get("spec")
+        self.spec: Dict[str, Any] = spec if isinstance(spec, dict) else {}
+        langs = self.spec.get("languages")
+        self.languages: List[str] = langs if isinstance(langs, list) and all(isinstance(l, str) for l in langs) else []
+        compiled = [l for l in self.languages if l in CPP_LANGUAGES]
+        scripted = [l for l in self.languages if l in PYTHON_LANGUAGES]
+        self.family = "mixed" if compiled and scripted else ("compiled" if compiled else ("python" if scripted else None))
+        srcs = manifest.get("sources")
+        self.sources: List[Any] = srcs if isinstance(srcs, list) else []
+
+    def source_paths(self) -> List[str]:
+        return [s["path"] for s in self.sources if isinstance(s, dict) and isinstance(s.get("path"), str)]
+
+
+def _listing(values) -> str:
+    return ", ".join(sorted(map(str, values))) or "none"
+
+
+def _rule_known_keys(v):
+    extra = set(v.manifest) - TOP_LEVEL_FIELDS
+    return f"solution.json has top-level keys this format does not know: {_listing(extra)}" if extra else None
+
+
+def _rule_identity(v):
+    ok = all(isinstance(v.manifest.get(k), str) and v.manifest.get(k) for k in ("name", "author"))
+    return None if ok else "`name` and `author` must both be non-empty strings"
+
+
+def _rule_definition(v):
+    want, got = v.expected_definition, v.manifest.get("definition")
+    return None if want is None or got == want else f"the manifest is for definition {got!r}, this directory must hold {want!r}"
+
+
+def _rule_spec_keys(v):
+    if not isinstance(v.manifest.get("spec"), dict):
+        return "`spec` must be an object"
+    have = set(v.spec)
+    if have == SPEC_FIELDS:
+        return None
+    return f"`spec` must have exactly its seven keys: absent {_listing(SPEC_FIELDS - have)}; not allowed {_listing(have - SPEC_FIELDS)}"
+
+
+def _rule_languages(v):
+    langs = v.spec.get("languages")
+    ok = isinstance(langs, list) and langs and all(l in ALLOWED_LANGUAGES for l in langs)
+    return None if ok or "languages" not in v.spec else f"`spec.languages` must be a non-empty list drawn from {_listing(ALLOWED_LANGUAGES)}"
+
+
+def _rule_one_family(v):
+    return "`spec.languages` combines compiled and Python languages; a submission is one or the other" if v.family == "mixed" else None
+
+
+def _rule_binding(v):
+    if v.family not in ("compiled", "python") or "binding" not in v.spec:
+        return None
+    want = "torch" if v.family == "compiled" else None
+    return None if v.spec["binding"] == want else f"`spec.binding` has to be {want!r} when the languages are {v.family}"
+
+
+def _rule_dependencies(v):
+    deps = v.spec.get("dependencies")
+    ok = isinstance(deps, list) and all(d in ALLOWED_DEPENDENCIES for d in deps)
+    return None if ok or "dependencies" not in v.spec else f"`spec.dependencies` must be a list drawn from {_listing(ALLOWED_DEPENDENCIES)}"
+
+
+def _rule_destination_passing(v):
+    ok = isinstance(v.spec.get("destination_passing_style"), bool)
+    return None if ok or "destination_passing_style" not in v.spec else "`spec.destination_passing_style` must be true or false"
+
+
+def _entry_parts(v):
+    entry = v.spec.get("entry_point")
+    if isinstance(entry, str):
+        parts = entry.split("::")
+        if len(parts) == 2 and all(parts):
+            return parts
+    return None
+
+
+def _rule_entry_shape(v):
+    return None if _entry_parts(v) or "entry_point" not in v.spec else "`spec.entry_point` must have the form file::symbol"
+
+
+def _rule_compile_options(v):
+    if v.family not in ("compiled", "python") or "compile_options" not in v.spec:
+        return None
+    options = v.spec["compile_options"]
+    want = {"cflags", "cuda_cflags", "ld_flags"} if v.family == "compiled" else set()
+    if not isinstance(options, dict) or set(options) != want:
+        return f"`spec.compile_options` must have exactly the keys {{{_listing(want)}}} for {v.family} languages"
+    bad = [k for k, flags in options.items() if not (isinstance(flags, list) and all(isinstance(f, str) for f in flags))]
+    return f"`spec.compile_options.{bad[0]}` must be a list of strings" if bad else None
+
+
+def _rule_target(v):
+    hw = v.spec.get("target_hardware")
+    ok = isinstance(hw, list) and "B200" in hw
+    return None if ok or "target_hardware" not in v.spec else "`spec.target_hardware` must be a list that names B200"
+
+
+def _rule_sources(v):
+    if not v.sources:
+        return "`sources` must be a non-empty list"
+    complaints, seen = [], set()
+    for index, entry in enumerate(v.sources):
+        if not (isinstance(entry, dict) and set(entry) == {"path"} and isinstance(entry["path"], str)):
+            complaints.append(f"`sources[{index}]` may carry the key `path` and nothing else")
+            continue
+        rel = Path(entry["path"])
+        posix = rel.as_posix()
+        if rel.is_absolute() or ".." in rel.parts:
+            complaints.append(f"`sources[{index}].path` points outside the submission directory: {posix}")
+            continue
+        if posix in seen:
+            complaints.append(f"`sources` lists {posix} twice")
+            continue
+        seen.add(posix)
+        local = v.directory / rel
+        if local.is_symlink() or not local.is_file():
+            complaints.append(f"{posix} is listed in `sources` but is not a regular file of the directory")
+            continue
+        try:
+            audit_source(local.read_text(encoding="utf-8"), posix)
+        except SubmissionError as exc:
+            complaints.append(str(exc))
+    return "; ".join(complaints) or None
+
+
+def _rule_entry_listed(v):
+    parts = _entry_parts(v)
+    if not parts or not v.sources:
+        return None
+    return None if parts[0] in v.source_paths() else f"`spec.entry_point` names {parts[0]}, which `sources` does not list"
+
+
+MANIFEST_RULES = (
+    _rule_known_keys, _rule_identity, _rule_definition, _rule_spec_keys, _rule_languages, _rule_one_family,
+    _rule_binding, _rule_dependencies, _rule_destination_passing, _rule_entry_shape, _rule_compile_options,
+    _rule_target, _rule_sources, _rule_entry_listed,
+)
 
 
 def validate(directory, definition: Optional[str] = None) -> Dict[str, Any]:
-    """Apply the reference's manifest rules to `directory/solution.json` and audit the listed sources.
-    Returns the manifest; raises SubmissionError with the first rule that fails."""
+    """Check `directory/solution.json` and the sources it lists against MANIFEST_RULES.  Returns the manifest;
+    raises SubmissionError naming every rule that is broken."""
     directory = Path(directory)
     path = directory / "solution.json"
-    _need(path.is_file(), f"{path} is missing")
+    if not path.is_file():
+        raise SubmissionError(f"{path}: no manifest")
     raw = path.read_bytes()
     try:
         manifest = json.loads(raw.decode("utf-8"))
     except ValueError as exc:
-        raise SubmissionError(f"{path} is not JSON: {exc}") from exc
-    _need(isinstance(manifest, dict), "solution.json must hold an object")
-    _need(raw == canonical_json_bytes(manifest), "solution.json is not canonical JSON")
-    unknown = set(manifest) - TOP_LEVEL_FIELDS
-    _need(not unknown, f"unsupported solution field(s): {', '.join(sorted(unknown))}")
-    if definition is not None:
-        _need(manifest.get("definition") == definition, f"solution definition does not match {definition}")
-    _need(bool(manifest.get("name")) and bool(manifest.get("author")), "solution name and author must be nonempty")
-    spec = manifest.get("spec")
-    _need(isinstance(spec, dict), "solution spec must be an object")
-    _need(set(spec) == SPEC_FIELDS, f"solution spec fields mismatch (missing={sorted(SPEC_FIELDS - set(spec))}, "
-                                    f"extra={sorted(set(spec) - SPEC_FIELDS)})")
-    languages = spec["languages"]
-    _need(isinstance(languages, list) and bool(languages) and all(l in ALLOWED_LANGUAGES for l in languages),
-          "solution languages are missing or unsupported")
-    uses_cpp = any(l in CPP_LANGUAGES for l in languages)
-    uses_python = any(l in PYTHON_LANGUAGES for l in languages)
-    _need(not (uses_cpp and uses_python), "C++ and Python solution languages cannot be mixed")
-    expected_binding = "torch" if uses_cpp else None
-    _need(spec["binding"] == expected_binding, f"solution binding must be {expected_binding!r} for its languages")
-    deps = spec["dependencies"]
-    _need(isinstance(deps, list) and all(d in ALLOWED_DEPENDENCIES for d in deps),
-          "solution dependencies are malformed or unsupported")
-    _need(isinstance(spec["destination_passing_style"], bool), "destination_passing_style must be a boolean")
-    entry = spec["entry_point"]
-    _need(isinstance(entry, str) and entry.count("::") == 1 and all(entry.split("::", 1)),
-          "solution entry point must be <source>::<symbol>")
-    options = spec["compile_options"]
-    expected_options = {"cflags", "cuda_cflags", "ld_flags"} if uses_cpp else set()
-    _need(isinstance(options, dict) and set(options) == expected_options,
-          f"compile_options fields must be {sorted(expected_options)}")
-    for key, values in options.items():
-        _need(isinstance(values, list) and all(isinstance(v, str) for v in values),
-              f"compile option {key} must be a list of strings")
-    targets = spec["target_hardware"]
-    _need(isinstance(targets, list) and "B200" in targets, "source solution must include B200 target hardware")
-    sources = manifest.get("sources")
-    _need(isinstance(sources, list) and bool(sources), "solution sources must be a nonempty list")
-    seen = set()
-    for source in sources:
-        _need(isinstance(source, dict) and set(source) == {"path"}, "source manifest entries must contain only path")
-        rel = Path(source["path"])
-        _need(not rel.is_absolute() and ".." not in rel.parts, f"unsafe source path: {rel}")
-        _need(rel.as_posix() not in seen, f"duplicate source path: {rel}")
-        seen.add(rel.as_posix())
-        local = directory / rel
-        _need(not local.is_symlink() and local.is_file(), f"missing kernel source: {rel}")
-        audit_source(local.read_text(encoding="utf-8"), rel.as_posix())
-    _need(entry.split("::", 1)[0] in seen, "entry point file is not listed in sources")
+        raise SubmissionError(f"{path} does not parse as JSON: {exc}") from exc
+    if not isinstance(manifest, dict):
+        raise SubmissionError(f"{path} must hold one JSON object")
+    complaints = []
+    if raw != canonical_json_bytes(manifest):
+        complaints.append("solution.json is not in canonical form (two-space indent, sorted keys, one final newline)")
+    view = _ManifestView(manifest, directory, definition)
+    complaints += [c for c in (rule(view) for rule in MANIFEST_RULES) if c]
+    if complaints:
+        raise SubmissionError(f"{path}: " + "; ".join(complaints))
     return manifest
 
 
 def package(directory, target: str = "B200", extra_cuda_cflags: Optional[Iterable[str]] = None) -> bytes:
-    """The artifact the evaluator takes: the manifest with every source's text embedded as `content` and the
-    target hardware narrowed to `target` (tools/extra_kernels.py:396-486)."""
+    """The single-file artifact the evaluator takes (the format `build_artifact` of the reference produces,
+    tools/extra_kernels.py:396-486): the checked manifest, with `target_hardware` narrowed to `target`, any extra
+    CUDA flags appended, and the text of every listed source stored beside its path as `content`."""
     directory = Path(directory)
     manifest = validate(directory)
-    packaged = json.loads(json.dumps(manifest))
-    packaged["spec"]["target_hardware"] = [target]
-    if extra_cuda_cflags:
-        _need(any(l in CPP_LANGUAGES for l in packaged["spec"]["languages"]),
-              "extra CUDA flags require a C++/CUDA source variant")
-        packaged["spec"]["compile_options"]["cuda_cflags"].extend(extra_cuda_cflags)
-    for source in packaged["sources"]:
-        source["content"] = (directory / source["path"]).read_text(encoding="utf-8")
-    return canonical_json_bytes(packaged)
+    spec = dict(manifest["spec"])
+    spec["target_hardware"] = [target]
+    extra = list(extra_cuda_cflags or ())
+    if extra:
+        options = spec["compile_options"]
+        if "cuda_cflags" not in options:
+            raise SubmissionError("extra CUDA flags only apply to a compiled (C++/CUDA) submission")
+        spec["compile_options"] = {**options, "cuda_cflags": [*options["cuda_cflags"], *extra]}
+    embedded = [{"path": entry["path"], "content": (directory / entry["path"]).read_text(encoding="utf-8")}
+                for entry in manifest["sources"]]
+    return canonical_json_bytes({**manifest, "spec": spec, "sources": embedded})
 
 
 def read_traces(path) -> List[Dict[str, Any]]:
-    """One JSON object per non-empty line (tools/extra_kernels.py:136-145)."""
-    traces = []
+    """The evaluator's trace file: one JSON object per line, blank lines ignored."""
+    records = []
     for number, line in enumerate(Path(path).read_text(encoding="utf-8").splitlines(), 1):
-        if not line.strip():
-            continue
-        value = json.loads(line)
-        _need(isinstance(value, dict), f"{path}: line {number} is not an object")
-        traces.append(value)
-    return traces
+        if line.strip():
+            record = json.loads(line)
+            if not isinstance(record, dict):
+                raise SubmissionError(f"{path}, line {number}: expected a JSON object")
+            records.append(record)
+    return records
+
+
+def _passed_latency(record: Dict[str, Any], trial: int, workload: int):
+    """(latency in ms, hardware label) of one trace record that must have passed."""
+    evaluation = record.get("evaluation") or {}
+    status = evaluation.get("status")
+    if status != "PASSED":
+        raise SubmissionError(f"trial {trial}, workload {workload} did not pass: {status}")
+    latency = (evaluation.get("performance") or {}).get("latency_ms")
+    if isinstance(latency, bool) or not isinstance(latency, (int, float)) or latency <= 0:
+        raise SubmissionError(f"trial {trial}, workload {workload} passed but carries no positive latency")
+    return float(latency), str((evaluation.get("environment") or {}).get("hardware", "unknown"))
 
 
 def summarize(trace_paths, workloads: int, problem_id: int, problem_name: str, contract_sha256: str) -> Dict[str, Any]:
-    """Condense exactly three evaluator traces (one per trial, `workloads` lines each) into the summary the
-    reference publishes: per-trial mean latency and per-workload mean / median; any workload that did not pass
-    makes the whole summary fail (tools/extra_kernels.py:699-746)."""
+    """Three evaluator trace files (one per trial, `workloads` records each) condensed into the summary record the
+    reference's `command_summarize` writes (tools/extra_kernels.py:699-746; the keys and the 9-digit rounding are that
+    format): mean latency per trial, mean and median per workload over the trials.  A record that did not pass, or
+    has no positive latency, fails the whole summary."""
     trace_paths = list(trace_paths)
-    _need(len(trace_paths) == 3, "exactly three trace files are required")
-    trials = [read_traces(p) for p in trace_paths]
-    _need(all(len(t) == workloads for t in trials), f"each trace must contain {workloads} workloads")
-    latencies: List[List[float]] = [[] for _ in range(workloads)]
-    hardware = set()
-    for trial_index, trial in enumerate(trials):
-        for workload_index, trace in enumerate(trial):
-            evaluation = trace.get("evaluation") or {}
-            _need(evaluation.get("status") == "PASSED",
-                  f"trial {trial_index + 1}, workload {workload_index} did not pass: {evaluation.get('status')}")
-            hardware.add(str((evaluation.get("environment") or {}).get("hardware", "unknown")))
-            latency = (evaluation.get("performance") or {}).get("latency_ms")
-            _need(isinstance(latency, (float, int)) and not isinstance(latency, bool) and latency > 0,
-                  "passed trace is missing a positive latency")
-            latencies[workload_index].append(float(latency))
-    trial_means = [statistics.fmean(latencies[w][t] for w in range(workloads)) for t in range(3)]
+    if len(trace_paths) != 3:
+        raise SubmissionError(f"a summary takes exactly three trace files, got {len(trace_paths)}")
+    table, hardware = [], set()      # table[trial][workload] = latency
+    for trial, path in enumerate(trace_paths, 1):
+        records = read_traces(path)
+        if len(records) != workloads:
+            raise SubmissionError(f"{path}: a trace must contain {workloads} records, this one has {len(records)}")
+        row = []
+        for workload, record in enumerate(records):
+            latency, label = _passed_latency(record, trial, workload)
+            row.append(latency)
+            hardware.add(label)
+        table.append(row)
+    per_workload = list(zip(*table))  # columns: one workload over the three trials
+    digits = 9
     return {
         "contract_sha256": contract_sha256,
         "hardware": sorted(hardware),
         "problem_id": int(problem_id),
         "problem_name": problem_name,
-        "trial_mean_latency_ms": [round(v, 9) for v in trial_means],
-        "workloads": [{"latency_ms_mean": round(statistics.fmean(v), 9),
-                       "latency_ms_median": round(statistics.median(v), 9)} for v in latencies],
+        "trial_mean_latency_ms": [round(statistics.fmean(row), digits) for row in table],
+        "workloads": [{"latency_ms_mean": round(statistics.fmean(col), digits),
+                       "latency_ms_median": round(statistics.median(col), digits)} for col in per_workload],
     }
 
 
@@ -297,7 +427,8 @@ def build_extension(directory, build_dir, name: Optional[str] = None, verbose: b
     directory, build_dir = Path(directory), Path(build_dir)
     manifest = validate(directory)
     spec = manifest["spec"]
-    _need(any(l in CPP_LANGUAGES for l in spec["languages"]), "only C++/CUDA submissions are compiled")
+    if not any(l in CPP_LANGUAGES for l in spec["languages"]):
+        raise SubmissionError("only compiled (C++/CUDA) submissions can be built")
     name = name or f"submission_{manifest['definition']}"
     build_dir.mkdir(parents=True, exist_ok=True)
     os.environ.setdefault("TORCH_CUDA_ARCH_LIST", "10.0a")

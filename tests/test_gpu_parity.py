@@ -80,6 +80,20 @@ def test_tile_kernel_parity(pkg, shape):
     _check(_run(pkg, inp, "tile"), inp, f"tile {shape}")
 
 
+PAIR_SHAPES = TILE_SHAPES + [(256, 128, 128), (384, 512, 256), (257, 256, 256), (512, 1024, 1792), (2000, 256, 640),
+                            (1, 256, 128)]
+
+
+@pytest.mark.parametrize("shape", PAIR_SHAPES)
+def test_pair_kernel_parity_and_equality_with_the_lone_cta_kernel(pkg, shape):
+    # CTA pairs (cta_group::2, 256-token tiles) forced for every M, also where the second CTA of a pair has no
+    # rows at all; same block order and FMA chain as the lone-CTA kernel, so the bits must be identical
+    inp = W.make_inputs(*shape, seed=1)
+    out = _run(pkg, inp, "tile_pair")
+    _check(out, inp, f"tile_pair {shape}")
+    assert torch.equal(out, _run(pkg, inp, "tile_dp"))
+
+
 @pytest.mark.parametrize("shape", TILE_SHAPES + [(128, 4096, 2048), (512, 1024, 1792), (2000, 256, 640)])
 def test_tile_kernel_stream_k_schedule_parity(pkg, shape):
     # same kernel, (tile, K block) units cut into equal ranges: partial sums cross CTAs through scratch
@@ -97,8 +111,9 @@ def test_stream_kernel_parity(pkg, shape):
 
 
 @pytest.mark.parametrize("shape", [(1, 512, 384), (16, 1024, 1024), (64, 1024, 1280), (48, 4096, 1792)])
-def test_both_kernels_agree_bit_for_bit_on_small_m(pkg, shape):
-    # same block order, same fp32 FMA chain (stream-K splits fall on K-block boundaries and add in order)
+def test_both_kernels_agree_within_tolerance_on_small_m(pkg, shape):
+    # same block order and FMA form; where a stream-K range boundary falls inside a column block the streaming kernel
+    # adds the ranges' partial sums (another association), so single roundings may differ
     inp = W.make_inputs(*shape, seed=3)
     a = _run(pkg, inp, "tile")
     b = _run(pkg, inp, "stream")
@@ -120,7 +135,8 @@ def test_small_config_through_public_run(pkg):
 
 
 def test_deterministic(pkg):
-    for shape, plan in (((300, 512, 384), "tile_dp"), ((300, 512, 384), "tile_sk"), ((128, 4096, 2048), "tile_sk"),
+    for shape, plan in (((300, 512, 384), "tile_dp"), ((300, 512, 384), "tile_pair"), ((1024, 1024, 1024), "tile"),
+                        ((300, 512, 384), "tile_sk"), ((128, 4096, 2048), "tile_sk"),
                         ((16, 8192, 2048), "stream"), ((7, 2048, 5632), "stream")):
         inp = W.make_inputs(*shape, seed=4)
         a = _run(pkg, inp, plan).clone()
