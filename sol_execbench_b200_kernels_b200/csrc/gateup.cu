@@ -134,7 +134,9 @@ int device_info(DeviceInfo** out) {
             cudaSuccess ||
         cudaFuncSetAttribute(gateup_stream_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
             cudaSuccess ||
-        cudaFuncSetAttribute(gateup_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
+        cudaFuncSetAttribute(gateup_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
+        cudaFuncSetAttribute(blockwise_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
+            cudaSuccess) {
       cudaGetLastError();
       return GU_ECUDA;
     }
@@ -889,6 +891,30 @@ int gu_blockwise_gemm(const void* a, const float* scale_a, const void* b, const 
   p.scale_out = nullptr;
   p.blocks_per_owner = 1;
   p.slot_rows = 0;
+  if (gu::tile_prefers_pairs(m, *dev)) {
+    // CTA pairs: 256-token x 256-column tiles, one per two-CTA cluster
+    p.num_m_blocks = static_cast<int>((m + 2 * gu::kTileM - 1) / (2 * gu::kTileM));
+    p.num_n_blocks = (p.n_blocks128 + 1) / 2;
+    const int64_t pair_tiles = int64_t(p.num_m_blocks) * p.num_n_blocks;
+    if (pair_tiles * (k / 128) >= (1ll << 31)) return GU_EINVAL_SHAPE;
+    p.num_tiles = static_cast<int>(pair_tiles);
+    int64_t pgm = (24ll << 20) / (256 * k);
+    if (pgm < 1) pgm = 1;
+    if (pgm > p.num_m_blocks) pgm = p.num_m_blocks;
+    p.group_m = static_cast<int>(pgm);
+    p.tile_begin = 0;
+    p.flags = nullptr;
+    p.partials = nullptr;
+    p.epoch = 0;
+    p.out_count = 1;
+    p.out_rank = 0;
+    p.out_col0 = 0;
+    const int clusters = p.num_tiles < dev->pair_clusters ? p.num_tiles : dev->pair_clusters;
+    gu::blockwise_gemm_pair_kernel<<<2 * clusters, gu::kPairThreads, gu::kPairSmemBytes,
+                                     static_cast<cudaStream_t>(stream_v)>>>(tm_a, tm_b, tm_c, p);
+    gu::g_launches.fetch_add(1, std::memory_order_relaxed);
+    return cudaGetLastError() == cudaSuccess ? GU_OK : GU_ECUDA;
+  }
   p.num_m_blocks = static_cast<int>((m + gu::kTileM - 1) / gu::kTileM);
   p.num_n_blocks = (p.n_blocks128 + 1) / 2;  // a CTA tile spans two 128-column blocks of B
   const int64_t tiles = int64_t(p.num_m_blocks) * p.num_n_blocks;

@@ -90,6 +90,7 @@ enum : unsigned {
 //                3 the issuer waits for each K block's completion before going on (issue-to-completion latency)
 //                4 as 2, and the issuer never waits for the consumers: MMA + TMA + issuer alone
 //                5 as 3 and 4 together: one K block in flight on an otherwise idle SM
+//                6 consumers do the promotion arithmetic on stale registers but never read TMEM
 //   -DGU_PAIR_THREADS=512, -DGU_PIECE=32, -DGU_INFLIGHT=1, -DGU_PAIR_STAGES=5   layout variants that were measured
 #ifdef GU_TRACE
 // Cycle counters of cluster 0 (both CTAs), summed over the launch: [rank][slot]
@@ -132,7 +133,7 @@ __device__ __forceinline__ void pair_fma(float2* sums, const float* piece, float
 }
 
 __device__ __forceinline__ void pair_ld(uint32_t taddr, float* v) {
-#if defined(GU_EXP) && (GU_EXP == 2 || GU_EXP == 4 || GU_EXP == 5)
+#if defined(GU_EXP) && (GU_EXP == 2 || GU_EXP == 4 || GU_EXP == 5 || GU_EXP == 6)
   (void)taddr;  // experiment: the partial is not read at all
   (void)v;
 #else
@@ -157,10 +158,15 @@ __device__ __forceinline__ void mbar_wait_lane(WaitCtx& ctx, bool elected, uint3
 }
 
 // TileParams as used here: num_m_blocks / group_m count 256-token pair blocks, num_tiles pair tiles.
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
-gateup_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_gate,
-                   const __grid_constant__ CUtensorMap tm_up, const __grid_constant__ CUtensorMap tm_out,
-                   const TileParams p) {
+//
+// kSingle: the same pipeline as a plain block-scaled GEMM, C = bf16(sum_kb scale_a * scale_b * (A_kb . B_kb^T)) — the
+// GEMM the reference launches twice (kernel.py:487-488); here the MLP's down projection.  The two 128-row weight
+// tiles of a K block are then two ADJACENT 128-column blocks of one B matrix (tm_gate; scale rows 2n and 2n+1 of
+// scale_gate), a pair tile is 256 x 256 outputs, and the epilogue warps only issue the stores of the handed-over tiles.
+template <bool kSingle>
+__device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tm_x, const CUtensorMap& tm_gate,
+                                                 const CUtensorMap& tm_up, const CUtensorMap& tm_out,
+                                                 const TileParams& p) {
   extern __shared__ uint8_t smem_raw[];
   // operand tiles need 1024-byte alignment for the 128-byte swizzle pattern; both CTAs of a pair get the same offsets
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -244,8 +250,15 @@ gateup_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
           if (ok && elected) {
             mbar_arrive_expect_tx_cluster(full, kPairStageBytes);
             tma_load_2d_pair(dst, &tm_x, full, j * kBlockK, row0);  // rows past M read as zero
-            // B rows [0, 128) of the MMA = the gate block (even CTA), [128, 256) = the up block (odd CTA)
-            tma_load_2d_pair(dst + kOperandTileBytes, rank == 0 ? &tm_gate : &tm_up, full, j * kBlockK, nb * kTileN);
+            if constexpr (kSingle) {
+              // B rows [0, 128) of the MMA = column block 2 nb of the one B matrix (even CTA), [128, 256) = block
+              // 2 nb + 1 (odd CTA; rows past N read as zero)
+              tma_load_2d_pair(dst + kOperandTileBytes, &tm_gate, full, j * kBlockK,
+                               (2 * nb + static_cast<int>(rank)) * kTileN);
+            } else {
+              // B rows [0, 128) of the MMA = the gate block (even CTA), [128, 256) = the up block (odd CTA)
+              tma_load_2d_pair(dst + kOperandTileBytes, rank == 0 ? &tm_gate : &tm_up, full, j * kBlockK, nb * kTileN);
+            }
           }
           __syncwarp();
         }
@@ -330,6 +343,25 @@ gateup_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
         named_bar_sync(2, kPairEpiThreads);
         GU_TR_END(8);
         GU_TR_BEGIN();
+        if constexpr (kSingle) {
+          // both handed-over tiles are final (and fenced by their writers): four half-tile stores, nothing to compute
+          if (et == 0) {
+            if (ok && !ctx.aborted && row0 < p.m) {
+              tma_store_2d(&tm_out, hand, 2 * nb * kTileN, row0);
+              tma_store_2d(&tm_out, hand + kTileOutHalfBytes, 2 * nb * kTileN + 64, row0);
+              if (2 * nb + 1 < p.n_blocks128) {
+                tma_store_2d(&tm_out, hand + 2 * kTileOutHalfBytes, (2 * nb + 1) * kTileN, row0);
+                tma_store_2d(&tm_out, hand + 3 * kTileOutHalfBytes, (2 * nb + 1) * kTileN + 64, row0);
+              }
+              tma_store_commit();
+              tma_store_wait_read0();
+            }
+            mbar_arrive(bar_hand_empty);
+          }
+          GU_TR_END(7);
+          hand_phase ^= 1u;
+          continue;
+        }
         // gate and up tiles have the same layout, so chunk q of one meets chunk q of the other whatever it holds
 #pragma unroll 4
         for (int i = 0; i < 2048 / kPairEpiThreads; ++i) {
@@ -369,7 +401,7 @@ gateup_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     const int row = quarter * 32 + lane;   // token row inside this CTA's 128
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + proj * kTileN;
     const uint32_t stage_free_even = mapa_shared(bar_stage_free, 0);
-    const float* scale_w = proj ? p.scale_up : p.scale_gate;
+    const float* scale_w = (proj && !kSingle) ? p.scale_up : p.scale_gate;
     uint32_t blocks_done = 0;  // K blocks walked so far: accumulator stage = bit 0, ring stage = low bits, phases above
     uint32_t hand_phase = 0;
 
@@ -383,7 +415,8 @@ gateup_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
       tile_coords(p, t, pm, nb);
       const int m_global = min((2 * pm + static_cast<int>(rank)) * kTileM + row, p.m - 1);
       sx_off = static_cast<uint32_t>(m_global) * static_cast<uint32_t>(p.kb);
-      sw_off = static_cast<uint32_t>(nb) * static_cast<uint32_t>(p.kb);
+      const int wblock = kSingle ? min(2 * nb + static_cast<int>(proj), p.n_blocks128 - 1) : nb;
+      sw_off = static_cast<uint32_t>(wblock) * static_cast<uint32_t>(p.kb);
       sx0 = __ldg(p.scale_x + sx_off);
       sw0 = __ldg(scale_w + sw_off);
     };
@@ -398,6 +431,13 @@ gateup_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
       float va[kPairPiece], vb[kPairPiece], vc[kPairInFlight == 2 ? kPairPiece : 1], vd[kPairInFlight == 2 ? kPairPiece : 1];
 #pragma unroll
       for (int i = 0; i < 64; ++i) sums[i] = make_float2(0.f, 0.f);
+#if defined(GU_EXP) && GU_EXP == 6
+#pragma unroll
+      for (int i = 0; i < kPairPiece; ++i) {
+        va[i] = vb[i] = 1.f;
+        if (kPairInFlight == 2) vc[i] = vd[i] = 1.f;
+      }
+#endif
 #ifdef GU_TRACE
       const unsigned long long tr_loop0 = clock64();
 #endif
@@ -486,6 +526,7 @@ gateup_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
           *reinterpret_cast<uint4*>(tile_row + (c >> 3) * kTileOutHalfBytes + (((c & 7) ^ (row & 7)) << 4)) = q;
         }
       }
+      if constexpr (kSingle) fence_proxy_async_smem();  // these bytes are read by the TMA stores as they are
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_hand_full);
       GU_TR_END(6);
@@ -511,6 +552,20 @@ gateup_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
 #ifdef GU_TRACE
   if (blockIdx.x < 2 && threadIdx.x == 0) atomicAdd(&g_trace[blockIdx.x & 1][9], (unsigned long long)(clock64() - tr_cta0));
 #endif
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
+gateup_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_gate,
+                   const __grid_constant__ CUtensorMap tm_up, const __grid_constant__ CUtensorMap tm_out,
+                   const TileParams p) {
+  pair_kernel_body<false>(tm_x, tm_gate, tm_up, tm_out, p);
+}
+
+// Plain block-scaled GEMM (single-projection mode) on CTA pairs.
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
+blockwise_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                           const __grid_constant__ CUtensorMap tm_c, const TileParams p) {
+  pair_kernel_body<true>(tm_a, tm_b, tm_b, tm_c, p);
 }
 
 }  // namespace gu

@@ -5,7 +5,7 @@ Needs a B200, the image's CUTLASS tree (the reference loads NVIDIA's CuTe-DSL bl
 example from $CUTLASS_DIR) and an unmodified copy of the reference's kernel directory at
 baseline/_ref/179_fp8_mlp_gate_up_projection (git-ignored).  Usage, from the repository root:
 
-    python tests/golden/make_golden.py --out <directory> [--time]
+    python tests/golden/make_golden.py --out <directory> [--only NAME[,NAME...]]
 
 Each shape runs in a fresh process because the reference caches its compiled kernel under a key
 that omits K and N (kernel.py:263).  For every shape a `<name>.pt` (sampled rows/columns of the
@@ -32,8 +32,10 @@ SHAPES = {
     "ref_square_128x512x512": (128, 512, 512, 21, 1, 1),
     "ref_native_256x3584x18944": (256, 3584, 18944, 22, 4, 37),
     "ref_256x1024x1024": (256, 1024, 1024, 23, 2, 2),
+    # the two large configurations of the benchmark line (tensor-bound prefill, and the shape that is column-sharded)
+    "ref_prefill_8b_4096x4096x14336": (4096, 4096, 14336, 0, 157, 37),
+    "ref_prefill_sharded_16384x7168x18432": (16384, 7168, 18432, 0, 1021, 37),
 }
-TIMED = {"prefill_8b": (4096, 4096, 14336), "reference_native_m4096": (4096, 3584, 18944)}
 
 
 def _load_reference():
@@ -83,51 +85,16 @@ def _one(name: str, out_dir: str) -> None:
     print(name, json.dumps(stats), flush=True)
 
 
-def _time(name: str, out_dir: str) -> None:
-    import torch
-
-    sys.path.insert(0, ROOT)
-    from sol_execbench_b200_kernels_b200 import workloads as W
-
-    ref = _load_reference()
-    m, k, n = TIMED[name]
-    g = W.make_inputs(m, k, n, seed=0, device="cuda:0")
-    out = torch.empty(m, n, dtype=torch.bfloat16, device="cuda:0")
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda:0")
-    for _ in range(5):
-        ref.run(*g.args(), out)
-    torch.cuda.synchronize()
-    times = []
-    for _ in range(20):
-        flush.zero_()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        ref.run(*g.args(), out)
-        b.record()
-        torch.cuda.synchronize()
-        times.append(a.elapsed_time(b))
-    times.sort()
-    med = times[len(times) // 2]
-    res = {"shape": [m, k, n], "median_ms": med, "min_ms": times[0], "tflops_median": 4.0 * m * k * n / (med * 1e-3) / 1e12,
-           "what": "reference kernel.py::run (2 CuTe-DSL GEMMs + Triton SwiGLU), CUDA events, L2 flushed between calls"}
-    os.makedirs(out_dir, exist_ok=True)
-    with open(os.path.join(out_dir, f"reference_gpu_time_{name}.json"), "w") as f:
-        json.dump(res, f, indent=1)
-    print(name, json.dumps(res), flush=True)
-
-
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--out", default=os.path.join(ROOT, "tests", "golden", "_generated"))
-    ap.add_argument("--time", action="store_true", help="also time the reference kernel on two large shapes")
+    ap.add_argument("--only", default=None, help="comma-separated fixture names to (re)generate instead of all")
     ap.add_argument("--one", default=None)
-    ap.add_argument("--time-one", default=None)
     args = ap.parse_args()
     if args.one:
         return _one(args.one, args.out)
-    if args.time_one:
-        return _time(args.time_one, args.out)
-    jobs = [["--one", n] for n in SHAPES] + ([["--time-one", n] for n in TIMED] if args.time else [])
+    names = [n for n in SHAPES if not args.only or n in args.only.split(",")]
+    jobs = [["--one", n] for n in names]
     failed = 0
     for job in jobs:
         rc = subprocess.run([sys.executable, os.path.abspath(__file__), "--out", args.out, *job], timeout=900).returncode

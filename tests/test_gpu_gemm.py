@@ -35,6 +35,25 @@ def test_blockwise_gemm_parity(shape):
     assert torch.equal(out.cpu(), O.gemm_blockwise(a, sa, b, sb)) or O.error_stats(out, O.gemm_blockwise(a, sa, b, sb))["rel_l2"] < 1e-4
 
 
+@pytest.mark.parametrize("shape", [(300, 512, 640), (513, 1024, 384), (1024, 2048, 128), (777, 256, 1152)])
+def test_blockwise_gemm_on_cta_pairs_equals_the_lone_cta_kernel_row_block_by_row_block(shape):
+    # more than 128 rows run on CTA pairs (256 x 256 tiles); token rows are independent, so the same rows fed in
+    # blocks of at most 128 (the lone-CTA kernel) must give the same bits — including an odd number of column blocks
+    import sol_execbench_b200_kernels_b200 as pkg
+
+    m, k, n = shape
+    a, sa, b, sb = (t.cuda() for t in _operands(m, k, n, seed=60 + m))
+    whole = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda:0")
+    pkg.blockwise_gemm(a, sa, b, sb, whole)
+    pieces = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda:0")
+    for lo in range(0, m, 128):
+        hi = min(m, lo + 128)
+        pkg.blockwise_gemm(a[lo:hi].contiguous(), sa[lo:hi].contiguous(), b, sb, pieces[lo:hi])
+    torch.cuda.synchronize()
+    assert pkg.last_status()[0] == 0
+    assert torch.equal(whole, pieces)
+
+
 def test_blockwise_gemm_pitched_output_and_errors():
     import sol_execbench_b200_kernels_b200 as pkg
 

@@ -4,7 +4,9 @@ It exists for hosts that may not allocate device memory themselves — a serving
 owns all of HBM and forbids cudaMalloc after start-up, or a decode loop that cannot take the
 device-wide synchronisation an allocation brings — so they have no workspace to pass to gu_run.
 The test calls it through the C ABI twice in a row and checks each result against gu_run (same
-kernel, caller-supplied workspace), with the tolerances of the other GPU tests.  The file sorts last
+kernel, caller-supplied workspace) and against the CPU oracle, with the tolerances of the other GPU
+tests, and that the device's free memory is the same before and after the second call (nothing was
+allocated behind the caller's back).  The file sorts last
 so that a run that stops at the first failure has already run every other test; it also passes
 on its own in a fresh process (the first call does the per-device set-up).
 """
@@ -13,6 +15,7 @@ import ctypes
 import pytest
 import torch
 
+from oracle import gateup_oracle as O
 from sol_execbench_b200_kernels_b200 import workloads as W
 
 pytestmark = pytest.mark.gpu
@@ -49,14 +52,26 @@ def test_static_scratch_entry_point_matches_workspace_entry_point(shape):
         pr = _problem(_cabi, g, want, m, k, n, ws, nbytes, _cabi.PLAN_STREAM)
         assert lib.gu_run(ctypes.byref(pr), stream) == 0
         ps = _problem(_cabi, g, got, m, k, n)              # no workspace at all
+        torch.cuda.synchronize()
+        free_before, _ = torch.cuda.mem_get_info(dev)
         assert lib.gu_run_decode_static(ctypes.byref(ps), stream) == 0
         torch.cuda.synchronize()
+        free_after, _ = torch.cuda.mem_get_info(dev)
+        if call == 1:                                       # (the first call on a device may load the module)
+            assert free_after == free_before, (free_before, free_after)
         detail = ctypes.c_int(0)
         assert lib.gu_last_status(ctypes.byref(detail), 1) == 0, hex(detail.value)
         assert torch.isfinite(got.float()).all() and not (got == 0).all()
         diff = (got.float() - want.float())
         assert diff.abs().max().item() <= ATOL
         assert (torch.linalg.vector_norm(diff) / torch.linalg.vector_norm(want.float())).item() <= REL_L2
+        # and against the CPU restatement, on every token and a few column blocks
+        blocks = torch.tensor(sorted({0, n // 256, n // 128 - 1}), device=dev)
+        sub = g.column_blocks(blocks).to("cpu")
+        cols = (blocks[:, None] * 128 + torch.arange(128, device=dev)[None]).reshape(-1)
+        for oracle in (O.gateup_blockwise, O.gateup_dequant):
+            st = O.error_stats(got[:, cols].cpu(), oracle(*sub.args()))
+            assert st["rel_l2"] <= REL_L2 and (st["max_abs"] <= ATOL or st["min_abs_ref_over"] >= 2.0), st
 
 
 def test_static_scratch_entry_point_rejects_more_than_16_tokens():
