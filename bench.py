@@ -373,10 +373,19 @@ def run_ours(args):
     # ---- end to end through the public host-memory entry point: pinned host activations in, host result out ----
     from sol_execbench_b200_kernels_b200.host_pipeline import HostPipeline
 
-    x_host = local.x.cpu().view(torch.uint8).pin_memory().view(torch.float8_e4m3fn)
-    sx_host = local.scale_x.cpu().pin_memory()
     out_host = torch.empty(m, n_local, dtype=torch.bfloat16).pin_memory()
-    pipe = HostPipeline(m, k, n_local, dev, chunks=args.e2e_chunks)
+    if n_gpus > 1:
+        # every rank holds only its row block of the activations in host memory; the blocks are exchanged over NVLink
+        from sol_execbench_b200_kernels_b200.host_pipeline import ShardedHostPipeline
+
+        pipe = ShardedHostPipeline(m, k, n_local, dev, chunks=max(1, args.e2e_chunks // 2))
+        lo, hi = rank * pipe.block_rows, (rank + 1) * pipe.block_rows
+        x_host = local.x[lo:hi].cpu().view(torch.uint8).pin_memory().view(torch.float8_e4m3fn)
+        sx_host = local.scale_x[lo:hi].cpu().pin_memory()
+    else:
+        pipe = HostPipeline(m, k, n_local, dev, chunks=args.e2e_chunks)
+        x_host = local.x.cpu().view(torch.uint8).pin_memory().view(torch.float8_e4m3fn)
+        sx_host = local.scale_x.cpu().pin_memory()
 
     def e2e_step():
         pipe.run(x_host, sx_host, local.gate_proj_weight, local.scale_gate, local.up_proj_weight, local.scale_up,
@@ -407,9 +416,15 @@ def run_ours(args):
            "pcie": {**pcie, "copy_bound_ms": round(copy_s * 1e3, 4),
                     "ceiling": round(flops_job / max(copy_s, ms_per_step * 1e-3) / 1e12, 1),
                     "note": "ceiling = the metric if a step took only the slower of its host copies (or the kernel)"},
-           "note": "HostPipeline.run: weights resident in HBM; x and scale_x copied from pinned host memory and the "
-                   f"bf16 output copied back to pinned host memory every step, in {len(pipe.bounds)} row chunks on three streams; "
-                   "wall clock"}
+           "note": ("HostPipeline.run: weights resident in HBM; x and scale_x copied from pinned host memory and the "
+                    f"bf16 output copied back to pinned host memory every step, in {len(pipe.bounds)} row chunks on three "
+                    "streams; wall clock") if n_gpus == 1 else
+                   ("ShardedHostPipeline.run: every rank copies its M/R row block of x and scale_x from pinned host "
+                    "memory, the blocks are exchanged over NVLink (NCCL all-gather), every rank copies its [M, N/R] slice "
+                    f"of the bf16 output back to pinned host memory, in {len(pipe.bounds)} row chunks on three streams; "
+                    "bytes are per rank; wall clock, max over ranks")}
+    if n_gpus > 1:
+        e2e["nvlink_bytes_in_per_step"] = pipe.bytes_nvlink_in
 
     result = None
     parity = None

@@ -179,6 +179,20 @@ int gu_reduce_gather(const void* slots, void* const* rank_outputs, int world, in
                      void* stream);
 
 /*
+ * Cross-rank barrier for the fused gather / reduce entry points above, enqueued on `stream`: a one-warp kernel in
+ * which this rank stamps its slot in every rank's flag array (plain stores, over NVLink for the peers) and then
+ * polls its OWN array until all `world` slots carry the stamp; everything this rank's earlier launches on the
+ * stream wrote to peer memory is visible to a peer once that peer has passed the barrier.  rank_flags[r] is rank r's
+ * flag array as mapped into this process: 64 uint32 of symmetric / peer-mapped memory, zeroed once (with a host-side
+ * barrier after the zeroing) before the first use and touched by nothing else.  Every rank must call it the same
+ * number of times.  The wait is bounded: after `limit_ns` nanoseconds (0: 2 s) the kernel gives up, gu_last_status
+ * reports GU_ETIMEOUT with wait id 20 and the index of a rank that did not arrive, and the context stays usable —
+ * where the reference's only cross-CTA wait spins without bound (blockwise_gemm_fused.py:85-91).  No load touches
+ * peer memory, nothing is multicast.  The reference is single-GPU: no counterpart.
+ */
+int gu_peer_barrier(void* const* rank_flags, int world, int rank, uint64_t limit_ns, void* stream);
+
+/*
  * Activation quantiser, the step in front of gu_run: x[M, K] (bf16, or fp32 when x_is_f32 != 0; row pitch ld_x
  * elements) -> q[M, K] e4m3 and scale[M, K/128] fp32 with scale = amax of the 1x128 block / 448, the layout
  * `x` / `scale_x` of gu_problem.  The reference takes its activations already quantised

@@ -10,13 +10,13 @@ with `python -m sol_execbench_b200_kernels_b200.build`.  Importing the compute
 entry points without the built library raises: there is no fallback path.
 """
 from . import workloads  # noqa: F401  (pure torch, no native code)
-from .sharded import (GatherBuffers, ReduceBuffers, assemble_gathered, gather_columns, mlp_block_sharded,  # noqa: F401
+from .sharded import (GatherBuffers, PeerBarrier, ReduceBuffers, assemble_gathered, gather_columns, mlp_block_sharded,  # noqa: F401
                       mlp_block_sharded_fused, owned_rows,
                       run_sharded, run_sharded_fused, shard_bounds, shard_concat_weights, shard_down_weights,
                       shard_weights)
 
 _NATIVE = ("run", "run_concat", "run_with_plan", "run_gather", "quantize_activation", "blockwise_gemm", "blockwise_gemm_scatter", "reduce_gather", "run_fp8_output", "mlp_block", "select_plan", "last_status",
-           "launch_count")
+           "launch_count", "peer_barrier")
 
 
 def __getattr__(name):
@@ -29,4 +29,4 @@ def __getattr__(name):
 
 __all__ = list(_NATIVE) + ["workloads", "run_sharded", "run_sharded_fused", "GatherBuffers", "shard_bounds",
                            "shard_weights", "shard_concat_weights", "shard_down_weights", "mlp_block_sharded", "mlp_block_sharded_fused", "ReduceBuffers", "owned_rows",
-                           "gather_columns", "assemble_gathered"]
+                           "gather_columns", "assemble_gathered", "PeerBarrier"]

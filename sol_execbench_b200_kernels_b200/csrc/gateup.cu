@@ -774,6 +774,24 @@ int gu_reduce_gather(const void* slots, void* const* rank_outputs, int world, in
   return cudaGetLastError() == cudaSuccess ? GU_OK : GU_ECUDA;
 }
 
+int gu_peer_barrier(void* const* rank_flags, int world, int rank, uint64_t limit_ns, void* stream_v) {
+  if (!rank_flags) return GU_EINVAL_NULL;
+  if (world < 1 || world > 8 || rank < 0 || rank >= world) return GU_EINVAL_SHAPE;
+  gu::PeerBarrierParams p;
+  std::memset(&p, 0, sizeof(p));
+  for (int r = 0; r < world; ++r) {
+    if (!rank_flags[r]) return GU_EINVAL_NULL;
+    if (reinterpret_cast<uintptr_t>(rank_flags[r]) & 3u) return GU_EINVAL_ALIGN;
+    p.flags[r] = static_cast<unsigned int*>(rank_flags[r]);
+  }
+  p.world = world;
+  p.rank = rank;
+  p.limit_ns = limit_ns ? limit_ns : 2000000000ull;
+  gu::peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream_v)>>>(p);
+  gu::g_launches.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError() == cudaSuccess ? GU_OK : GU_ECUDA;
+}
+
 int gu_quantize_activation(const void* x, int x_is_f32, int64_t ld_x, void* q, float* scale, int64_t m, int64_t k,
                            void* stream_v) {
   if (!x || !q || !scale) return GU_EINVAL_NULL;

@@ -10,6 +10,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "ptx_sm100.cuh"
+
 namespace gu {
 
 struct ReduceGatherParams {
@@ -46,6 +48,58 @@ __global__ void __launch_bounds__(256) reduce_gather_kernel(const ReduceGatherPa
     for (int d = 0; d < 8; ++d)  // unrolled so that the pointer table stays in the parameter space
       if (d < p.world && p.outputs[d] != nullptr) p.outputs[d][p.out_word0 + i] = r;
   }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Cross-rank barrier of one box, on the stream: every rank stamps its slot in every rank's flag array (plain
+// stores, local and over NVLink) with this call's epoch and then polls ITS OWN array until every slot carries
+// that epoch.  No load touches peer memory, and the wait is bounded: after `limit_ns` it records
+// (GU_ETIMEOUT, wait id 20, missing rank) in the status word and the kernel returns, so a rank that never
+// arrives costs its peers the time limit and an error code, not a hung GPU.
+// Flag array of a rank (64 words, zeroed once before first use): [0, 8) arrival stamps by rank, [16] the number
+// of barriers this rank has passed.  All ranks call the barrier the same number of times, so the counters agree.
+// ---------------------------------------------------------------------------------------------------------
+constexpr unsigned kWaitPeerBarrier = 20;
+constexpr int kPeerFlagWords = 64;
+
+struct PeerBarrierParams {
+  unsigned int* flags[8];  // every rank's flag array as mapped into this process
+  int world, rank;
+  unsigned long long limit_ns;
+};
+
+__global__ void __launch_bounds__(32) peer_barrier_kernel(const PeerBarrierParams p) {
+  const int t = threadIdx.x;
+  unsigned int* mine = p.flags[p.rank];
+  const unsigned int epoch = *reinterpret_cast<volatile unsigned int*>(mine + 16) + 1u;
+  __syncwarp();
+  unsigned int missing = 0;
+  if (t < p.world) {
+    // everything this rank's earlier kernels on the stream wrote (to any rank) is visible before the stamp is
+    asm volatile("fence.acq_rel.sys;" ::: "memory");
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.flags[t] + p.rank), "r"(epoch) : "memory");
+    unsigned long long t0 = 0;
+    for (unsigned int it = 1;; ++it) {
+      unsigned int v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine + t) : "memory");
+      if (static_cast<int>(v - epoch) >= 0) break;  // (a peer may already be one barrier ahead)
+      if ((it & 63u) == 0u) {
+        const unsigned long long now = globaltimer_ns();
+        if (t0 == 0) {
+          t0 = now;
+        } else if (now - t0 > p.limit_ns) {
+          missing = 1;
+          if (atomicCAS(&g_status[0], 0u, kWaitPeerBarrier) == 0u)
+            g_status[1] = (kWaitPeerBarrier << 24) | static_cast<unsigned int>(t);
+          break;
+        }
+        spin_backoff_ns(200u);
+      }
+    }
+  }
+  (void)missing;
+  __syncwarp();
+  if (t == 0) *reinterpret_cast<volatile unsigned int*>(mine + 16) = epoch;
 }
 
 }  // namespace gu

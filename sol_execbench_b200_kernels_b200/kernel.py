@@ -312,6 +312,20 @@ def reduce_gather(slots: torch.Tensor, rank_output_ptrs, rank: int, m: int, h: i
     _raise_for(code)
 
 
+def peer_barrier(rank_flag_ptrs, rank: int, device, limit_ns: int = 0) -> None:
+    """Enqueue the library's bounded cross-rank barrier on the current stream of `device`.  `rank_flag_ptrs[r]` is
+    the device address of rank r's 64-word flag array as mapped into this process (see `sharded.PeerBarrier`);
+    `limit_ns` = 0 keeps the default time limit of 2 s.  Asynchronous; a rank that never arrives shows up as
+    GU_ETIMEOUT in `last_status`, not as a hang."""
+    world = len(rank_flag_ptrs)
+    dev = torch.device(device)
+    with torch.cuda.device(dev):
+        stream_ptr = torch.cuda.current_stream(dev).cuda_stream
+        ptrs = (ctypes.c_void_p * world)(*[int(p) for p in rank_flag_ptrs])
+        code = _cabi.lib.gu_peer_barrier(ptrs, world, rank, int(limit_ns), stream_ptr)
+    _raise_for(code)
+
+
 @torch.no_grad()
 def quantize_activation(x: torch.Tensor, q: Optional[torch.Tensor] = None,
                         scale: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:

@@ -84,12 +84,40 @@ def gather_columns(local: torch.Tensor, group=None, out: Optional[torch.Tensor] 
     return assemble_gathered(scratch, out)
 
 
+class PeerBarrier:
+    """The library's own cross-rank barrier for the fused gather / reduce paths (`gu_peer_barrier`): a 64-word flag
+    array per rank in symmetric memory, stamped by plain peer stores and polled locally with a time limit, so a
+    rank that never arrives costs its peers the limit and an error status instead of a kernel that spins forever
+    (torch's symmetric-memory barrier has no such bound).  Collective to construct; `__call__` enqueues one barrier
+    on the current stream."""
+
+    def __init__(self, device, group=None, limit_ns: int = 0):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.device = torch.device(device)
+        self.flags = symm_mem.empty((64,), dtype=torch.int32, device=self.device)
+        self.flags.zero_()
+        self.handle = symm_mem.rendezvous(self.flags, self.group)
+        self.rank = self.handle.rank
+        self.world = self.handle.world_size
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.limit_ns = int(limit_ns)
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)  # every rank's flags are zero before anyone stamps them
+
+    def __call__(self) -> None:
+        from .kernel import peer_barrier
+
+        peer_barrier(self.ptrs, self.rank, self.device, self.limit_ns)
+
+
 class GatherBuffers:
     """One bf16 [M, N] result buffer per rank, each mapped into every rank of the group.
 
     Built on torch's symmetric memory (CUDA peer mappings over NVLink / NVSwitch).  `out` is this rank's
-    buffer; `ptrs[r]` the address of rank r's buffer in this process; `barrier()` enqueues a cross-rank
-    barrier on the current stream.  Allocate once and reuse: the rendezvous is collective and slow.
+    buffer; `ptrs[r]` the address of rank r's buffer in this process; `barrier()` enqueues the library's bounded
+    cross-rank barrier (`PeerBarrier`) on the current stream.  Allocate once and reuse: the rendezvous is collective and slow.
     """
 
     def __init__(self, m: int, n: int, device, group=None):
@@ -102,9 +130,10 @@ class GatherBuffers:
         self.world = self.handle.world_size
         self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
         self.shape = (m, n)
+        self._barrier = PeerBarrier(device, self.group)
 
     def barrier(self) -> None:
-        self.handle.barrier()
+        self._barrier()
 
 
 @torch.no_grad()
@@ -185,9 +214,10 @@ class ReduceBuffers:
         self.slot_ptrs = [int(p) for p in self.slots_handle.buffer_ptrs]
         self.out_ptrs = [int(p) for p in self.handle.buffer_ptrs]
         self.shape = (m, h)
+        self._barrier = PeerBarrier(device, self.group)
 
     def barrier(self) -> None:
-        self.handle.barrier()
+        self._barrier()
 
 
 @torch.no_grad()

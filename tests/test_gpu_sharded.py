@@ -106,6 +106,20 @@ for _ in range(2):
     mine = pkg.mlp_block_sharded_fused(xb, gw, sg, uw, su, dw, ds, rb, gather=False)
     torch.cuda.synchronize()
     assert torch.equal(mine, want[rank * rows:(rank + 1) * rows]), f"rank {rank}: reduce-scatter form differs"
+# host-memory callers: every rank holds its row block of the activations in pinned host memory, the blocks are
+# exchanged over NVLink, every rank copies its columns of all rows back to the host
+from sol_execbench_b200_kernels_b200.host_pipeline import ShardedHostPipeline
+pipe = ShardedHostPipeline(m, k, n // world, dev, chunks=2)
+lo, hi = rank * pipe.block_rows, (rank + 1) * pipe.block_rows
+x_host = inp.x[lo:hi].cpu().view(torch.uint8).pin_memory().view(torch.float8_e4m3fn)
+sx_host = inp.scale_x[lo:hi].cpu().pin_memory()
+out_host = torch.zeros(m, n // world, dtype=torch.bfloat16).pin_memory()
+clo, chi = pkg.shard_bounds(n, rank, world)
+for _ in range(2):
+    pipe.run(x_host, sx_host, gw, sg, uw, su, out_host)
+    pipe.synchronize()
+    assert torch.equal(out_host.to(dev), ref[:, clo:chi]), f"rank {rank}: sharded host pipeline differs"
+assert pipe.bytes_h2d == (m // world) * (k + 4 * (k // 128)) and pipe.bytes_d2h == 2 * m * (n // world)
 dist.barrier()
 dist.destroy_process_group()
 print(f"rank {rank} ok")

@@ -55,3 +55,35 @@ def test_wait_limit_setter_round_trip():
 
     assert _cabi.lib.gu_set_wait_limit_ns(5_000_000_000) == 0
     assert _cabi.lib.gu_set_wait_limit_ns(0) == 0
+
+
+def test_peer_barrier_gives_up_on_a_rank_that_never_arrives_and_passes_once_it_has():
+    """`gu_peer_barrier` for rank 0 of 2 with nobody stamping for rank 1: the launch must return at its time limit
+    and name the missing rank; rank 1's own barrier, launched afterwards, finds rank 0's stamp and passes at once.
+    (The two ranks' flag arrays live on this one GPU; no kernel ever waits for a kernel launched after it to finish
+    normally — the first launch is meant to run out.)"""
+    import sol_execbench_b200_kernels_b200 as pkg
+    from sol_execbench_b200_kernels_b200 import _cabi
+
+    dev = torch.device("cuda:0")
+    pkg.last_status(clear=True)
+    flags = torch.zeros(2, 64, dtype=torch.int32, device=dev)
+    ptrs = [flags[0].data_ptr(), flags[1].data_ptr()]
+    t0 = time.perf_counter()
+    pkg.peer_barrier(ptrs, 0, dev, limit_ns=3_000_000)
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 1.0
+    code, detail = pkg.last_status(clear=True)
+    assert code == _cabi.GU_ETIMEOUT and (detail >> 24) & 0xFF == 20 and (detail & 0xFF) == 1   # rank 1 is missing
+    pkg.peer_barrier(ptrs, 1, dev, limit_ns=3_000_000)
+    torch.cuda.synchronize()
+    assert pkg.last_status() == (0, 0)
+    f = flags.cpu()
+    assert f[0, 0] == 1 and f[0, 1] == 1 and f[1, 0] == 1 and f[1, 1] == 1     # both ranks stamped both arrays
+    assert f[0, 16] == 1 and f[1, 16] == 1                                     # both have passed barrier number 1
+    # a barrier of one rank needs nobody else
+    solo = torch.zeros(64, dtype=torch.int32, device=dev)
+    for expect in (1, 2, 3):
+        pkg.peer_barrier([solo.data_ptr()], 0, dev)
+        torch.cuda.synchronize()
+        assert pkg.last_status() == (0, 0) and int(solo[16]) == expect
