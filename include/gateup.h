@@ -38,6 +38,7 @@ extern "C" {
 #define GU_EDEVICE (-7)          /* not a compute-capability-10.x device               */
 #define GU_ETIMEOUT (-8)         /* a bounded device-side wait gave up (gu_last_status) */
 #define GU_ESTATIC_LIMIT (-9)    /* gu_run_decode_static: more tokens than its built-in scratch holds */
+#define GU_EBOUNDS (-10)         /* range-checked debug build only: an index or coordinate left its extent (gu_last_status) */
 
 /* plans */
 #define GU_PLAN_AUTO 0    /* shape heuristic (gu_select_plan)                                      */
@@ -204,12 +205,22 @@ int gu_quantize_activation(const void* x, int x_is_f32, int64_t ld_x, void* q, f
 
 /*
  * Device-side status of the current device: 0, or GU_ETIMEOUT with `detail`
- * = (wait id << 24 | block index) of the first wait that gave up.  Synchronises
+ * = (wait id << 24 | block index) of the first wait that gave up (or, from the
+ * range-checked debug build, GU_EBOUNDS with detail = site << 16 | block).  Synchronises
  * the device; meant for tests and debugging, never for the timed path.  The
  * reference has no counterpart (its cluster wait spins without bound,
  * variants/cute_fused_v1/blockwise_gemm_fused.py:85-91).  `clear` != 0 resets it.
  */
 int gu_last_status(int* detail, int clear);
+
+/*
+ * 1 if this library was built with -DGU_BOUNDS=1, the range-checked debug build that stands in for a memory
+ * checker: every computed TMA coordinate, global index and ring / accumulator stage index of the kernels is tested
+ * against its extent before use, a violation is recorded (gu_last_status returns GU_EBOUNDS with detail =
+ * site << 16 | block) and the access is skipped.  0 for the regular library, where the tests compile to nothing.
+ * No counterpart in the reference.
+ */
+int gu_is_range_checked_build(void);
 
 /*
  * Decode-sized variant of gu_run for callers that cannot hand the library any
@@ -227,7 +238,14 @@ int gu_last_status(int* detail, int clear);
  *     launches nothing.
  *   - The first call on each device looks up the array's device address and
  *     sets the kernel's shared-memory attribute.  Make that call with the
- *     device current, and before any stream capture begins.
+ *     device current, and before any stream capture begins.  That first call
+ *     (or, with lazy module loading, the first launch of any kernel of this
+ *     library) is also what loads the module onto the device: its code plus
+ *     the 4 MiB + 4 KiB array.  A host that claims all of HBM for an arena
+ *     of its own must therefore make this call — or load the library with
+ *     CUDA_MODULE_LOADING=EAGER and touch the device — BEFORE it claims the
+ *     arena; GU_ECUDA from the first call most likely means that the module
+ *     load found no memory left.
  *   - Every call this process makes on a device uses the same array, and the
  *     array keeps what the previous call left in it.  Nothing has to be
  *     cleared between calls (each call stamps its hand-off flags with an epoch
@@ -239,6 +257,15 @@ int gu_last_status(int* detail, int clear);
  * scratch inside every call.
  */
 int gu_run_decode_static(const gu_problem* problem, void* stream);
+
+/*
+ * Numerical notes that hold for every entry point above.  The activation is computed as g / (1 + exp(-g)) with
+ * the hardware's approximate division: for gate values between about -88.7 and -87.3 (denominator in
+ * (2^126, 2^128)) that division returns 0 where g * sigmoid(g) would be a normal number of magnitude ~1e-36 — a
+ * deviation of that size and nothing more.  gu_quantize_activation takes the block maximum with a maximum that
+ * ignores NaN: a NaN input does not poison its block's scale (torch's amax would propagate it); the NaN element
+ * itself goes through the hardware's saturating e4m3 conversion.  Inputs are expected to be finite.
+ */
 
 /* Kernel launches issued by this library in this process so far. */
 int64_t gu_launch_count(void);

@@ -20,6 +20,7 @@ GU_ECUDA = -6
 GU_EDEVICE = -7
 GU_ETIMEOUT = -8
 GU_ESTATIC_LIMIT = -9
+GU_EBOUNDS = -10
 
 PLAN_AUTO, PLAN_TILE, PLAN_STREAM, PLAN_TILE_DP, PLAN_TILE_SK, PLAN_TILE_PAIR = 0, 1, 2, 3, 4, 5
 PLAN_NAMES = {PLAN_AUTO: "auto", PLAN_TILE: "tile", PLAN_STREAM: "stream", PLAN_TILE_DP: "tile_dp",
@@ -28,7 +29,7 @@ PLAN_NAMES = {PLAN_AUTO: "auto", PLAN_TILE: "tile", PLAN_STREAM: "stream", PLAN_
 EXPORTS = (
     "gu_version", "gu_error_string", "gu_select_plan", "gu_workspace_bytes", "gu_workspace_init",
     "gu_run", "gu_run_concat", "gu_last_status", "gu_launch_count", "gu_run_decode_static", "gu_run_gather", "gu_quantize_activation", "gu_blockwise_gemm", "gu_run_fp8out",
-    "gu_blockwise_gemm_scatter", "gu_reduce_gather", "gu_set_wait_limit_ns", "gu_trace_read", "gu_wait_probe", "gu_peer_barrier",
+    "gu_blockwise_gemm_scatter", "gu_reduce_gather", "gu_set_wait_limit_ns", "gu_trace_read", "gu_wait_probe", "gu_peer_barrier", "gu_is_range_checked_build",
 )
 
 
@@ -94,6 +95,7 @@ def _load() -> ctypes.CDLL:
     lib.gu_set_wait_limit_ns.argtypes = [ctypes.c_uint64]
     lib.gu_peer_barrier.restype = c_int
     lib.gu_peer_barrier.argtypes = [POINTER(c_void_p), c_int, c_int, ctypes.c_uint64, c_void_p]
+    lib.gu_is_range_checked_build.restype = c_int
     lib.gu_wait_probe.restype = c_int
     lib.gu_wait_probe.argtypes = [c_void_p]
     lib.gu_trace_read.restype = c_int

@@ -78,6 +78,16 @@ def build_trace(force: bool = False, verbose: bool = False) -> Path:
     return TRACE_LIB_PATH
 
 
+# the range-checked debug build (-DGU_BOUNDS=1): same entry points, every computed coordinate and index tested
+BOUNDS_LIB_PATH = PKG_DIR / "libgateup_bounds.so"
+
+
+def build_bounds(force: bool = False, verbose: bool = False) -> Path:
+    if force or _stale(BOUNDS_LIB_PATH, SOURCES + HEADERS):
+        _compile(BOUNDS_LIB_PATH, SOURCES, verbose, defines=("GU_BOUNDS=1",))
+    return BOUNDS_LIB_PATH
+
+
 def build_study(name: str, defines, verbose: bool = False) -> Path:
     """Compile libgateup_<name>.so with extra -D switches (the study builds listed in csrc/gateup_pair.cuh)."""
     lib = PKG_DIR / f"libgateup_{name}.so"
@@ -86,10 +96,12 @@ def build_study(name: str, defines, verbose: bool = False) -> Path:
 
 
 if __name__ == "__main__":
-    # python -m sol_execbench_b200_kernels_b200.build [--force] [-v] [--trace] [--study NAME DEFINE[,DEFINE...]]
+    # python -m sol_execbench_b200_kernels_b200.build [--force] [-v] [--trace] [--bounds] [--study NAME DEFINE[,DEFINE...]]
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
     if "--trace" in sys.argv:
         print(build_trace(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    if "--bounds" in sys.argv:
+        print(build_bounds(force="--force" in sys.argv, verbose="-v" in sys.argv))
     if "--study" in sys.argv:
         at = sys.argv.index("--study")
         print(build_study(sys.argv[at + 1], sys.argv[at + 2].split(","), verbose="-v" in sys.argv))

@@ -295,6 +295,8 @@ int launch_tile(const gu_problem* pr, const DeviceInfo& dev, cudaStream_t stream
   p.scale_out = nullptr;
   p.blocks_per_owner = 1;
   p.slot_rows = 0;
+  p.out_rows = static_cast<int>(m);
+  p.out_cols = static_cast<int>(n);
   const int total_tiles = p.num_tiles;
   const int sms = dev.sm_count;
   // Hybrid schedule: whole rounds of tiles run data-parallel; the last round plus the remainder (between one and
@@ -319,7 +321,9 @@ int launch_tile(const gu_problem* pr, const DeviceInfo& dev, cudaStream_t stream
     int64_t grid = sms < kTileMaxGrid ? sms : kTileMaxGrid;
     const int64_t units = int64_t(p.num_tiles) * p.kb;
     if (units < grid) grid = units;
-    p.flags = static_cast<unsigned int*>(pr->workspace);
+    // words [256, 512) of the flag block: the streaming kernel stamps words [0, 256) of the same workspace with
+    // epochs of its own counter, and a stale stamp of one kernel must never look like the other's epoch
+    p.flags = static_cast<unsigned int*>(pr->workspace) + 256;
     p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(pr->workspace) + kTileFlagBytes);
     p.epoch = next_epoch();
     gateup_tile_kernel<true><<<static_cast<int>(grid), kTileThreads, kTileSmemBytes, stream>>>(tm_x, tm_g, tm_u, tm_o, p);
@@ -361,6 +365,8 @@ int launch_pair(const gu_problem* pr, const DeviceInfo& dev, cudaStream_t stream
   p.group_m = static_cast<int>(gm);
   p.out_count = 1;
   p.blocks_per_owner = 1;
+  p.out_rows = static_cast<int>(m);
+  p.out_cols = static_cast<int>(n);
 
   const int clusters = p.num_tiles < dev.pair_clusters ? p.num_tiles : dev.pair_clusters;
   gateup_pair_kernel<<<2 * clusters, kPairThreads, kPairSmemBytes, stream>>>(tm_x, tm_g, tm_u, tm_o, p);
@@ -477,6 +483,7 @@ const char* gu_error_string(int code) {
     case GU_EDEVICE: return "the current device is not compute capability 10.x";
     case GU_ETIMEOUT: return "a bounded device-side wait gave up";
     case GU_ESTATIC_LIMIT: return "gu_run_decode_static: at most 16 tokens fit the built-in scratch";
+    case GU_EBOUNDS: return "the range-checked debug build found an index or coordinate outside its extent";
     default: return "unknown error";
   }
 }
@@ -909,6 +916,8 @@ int gu_blockwise_gemm(const void* a, const float* scale_a, const void* b, const 
   p.scale_out = nullptr;
   p.blocks_per_owner = 1;
   p.slot_rows = 0;
+  p.out_rows = static_cast<int>(m);
+  p.out_cols = static_cast<int>(n);
   if (gu::tile_prefers_pairs(m, *dev)) {
     // CTA pairs: 256-token x 256-column tiles, one per two-CTA cluster
     p.num_m_blocks = static_cast<int>((m + 2 * gu::kTileM - 1) / (2 * gu::kTileM));
@@ -966,7 +975,16 @@ int gu_last_status(int* detail, int clear) {
     unsigned int zero[4] = {0, 0, 0, 0};
     if (cudaMemcpyToSymbol(gu::g_status, zero, sizeof(zero)) != cudaSuccess) return GU_ECUDA;
   }
-  return host[0] == 0 ? GU_OK : GU_ETIMEOUT;
+  if (host[0] == 0) return GU_OK;
+  return host[0] == gu::kStatusBounds ? GU_EBOUNDS : GU_ETIMEOUT;
+}
+
+int gu_is_range_checked_build(void) {
+#ifdef GU_BOUNDS
+  return 1;
+#else
+  return 0;
+#endif
 }
 
 int64_t gu_launch_count(void) { return gu::g_launches.load(std::memory_order_relaxed); }

@@ -247,7 +247,10 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tm_x, const 
           GU_TR_END(0);
           const uint32_t full = full_even + 8 * stage;
           const uint32_t dst = ring + stage * kPairStageBytes;
-          if (ok && elected) {
+          const int b_row = kSingle ? (2 * nb + static_cast<int>(rank)) * kTileN : nb * kTileN;
+          if (ok && elected && GU_IN_RANGE(stage < kPairStages, kSitePairStage) &&
+              GU_IN_RANGE(load_coords_ok(p.kb, j, row0, 2 * p.num_m_blocks * kTileM) &&
+                              load_coords_ok(p.kb, j, b_row, (kSingle ? 2 : 1) * p.num_n_blocks * kTileN), kSitePairLoad)) {
             mbar_arrive_expect_tx_cluster(full, kPairStageBytes);
             tma_load_2d_pair(dst, &tm_x, full, j * kBlockK, row0);  // rows past M read as zero
             if constexpr (kSingle) {
@@ -346,7 +349,9 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tm_x, const 
         if constexpr (kSingle) {
           // both handed-over tiles are final (and fenced by their writers): four half-tile stores, nothing to compute
           if (et == 0) {
-            if (ok && !ctx.aborted && row0 < p.m) {
+            if (ok && !ctx.aborted && row0 < p.m &&
+                GU_IN_RANGE(p.out_cols == 0 || (2 * nb * kTileN + 128 <= p.out_cols && row0 >= 0 && row0 < p.out_rows),
+                            kSitePairStore)) {
               tma_store_2d(&tm_out, hand, 2 * nb * kTileN, row0);
               tma_store_2d(&tm_out, hand + kTileOutHalfBytes, 2 * nb * kTileN + 64, row0);
               if (2 * nb + 1 < p.n_blocks128) {
@@ -378,7 +383,9 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tm_x, const 
         fence_proxy_async_smem();
         named_bar_sync(1, kPairEpiThreads);
         if (et == 0) {
-          if (ok && !ctx.aborted && row0 < p.m) {
+          if (ok && !ctx.aborted && row0 < p.m &&
+              GU_IN_RANGE(p.out_cols == 0 || (nb * kTileN + 128 <= p.out_cols && row0 >= 0 && row0 < p.out_rows),
+                          kSitePairStore)) {
             tma_store_2d(&tm_out, hand, nb * kTileN, row0);
             tma_store_2d(&tm_out, hand + kTileOutHalfBytes, nb * kTileN + 64, row0);
             tma_store_commit();
@@ -417,6 +424,9 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tm_x, const 
       sx_off = static_cast<uint32_t>(m_global) * static_cast<uint32_t>(p.kb);
       const int wblock = kSingle ? min(2 * nb + static_cast<int>(proj), p.n_blocks128 - 1) : nb;
       sw_off = static_cast<uint32_t>(wblock) * static_cast<uint32_t>(p.kb);
+      if (!GU_IN_RANGE(m_global >= 0 && m_global < p.m && wblock >= 0 &&
+                           wblock < (kSingle ? p.n_blocks128 : p.num_n_blocks), kSitePairScale))
+        return;
       sx0 = __ldg(p.scale_x + sx_off);
       sw0 = __ldg(scale_w + sw_off);
     };

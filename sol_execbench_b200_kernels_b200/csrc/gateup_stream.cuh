@@ -139,7 +139,9 @@ gateup_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_cons
       int nbk = static_cast<int>(u_begin / p.kb);
       int j = static_cast<int>(u_begin - static_cast<long long>(nbk) * p.kb);
       for (long long u = u_begin; u < u_end; ++u) {
-        const bool ok = mbar_wait(ctx, bar_empty + 8 * stage, phase ^ 1u, kWaitStreamEmpty);
+        bool ok = mbar_wait(ctx, bar_empty + 8 * stage, phase ^ 1u, kWaitStreamEmpty);
+        ok = ok && GU_IN_RANGE(stage >= 0 && stage < p.stages && p.stages <= kStreamMaxStages, kSiteStreamStage) &&
+             GU_IN_RANGE(load_coords_ok(p.kb, j, nbk * 128, p.nb * 128), kSiteStreamLoad);
         if (ok) {
           const uint32_t full = bar_full + 8 * stage;
           const uint32_t dst = ring + stage * Cfg::kStageBytes;
@@ -208,8 +210,11 @@ gateup_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_cons
     int nbk = static_cast<int>(u_begin / p.kb);
     int j = static_cast<int>(u_begin - static_cast<long long>(nbk) * p.kb);
     int seg_first_j = j;
-    float sg_next = __ldg(p.scale_gate + u_begin);  // scale grids are [nb][kb]: unit index == flat index
-    float su_next = __ldg(p.scale_up + u_begin);
+    float sg_next = 0.f, su_next = 0.f;
+    if (GU_IN_RANGE(u_begin >= 0 && u_begin < units && u_end <= units, kSiteStreamScale)) {
+      sg_next = __ldg(p.scale_gate + u_begin);  // scale grids are [nb][kb]: unit index == flat index
+      su_next = __ldg(p.scale_up + u_begin);
+    }
 
     for (long long u = u_begin; u < u_end; ++u) {
       const float sgw = sg_next, suw = su_next;
@@ -267,6 +272,7 @@ gateup_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_cons
         if (seg_first_j != 0) {
           // started mid-block: publish the partial sums for the block's owner
           float* slot = p.partials + static_cast<size_t>(my_range) * (2 * MPAD * 128);
+          if (GU_IN_RANGE(my_range >= 0 && my_range < kStreamMaxGrid && row >= 0 && row < 128, kSiteStreamHandOff))
 #pragma unroll
           for (int t = 0; t < MPAD; ++t) {
             __stcg(slot + t * 128 + row, g[t]);
@@ -308,6 +314,7 @@ gateup_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_cons
           }
           // SwiGLU and store: consecutive lanes hold consecutive output columns
           __nv_bfloat16* out_col = p.out + static_cast<size_t>(nbk) * 128 + row;
+          if (GU_IN_RANGE(nbk >= 0 && nbk < p.nb && static_cast<long long>(nbk) * 128 + row < p.ld_out, kSiteStreamStore))
 #pragma unroll
           for (int t = 0; t < MPAD; ++t) {
             if (t < p.m) out_col[static_cast<size_t>(t) * p.ld_out] = __float2bfloat16_rn(swiglu_bf16(g[t], up[t]));

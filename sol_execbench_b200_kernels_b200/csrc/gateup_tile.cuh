@@ -98,7 +98,21 @@ struct TileParams {
   unsigned int* flags;      // [gridDim.x] epoch of the last call that filled slot i
   float* partials;          // [gridDim.x][32][256] float4: values 4i..4i+3 of consumer thread t at [i * 256 + t]
   unsigned int epoch;       // this call's stamp, never 0
+  // extents of the destination for the range-checked debug build (0: not checked)
+  int out_rows = 0, out_cols = 0;
 };
+
+// sites of the range-checked debug build (see GU_IN_RANGE)
+enum : unsigned {
+  kSiteTileLoad = 1, kSiteTileScale = 2, kSiteTileStage = 3, kSiteTileStore = 4, kSiteTileHandOff = 5, kSiteTileScaleOut = 6,
+  kSitePairLoad = 17, kSitePairScale = 18, kSitePairStage = 19, kSitePairStore = 20,
+  kSiteStreamLoad = 33, kSiteStreamScale = 34, kSiteStreamStage = 35, kSiteStreamStore = 36, kSiteStreamHandOff = 37,
+};
+
+// TMA load coordinates of a K block: x = K offset (16-byte aligned, inside K), rows inside the padded row range
+__device__ __forceinline__ bool load_coords_ok(int kb, int j, int row, int row_limit) {
+  return j >= 0 && j < kb && ((j * kBlockK) & 15) == 0 && row >= 0 && row < row_limit && (row & 127) == 0;
+}
 
 constexpr uint32_t kTileFlagBytes = 4096;                       // hand-off flags at the start of the workspace
 constexpr int kTileMaxGrid = 256;                               // workspace is sized for at most this many ranges
@@ -225,7 +239,10 @@ __device__ __forceinline__ void tile_kernel_body(const CUtensorMap& tm_x, const 
         int mb, nb;
         tile_coords(p, kStreamK ? tile + p.tile_begin : tile, mb, nb);
         for (int j = jb; j < je; ++j) {
-          const bool ok = mbar_wait(ctx, bar_empty + 8 * stage, phase ^ 1u, kWaitTileEmpty);
+          bool ok = mbar_wait(ctx, bar_empty + 8 * stage, phase ^ 1u, kWaitTileEmpty);
+          ok = ok && GU_IN_RANGE(stage >= 0 && stage < kTileStages, kSiteTileStage) &&
+               GU_IN_RANGE(load_coords_ok(p.kb, j, mb * kTileM, p.num_m_blocks * kTileM) &&
+                               load_coords_ok(p.kb, j, nb * kTileN, p.num_n_blocks * kTileN), kSiteTileLoad);
           if (ok) {
             const uint32_t full = bar_full + 8 * stage;
             const uint32_t dst = ring + stage * kTileStageBytes;
@@ -304,6 +321,10 @@ __device__ __forceinline__ void tile_kernel_body(const CUtensorMap& tm_x, const 
           sg_row = p.scale_gate + static_cast<size_t>(nb) * p.kb;
           su_row = p.scale_up + static_cast<size_t>(nb) * p.kb;
         }
+        const int w_blocks = kSingle ? p.n_blocks128 : p.num_n_blocks;
+        if (!GU_IN_RANGE(m_global >= 0 && m_global < p.m && (sg_row - p.scale_gate) / p.kb < w_blocks &&
+                             (su_row - (kSingle ? p.scale_gate : p.scale_up)) / p.kb < w_blocks, kSiteTileScale))
+          return;
         sx0 = __ldg(sx_row); sg0 = __ldg(sg_row); su0 = __ldg(su_row);
         if (p.kb > 1) { sx1 = __ldg(sx_row + 1); sg1 = __ldg(sg_row + 1); su1 = __ldg(su_row + 1); }
       };
@@ -398,7 +419,7 @@ __device__ __forceinline__ void tile_kernel_body(const CUtensorMap& tm_x, const 
             const int chunk = half * 4 + c;
             *reinterpret_cast<uint4*>(out_row + ((chunk ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
           }
-          if (half == 0 && cur_mb * kTileM + row < p.m)
+          if (half == 0 && cur_mb * kTileM + row < p.m && GU_IN_RANGE(cur_nb >= 0 && cur_nb < p.n_blocks128, kSiteTileScaleOut))
             p.scale_out[static_cast<size_t>(cur_mb * kTileM + row) * p.n_blocks128 + cur_nb] = sc;
           fence_proxy_async_smem();
           named_bar_sync(3, 256);
@@ -468,7 +489,9 @@ __device__ __forceinline__ void tile_kernel_body(const CUtensorMap& tm_x, const 
                 const int hop = 1 + (i + static_cast<int>(blockIdx.x) + cur_mb) % peers;
                 tma_store_2d(&outs[(p.out_rank + hop) % p.out_count], out_half, col, cur_mb * kTileM);
               }
-            } else {
+            } else if (GU_IN_RANGE(p.out_cols == 0 || (cur_nb * kTileN + half * 64 + 64 <= p.out_cols &&
+                                                       cur_mb * kTileM >= 0 && cur_mb * kTileM < p.out_rows),
+                                   kSiteTileStore)) {
               tma_store_2d(&outs[0], out_half, cur_nb * kTileN + half * 64, cur_mb * kTileM);
             }
             tma_store_commit();
@@ -538,6 +561,7 @@ __device__ __forceinline__ void tile_kernel_body(const CUtensorMap& tm_x, const 
         if (jb != 0) {
           // started inside the tile: publish the running sums for the range that owns the tile's first K block
           float4* slot = reinterpret_cast<float4*>(p.partials + static_cast<size_t>(my_range) * kTilePartialFloats) + ctid;
+          if (GU_IN_RANGE(my_range >= 0 && my_range < kTileMaxGrid && ctid >= 0 && ctid < 256, kSiteTileHandOff))
 #pragma unroll
           for (int i = 0; i < 16; ++i) {  // 16-byte stores, consecutive threads 16 bytes apart
             __stcg(slot + i * 256, make_float4(g[2 * i].x, g[2 * i].y, g[2 * i + 1].x, g[2 * i + 1].y));

@@ -74,6 +74,24 @@ struct WaitCtx {
 };
 
 // ---------------------------------------------------------------------------
+// Range-checked debug build (-DGU_BOUNDS=1; never the shipped library): every
+// computed TMA coordinate, global index and ring / accumulator stage index is
+// tested against its extent before it is used; the first violation is recorded
+// in the status word (code kStatusBounds, detail = site << 16 | block) and the
+// access is skipped.  In the regular build the tests compile to nothing.
+// ---------------------------------------------------------------------------
+constexpr unsigned kStatusBounds = 0x42;
+#ifdef GU_BOUNDS
+__device__ __forceinline__ bool bounds_ok(bool cond, unsigned site) {
+  if (!cond && atomicCAS(&g_status[0], 0u, kStatusBounds) == 0u) g_status[1] = (site << 16) | (blockIdx.x & 0xffffu);
+  return cond;
+}
+#define GU_IN_RANGE(cond, site) ::gu::bounds_ok((cond), (site))
+#else
+#define GU_IN_RANGE(cond, site) true
+#endif
+
+// ---------------------------------------------------------------------------
 // mbarrier
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {

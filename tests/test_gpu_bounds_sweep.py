@@ -1,0 +1,76 @@
+"""Exhaustive small-shape sweep under the range-checked debug build of the library.
+
+`compute-sanitizer` is not available on the machines these tests run on, so the library carries its own checker:
+built with -DGU_BOUNDS=1 (libgateup_bounds.so) every kernel tests each computed TMA coordinate, global index and
+ring / accumulator stage index against its extent before using it, records the first violation in the status word
+(`gu_last_status` -> GU_EBOUNDS) and skips the access.  This test runs every token count M = 1 ... 129 at
+K, N in {128, 256} through every plan that takes the shape — the lone-CTA tile kernel, the CTA-pair kernel (forced
+also where the second CTA of a pair has no rows), its stream-K schedule and the weight-streaming kernel — inside
+that build, with canary rows and columns around the destination, against the CPU oracle.  A process binds one build
+of the library, so the sweep runs in a child process.
+"""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+_SWEEP = r"""
+import os, sys
+sys.path.insert(0, os.environ["GU_ROOT"])
+import sol_execbench_b200_kernels_b200.build as B
+B.LIB_PATH = B.BOUNDS_LIB_PATH
+import torch
+import sol_execbench_b200_kernels_b200 as pkg
+from sol_execbench_b200_kernels_b200 import _cabi, workloads as W
+from oracle import gateup_oracle as O
+
+assert _cabi.lib.gu_is_range_checked_build() == 1
+dev = torch.device("cuda:0")
+pkg.last_status(clear=True)
+launches = 0
+for k in (128, 256):
+    for n in (128, 256):
+        wide = torch.empty(129 + 2, n + 256, dtype=torch.bfloat16, device=dev)
+        for m in range(1, 130):
+            inp = W.make_inputs(m, k, n, seed=1000 * k + 10 * n + m)
+            ref = O.gateup_blockwise(*inp.args())
+            g = inp.to(dev)
+            plans = ["tile_dp", "tile_pair", "tile_sk"] + (["stream"] if m <= 64 else [])
+            for plan in plans:
+                wide.fill_(7.0)
+                view = wide[1:m + 1, 128:128 + n]
+                pkg.run_with_plan(*g.args(), view, plan)
+                launches += 1
+                torch.cuda.synchronize()
+                code, detail = pkg.last_status()
+                assert code == 0, f"M={m} K={k} N={n} {plan}: device status {code}, detail {detail:#x}"
+                got = view.float().cpu()
+                st = O.error_stats(got, ref)
+                # (a stream-K hand-off adds partial sums in another association: single roundings may differ)
+                assert st["finite"] and st["rel_l2"] <= 1e-3 and st["max_abs"] <= 2e-2, (m, k, n, plan, st)
+                mask = torch.ones_like(wide, dtype=torch.bool)
+                mask[1:m + 1, 128:128 + n] = False
+                assert bool((wide[mask] == 7.0).all()), f"M={m} K={k} N={n} {plan}: wrote outside the destination"
+print(f"swept {launches} launches under the range-checked build: status 0 throughout")
+"""
+
+
+def test_every_small_shape_through_every_plan_under_the_range_checked_build():
+    lib = os.path.join(ROOT, "sol_execbench_b200_kernels_b200", "libgateup_bounds.so")
+    assert os.path.exists(lib), "libgateup_bounds.so is missing: python -m sol_execbench_b200_kernels_b200.build --bounds"
+    proc = subprocess.run([sys.executable, "-c", _SWEEP], env=dict(os.environ, GU_ROOT=ROOT), capture_output=True,
+                          text=True, timeout=1500)
+    assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-4000:]
+    assert "status 0 throughout" in proc.stdout
+
+
+def test_the_regular_library_is_not_the_range_checked_build():
+    from sol_execbench_b200_kernels_b200 import _cabi
+
+    assert _cabi.lib.gu_is_range_checked_build() == 0
