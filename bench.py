@@ -819,9 +819,9 @@ def run_mlp(args):
 
 
 def run_side(args):
-    """The two HBM-bound side operators (per-head RMSNorm of query / key; Mamba conv1d tail) on one GPU:
-    CUDA-event time per launch with L2 flushed, achieved algorithmic GB/s against the measured copy bandwidth.
-    A study line, not the headline metric."""
+    """The side operators on one GPU, CUDA-event time per launch with L2 flushed: the two HBM-bound ones (per-head
+    RMSNorm of query / key; Mamba conv1d tail) as achieved algorithmic GB/s against the measured copy bandwidth, the
+    Mamba input projection as TFLOP/s against the measured bf16 GEMM rate.  A study line, not the headline metric."""
     from sol_execbench_b200_kernels_b200 import side_ops
     from sol_execbench_b200_kernels_b200 import workloads as W
 
@@ -846,12 +846,42 @@ def run_side(args):
         total, _ = time_device_steps(lambda: side_ops.mamba_conv1d_tail(p, mask, cw, cb, out), args.steps, args.warmup, flush)
         nbytes = 2 * b * l * c * 2          # the convolved half read once, the result written once, bf16
         rows[name] = (total / args.steps, nbytes)
+    # the Mamba input projection (tensor-bound): this library's tcgen05 kernel and, as the library baseline on the same
+    # inputs, torch's linear (cuBLAS); K = 8192, N = 32768 as the reference fixes them
+    proj = {}
+    for name, (b, l, c, w) in W.MAMBA_TAIL_SHAPES.items():
+        if args.workload and args.workload != name:
+            continue
+        m, kdim = b * l, 8192
+        g = torch.Generator().manual_seed(0)
+        hidden = (torch.randn(m, kdim, generator=g) * 0.5).to(torch.bfloat16).to(dev)
+        weight = (torch.randn(w, 512, generator=g) * 0.02).to(torch.bfloat16).to(dev).repeat(1, kdim // 512)
+        bias = (torch.randn(w, generator=g) * 0.1).to(torch.bfloat16).to(dev)
+        out = torch.empty(m, w, dtype=torch.bfloat16, device=dev)
+        total, _ = time_device_steps(lambda: side_ops.mamba_in_proj(hidden, weight, bias, out), args.steps, args.warmup, flush)
+        lib_total, _ = time_device_steps(lambda: torch.nn.functional.linear(hidden, weight, bias), args.steps, args.warmup, flush)
+        want = torch.nn.functional.linear(hidden, weight, bias)
+        rel = float(torch.linalg.vector_norm(out.float() - want.float()) / torch.linalg.vector_norm(want.float()))
+        flops = 2.0 * m * kdim * w
+        proj[name + "_in_proj"] = {
+            "m": m, "k": kdim, "n": w, "us": round(total / args.steps * 1e3, 2),
+            "tflops": round(flops / (total / args.steps) / 1e9, 1),
+            "frac": round(flops / (total / args.steps) / 1e9 / peaks["bf16_tflops"], 4),
+            "torch_linear_us": round(lib_total / args.steps * 1e3, 2),
+            "torch_linear_tflops": round(flops / (lib_total / args.steps) / 1e9, 1),
+            "rel_l2_vs_torch_linear": rel}
+        del hidden, weight, bias, out, want
+    code, detail = side_ops.last_status()
+    if code != 0:
+        raise SystemExit(f"bench.py: side-ops device status {code} detail {detail:#x}")
     src = "of measured" if peaks["_source"] == "measured" else "of fallback"
     print(json.dumps({
         "study": "side operators", "steps": args.steps, "warmup": args.warmup, "peak_gbs": peaks["hbm_gbs"],
         "peak_source": f"hbm_gbs, {src}", "gpu_launches": side_ops.launch_count(),
         "rows": {k: {"us": round(ms * 1e3, 2), "algorithmic_bytes": nb, "gbs": round(nb / ms / 1e6, 1),
-                     "frac": round(nb / ms / 1e6 / peaks["hbm_gbs"], 4)} for k, (ms, nb) in rows.items()}}), flush=True)
+                     "frac": round(nb / ms / 1e6 / peaks["hbm_gbs"], 4)} for k, (ms, nb) in rows.items()},
+        "projection": {"peak_tflops": peaks["bf16_tflops"], "peak_source": f"bf16_tflops burst, {src}", "rows": proj}}),
+        flush=True)
 
 
 def run_graph(args):

@@ -21,6 +21,8 @@ extern "C" {
 #define SO_EINVAL_SHAPE -2 /* a size is outside the contract */
 #define SO_EINVAL_ALIGN -3 /* a pointer is not 16-byte aligned */
 #define SO_ECUDA -4        /* the launch failed */
+#define SO_EDEVICE -5      /* the current device is not a compute capability 10.x GPU */
+#define SO_ETIMEOUT -6     /* so_last_status: a bounded device-side wait of an earlier launch ran out */
 
 int so_version(void);
 const char* so_error_string(int code);
@@ -54,6 +56,27 @@ int so_rmsnorm_qk(const float* query, const float* key, const float* weight_q, c
 int so_mamba_conv1d_tail(const void* projected, const void* attention_mask, const void* conv_weight,
                          const void* conv_bias, void* output, int64_t batch, int64_t sequence, int64_t channels,
                          int64_t projected_width, void* stream);
+
+/*
+ * Input projection of the Mamba mixer: projected[m, n] = bf16(hidden[m, k] . weight[n, k]^T + bias[n]); all tensors
+ * bf16 row-major and contiguous, fp32 accumulation, the bias added in fp32 before the one rounding.  One launch of
+ * a persistent tcgen05 (kind::f16) kernel: CTA pairs on 256 x 256 tiles for m > 128, lone CTAs on 128 x 256 tiles
+ * otherwise.  Replaces `launch_sm100_cutlass_projection` of kernels/029_mamba_conv1d_with_gating/kernel.cu:274-312
+ * (a CUTLASS builder GEMM with a row-broadcast bias, kernel.cu:36-160), which fixes k = 8192 and n = 32768 and needs
+ * m to be B x L of a [B, L, 8192] tensor; here m >= 0 and k, n are any multiples of 8 (rows are 16-byte aligned).
+ * Every device-side wait of the kernel is bounded; so_last_status reports one that ran out.
+ */
+int so_mamba_in_proj(const void* hidden, const void* weight, const void* bias, void* projected, int64_t m, int64_t k,
+                     int64_t n, void* stream);
+
+/*
+ * Synchronises the device and returns SO_OK, or SO_ETIMEOUT if a bounded wait inside so_mamba_in_proj ran out since
+ * the status was last cleared (`detail`: wait id << 24 | block); `clear` != 0 resets it.
+ */
+int so_last_status(int* detail, int clear);
+
+/* Time limit of the device-side waits in nanoseconds (0 restores the default of 2 s).  Synchronises the device. */
+int so_set_wait_limit_ns(uint64_t ns);
 
 /* Number of kernel launches issued by this library in this process. */
 int64_t so_launch_count(void);

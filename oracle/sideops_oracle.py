@@ -1,4 +1,4 @@
-"""CPU restatement of the two side operators.  TEST INFRASTRUCTURE ONLY: imported by tests/, the smoke check and
+"""CPU restatement of the side operators.  TEST INFRASTRUCTURE ONLY: imported by tests/, the smoke check and
 bench.py's CPU-baseline leg; never by the package.
 
 * `rmsnorm_qk`: kernels/038_flux_multi_head_rmsnorm_qk/kernel.cu:143-196 — per (token, head) row of 128 fp32:
@@ -8,6 +8,9 @@ bench.py's CPU-baseline leg; never by the package.
   multiply, after the convolution (fp32 accumulation in tap order, then bias), after the sigmoid and after the
   product; an output is kept where the mask is at least one half.  The products of two bf16 values are exact in
   fp32, so the fp32 accumulation below is bit-identical to a fused-multiply-add chain.
+* `mamba_in_proj`: kernels/029_mamba_conv1d_with_gating/kernel.cu:36-64, 274-312 — a bf16 GEMM with fp32
+  accumulation whose epilogue adds the bf16 bias in fp32 and rounds once to bf16.  Floating point: the order of the
+  K sum differs between implementations, so parity is a tolerance of one bf16 rounding step (stated in the tests).
 
 Pinned against outputs of the reference's own CUDA kernels run on a B200 (fixtures under tests/golden/, made by
 tests/golden/make_sideops_golden.py).
@@ -24,6 +27,15 @@ def rmsnorm_qk(query: torch.Tensor, key: torch.Tensor, weight_q: torch.Tensor, w
         return (x * scale) * w.float()
 
     return one(query, weight_q), one(key, weight_k)
+
+
+def mamba_in_proj(hidden_states: torch.Tensor, in_proj_weight: torch.Tensor, in_proj_bias: torch.Tensor,
+                  exact: bool = False) -> torch.Tensor:
+    """bf16 [..., K], [N, K], [N] -> bf16 [..., N]; with `exact` the unrounded float64 result instead."""
+    if exact:
+        return hidden_states.double() @ in_proj_weight.double().t() + in_proj_bias.double()
+    acc = hidden_states.float() @ in_proj_weight.float().t()
+    return (acc + in_proj_bias.float()).to(torch.bfloat16)
 
 
 def mamba_conv1d_tail(projected: torch.Tensor, attention_mask: torch.Tensor, conv1d_weight: torch.Tensor,

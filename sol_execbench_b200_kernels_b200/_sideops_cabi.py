@@ -3,14 +3,15 @@ the built library raises."""
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_char_p, c_float, c_int, c_int64, c_void_p
+from ctypes import POINTER, c_char_p, c_float, c_int, c_int64, c_uint64, c_void_p
 from pathlib import Path
 
 LIB_PATH = Path(__file__).resolve().parent / "libsideops.so"
 
-SO_OK, SO_EINVAL_NULL, SO_EINVAL_SHAPE, SO_EINVAL_ALIGN, SO_ECUDA = 0, -1, -2, -3, -4
+SO_OK, SO_EINVAL_NULL, SO_EINVAL_SHAPE, SO_EINVAL_ALIGN, SO_ECUDA, SO_EDEVICE, SO_ETIMEOUT = 0, -1, -2, -3, -4, -5, -6
 
-EXPORTS = ("so_version", "so_error_string", "so_rmsnorm_qk", "so_mamba_conv1d_tail", "so_launch_count")
+EXPORTS = ("so_version", "so_error_string", "so_rmsnorm_qk", "so_mamba_conv1d_tail", "so_mamba_in_proj", "so_last_status",
+           "so_set_wait_limit_ns", "so_launch_count")
 
 
 class SideOpsError(RuntimeError):
@@ -34,6 +35,12 @@ def _load() -> ctypes.CDLL:
     lib.so_mamba_conv1d_tail.restype = c_int
     lib.so_mamba_conv1d_tail.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                          c_int64, c_void_p]
+    lib.so_mamba_in_proj.restype = c_int
+    lib.so_mamba_in_proj.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p]
+    lib.so_last_status.restype = c_int
+    lib.so_last_status.argtypes = [POINTER(c_int), c_int]
+    lib.so_set_wait_limit_ns.restype = c_int
+    lib.so_set_wait_limit_ns.argtypes = [c_uint64]
     lib.so_launch_count.restype = c_int64
     return lib
 

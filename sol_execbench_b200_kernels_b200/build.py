@@ -22,7 +22,7 @@ TRACE_LIB_PATH = PKG_DIR / "libgateup_trace.so"
 
 SIDE_LIB_PATH = PKG_DIR / "libsideops.so"
 SIDE_SOURCES = [CSRC / "sideops.cu"]
-SIDE_HEADERS = [PKG_DIR.parent / "include" / "sideops.h"]
+SIDE_HEADERS = [PKG_DIR.parent / "include" / "sideops.h", CSRC / "proj_gemm.cuh", CSRC / "ptx_sm100.cuh"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -1,6 +1,7 @@
-// libsideops.so: the two HBM-bound operators that sit beside the FP8 gate/up path in the reference
-// repository — per-head RMSNorm of the Flux query / key tensors (problem 038) and the depthwise
-// convolution + SiLU tail of the Mamba mixer (problem 029).  sm_100a only; the C ABI is include/sideops.h.
+// libsideops.so: the operators that sit beside the FP8 gate/up path in the reference repository — per-head
+// RMSNorm of the Flux query / key tensors (problem 038) and both halves of the Mamba mixer's front end (problem 029):
+// the bf16 input projection with bias (a tcgen05 GEMM, proj_gemm.cuh) and the depthwise convolution + SiLU tail.
+// sm_100a only; the C ABI is include/sideops.h.
 #include "../../include/sideops.h"
 
 #include <cuda_bf16.h>
@@ -8,6 +9,10 @@
 #include <stdint.h>
 
 #include <atomic>
+#include <cstring>
+#include <mutex>
+
+#include "proj_gemm.cuh"
 
 namespace so {
 
@@ -355,6 +360,125 @@ mamba_conv1d_tail_kernel(const __nv_bfloat16* __restrict__ projected, const __nv
   }
 }
 
+// ------------------------------------------------------------------------------------------------------------
+// Host side of the input projection: tensor maps, per-device set-up, launch.
+// ------------------------------------------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// resolved through the runtime, so the library has no link-time dependency on the driver library
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// bf16 row-major [rows, cols], box [box_rows, 64 columns = 128 bytes], 128-byte swizzle; out-of-range reads are zero
+int bf16_map(CUtensorMap* out, const void* ptr, uint64_t cols, uint64_t rows, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return SO_ECUDA;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * 2};
+  cuuint32_t box[2] = {64, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? SO_OK : SO_ECUDA;
+}
+
+struct ProjDevice {
+  bool ready = false;
+  int sm_count = 0;
+  int pair_clusters = 0;  // two-CTA clusters of the pair kernel that are resident at once
+};
+std::mutex g_proj_mutex;
+ProjDevice g_proj_dev[64];
+
+int proj_device(ProjDevice** out) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return SO_ECUDA;
+  std::lock_guard<std::mutex> lock(g_proj_mutex);
+  ProjDevice& d = g_proj_dev[dev];
+  if (!d.ready) {
+    int major = 0;
+    if (cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess)
+      return SO_ECUDA;
+    if (major != 10) return SO_EDEVICE;
+    if (cudaFuncSetAttribute(proj_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             PjCfg<true>::smem_bytes) != cudaSuccess ||
+        cudaFuncSetAttribute(proj_gemm_lone_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             PjCfg<false>::smem_bytes) != cudaSuccess) {
+      cudaGetLastError();
+      return SO_ECUDA;
+    }
+    cudaLaunchConfig_t cfg;
+    std::memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(2 * static_cast<unsigned>(d.sm_count), 1, 1);
+    cfg.blockDim = dim3(kPjThreads, 1, 1);
+    cfg.dynamicSmemBytes = PjCfg<true>::smem_bytes;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, proj_gemm_pair_kernel, &cfg) != cudaSuccess) {
+      cudaGetLastError();
+      clusters = 0;
+    }
+    d.pair_clusters = clusters;
+    d.ready = true;
+  }
+  *out = &d;
+  return SO_OK;
+}
+
+int launch_projection(const void* hidden, const void* weight, const void* bias, void* projected, int64_t m, int64_t k,
+                      int64_t n, cudaStream_t stream) {
+  ProjDevice* dev = nullptr;
+  int rc = proj_device(&dev);
+  if (rc != SO_OK) return rc;
+  const bool pair = m > kPjTileM && dev->pair_clusters >= 1;
+  CUtensorMap tm_a, tm_w, tm_o;
+  if ((rc = bf16_map(&tm_a, hidden, k, m, kPjTileM)) != SO_OK) return rc;
+  if ((rc = bf16_map(&tm_w, weight, k, n, pair ? PjCfg<true>::b_rows : PjCfg<false>::b_rows)) != SO_OK) return rc;
+  if ((rc = bf16_map(&tm_o, projected, n, m, kPjTileM)) != SO_OK) return rc;
+  ProjParams p;
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.m = static_cast<int>(m);
+  p.n = static_cast<int>(n);
+  p.kb = static_cast<int>((k + kPjBlockK - 1) / kPjBlockK);
+  const int rows_per_tile = pair ? PjCfg<true>::rows_per_tile : PjCfg<false>::rows_per_tile;
+  p.m_tiles = static_cast<int>((m + rows_per_tile - 1) / rows_per_tile);
+  p.n_tiles = static_cast<int>((n + kPjTileN - 1) / kPjTileN);
+  const int64_t tiles = int64_t(p.m_tiles) * p.n_tiles;
+  if (tiles * p.kb >= (1ll << 31)) return SO_EINVAL_SHAPE;
+  p.num_tiles = static_cast<int>(tiles);
+  // Raster: the tiles that run at the same time form a block of about 8 row tiles x (resident tiles / 8) column
+  // tiles and walk K together, so a K block of `hidden` or `weight` is fetched from HBM once per block, not per tile.
+  p.group_m = p.m_tiles < 8 ? p.m_tiles : 8;
+  if (pair) {
+    const int clusters = p.num_tiles < dev->pair_clusters ? p.num_tiles : dev->pair_clusters;
+    proj_gemm_pair_kernel<<<2 * clusters, kPjThreads, PjCfg<true>::smem_bytes, stream>>>(tm_a, tm_w, tm_o, p);
+  } else {
+    const int ctas = p.num_tiles < dev->sm_count ? p.num_tiles : dev->sm_count;
+    proj_gemm_lone_kernel<<<ctas, kPjThreads, PjCfg<false>::smem_bytes, stream>>>(tm_a, tm_w, tm_o, p);
+  }
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError() == cudaSuccess ? SO_OK : SO_ECUDA;
+}
+
 }  // namespace so
 
 extern "C" {
@@ -368,6 +492,8 @@ const char* so_error_string(int code) {
     case SO_EINVAL_SHAPE: return "a size is outside the contract";
     case SO_EINVAL_ALIGN: return "a pointer is not 16-byte aligned";
     case SO_ECUDA: return "the CUDA launch failed";
+    case SO_EDEVICE: return "the current device is not a compute capability 10.x GPU";
+    case SO_ETIMEOUT: return "a device-side wait of an earlier launch ran out; its output is not valid";
     default: return "unknown error code";
   }
 }
@@ -416,6 +542,35 @@ int so_mamba_conv1d_tail(const void* projected, const void* attention_mask, cons
       static_cast<__nv_bfloat16*>(output), static_cast<int>(sequence), static_cast<int>(channels), projected_width);
   so::g_launches.fetch_add(1, std::memory_order_relaxed);
   return cudaGetLastError() == cudaSuccess ? SO_OK : SO_ECUDA;
+}
+
+int so_mamba_in_proj(const void* hidden, const void* weight, const void* bias, void* projected, int64_t m, int64_t k,
+                     int64_t n, void* stream) {
+  if (!hidden || !weight || !bias || !projected) return SO_EINVAL_NULL;
+  if (m < 0 || k < 8 || n < 8 || k % 8 != 0 || n % 8 != 0 || m >= (1ll << 31) || k >= (1ll << 31) || n >= (1ll << 31))
+    return SO_EINVAL_SHAPE;
+  if (!so::aligned16(hidden) || !so::aligned16(weight) || !so::aligned16(bias) || !so::aligned16(projected))
+    return SO_EINVAL_ALIGN;
+  if (m == 0) return SO_OK;
+  return so::launch_projection(hidden, weight, bias, projected, m, k, n, static_cast<cudaStream_t>(stream));
+}
+
+int so_last_status(int* detail, int clear) {
+  unsigned int host[4] = {0, 0, 0, 0};
+  if (cudaDeviceSynchronize() != cudaSuccess) return SO_ECUDA;
+  if (cudaMemcpyFromSymbol(host, gu::g_status, sizeof(host)) != cudaSuccess) return SO_ECUDA;
+  if (detail) *detail = static_cast<int>(host[1]);
+  if (clear && host[0] != 0) {
+    const unsigned int zero[4] = {0, 0, 0, 0};
+    if (cudaMemcpyToSymbol(gu::g_status, zero, sizeof(zero)) != cudaSuccess) return SO_ECUDA;
+  }
+  return host[0] == 0 ? SO_OK : SO_ETIMEOUT;
+}
+
+int so_set_wait_limit_ns(uint64_t ns) {
+  const unsigned long long v = ns ? ns : 2000000000ull;
+  if (cudaDeviceSynchronize() != cudaSuccess) return SO_ECUDA;
+  return cudaMemcpyToSymbol(gu::g_wait_limit_ns, &v, sizeof(v)) == cudaSuccess ? SO_OK : SO_ECUDA;
 }
 
 }  // extern "C"

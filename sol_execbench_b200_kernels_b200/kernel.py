@@ -112,9 +112,10 @@ def _workspace(device: torch.device, stream_ptr: int, nbytes: int) -> Optional[t
     key = (device.index if device.index is not None else torch.cuda.current_device(), stream_ptr)
     ws = _WORKSPACES.get(key)
     if ws is None or ws.numel() < nbytes:
-        if torch.cuda.is_current_stream_capturing():
-            raise _cabi.GateUpError(_cabi.GU_EWORKSPACE, "the scratch of this plan has to exist before stream capture "
-                                    "begins: make one call with this shape on this stream outside the capture first")
+        # Under stream capture (torch.cuda.graph switches to a stream of its own, which no eager call has used) the
+        # scratch comes from the graph's memory pool and its initialisation is recorded with the launch: every replay
+        # then starts from zeroed flags and a zero epoch counter, which is a valid state for the kernels.  The tensor
+        # kept here holds the pool's block alive for later calls on that stream.
         ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
         _cabi.check(_cabi.lib.gu_workspace_init(ws.data_ptr(), nbytes, stream_ptr))
         _WORKSPACES[key] = ws

@@ -1,10 +1,10 @@
-"""Host-side mirror of the two operators that sit beside the FP8 gate/up path in the reference repository.
+"""Host-side mirror of the operators that sit beside the FP8 gate/up path in the reference repository.
 
 `rmsnorm_qk` has the signature of the reference's problem-038 entry point
 (kernels/038_flux_multi_head_rmsnorm_qk/binding.cpp:26-64: destination passing, current stream, fp32 tensors);
 `mamba_conv1d_with_gating` that of problem 029 (kernels/029_mamba_conv1d_with_gating/binding.cpp:31-104:
-returns (output_hidden_states, gate)), with `mamba_conv1d_tail` as its hand-written part.  Both call
-libsideops.so through its C ABI; there is no other implementation behind them.
+returns (output_hidden_states, gate)), made of `mamba_in_proj` (the bf16 projection GEMM with bias) and
+`mamba_conv1d_tail`.  All call libsideops.so through its C ABI; there is no other implementation behind them.
 """
 from __future__ import annotations
 
@@ -102,20 +102,60 @@ def mamba_conv1d_tail(projected: torch.Tensor, attention_mask: torch.Tensor, con
 
 
 @torch.no_grad()
+def mamba_in_proj(hidden_states: torch.Tensor, in_proj_weight: torch.Tensor, in_proj_bias: torch.Tensor,
+                  projected: torch.Tensor) -> None:
+    """projected[..., N] = bf16(hidden_states[..., K] . in_proj_weight[N, K]^T + in_proj_bias[N]), fp32 accumulation.
+
+    The reference's projection launch (kernels/029_mamba_conv1d_with_gating/kernel.cu:274-312) fixes K = 8192 and
+    N = 32768; here K and N are any multiples of 8 and the leading dimensions are flattened into the row count.
+    """
+    _need(hidden_states.dim() >= 2, "hidden_states must be [..., K]")
+    _need(in_proj_weight.dim() == 2, "in_proj_weight must have shape [N, K]")
+    n, k = in_proj_weight.shape
+    _need(hidden_states.shape[-1] == k, f"hidden_states must have shape [..., {k}]")
+    _need(tuple(in_proj_bias.shape) == (n,), f"in_proj_bias must have shape [{n}]")
+    _need(tuple(projected.shape) == tuple(hidden_states.shape[:-1]) + (n,),
+          "projected must have the leading dimensions of hidden_states and N columns")
+    _need(k % 8 == 0 and n % 8 == 0 and k >= 8 and n >= 8, "K and N must be multiples of 8")
+    for t, name in ((hidden_states, "hidden_states"), (in_proj_weight, "in_proj_weight"),
+                    (in_proj_bias, "in_proj_bias"), (projected, "projected")):
+        _check_bf16(t, name, hidden_states.device)
+    m = hidden_states.numel() // k
+    if m == 0:
+        return
+    with torch.cuda.device(hidden_states.device):
+        stream = torch.cuda.current_stream(hidden_states.device).cuda_stream
+        _so.check(_so.lib.so_mamba_in_proj(hidden_states.data_ptr(), in_proj_weight.data_ptr(),
+                                           in_proj_bias.data_ptr(), projected.data_ptr(), m, k, n, stream))
+
+
+def last_status(clear: bool = True) -> Tuple[int, int]:
+    """(code, detail) of the library's device status word after a device synchronisation: code 0, or SO_ETIMEOUT
+    when a bounded wait inside the projection kernel ran out since the status was last cleared."""
+    import ctypes
+
+    detail = ctypes.c_int(0)
+    code = _so.lib.so_last_status(ctypes.byref(detail), 1 if clear else 0)
+    return code, detail.value
+
+
+@torch.no_grad()
 def mamba_conv1d_with_gating(hidden_states: torch.Tensor, attention_mask: torch.Tensor, in_proj_weight: torch.Tensor,
                              in_proj_bias: torch.Tensor, conv1d_weight: torch.Tensor,
                              conv1d_bias: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     """Problem 029 as the reference exposes it: (output_hidden_states [B, C, L], gate [B, C, L] view).
 
-    The input projection is a plain bf16 GEMM + bias and goes to the vendor library (the reference uses a CUTLASS
-    builder GEMM there, kernel.cu:36-160); the tail after it is this package's kernel.  `gate` is the transposed
-    view of the projection's upper half, as in the reference (binding.cpp:88-92).
+    Two launches of this package's kernels: the input projection (a tcgen05 bf16 GEMM with the bias in its epilogue;
+    the reference uses a CUTLASS builder GEMM there, kernel.cu:36-160) and the convolution tail.  `gate` is the
+    transposed view of the projection's upper half, as in the reference (binding.cpp:88-92).
     """
     _need(hidden_states.dim() == 3, "hidden_states must have shape [B, L, H]")
     projected_width = in_proj_weight.shape[0]
     _need(projected_width % 2 == 0, "in_proj_weight must have an even number of rows")
     channels = projected_width // 2
-    projected = torch.nn.functional.linear(hidden_states, in_proj_weight, in_proj_bias)
+    projected = torch.empty(hidden_states.shape[0], hidden_states.shape[1], projected_width,
+                            dtype=hidden_states.dtype, device=hidden_states.device)
+    mamba_in_proj(hidden_states, in_proj_weight, in_proj_bias, projected)
     gate = projected[:, :, channels:].transpose(1, 2)
     out = torch.empty(hidden_states.shape[0], channels, hidden_states.shape[1], dtype=hidden_states.dtype,
                       device=hidden_states.device)

@@ -84,15 +84,18 @@ PROBLEMS: Dict[str, Dict[str, Any]] = {
                        "issued before the reduction, HBM-bound.",
         "destination_passing_style": True,
         "sources": [("binding.cpp", BINDINGS / "binding_038.cpp"), ("sideops.cu", CSRC / "sideops.cu"),
+                    ("proj_gemm.cuh", CSRC / "proj_gemm.cuh"), ("ptx_sm100.cuh", CSRC / "ptx_sm100.cuh"),
                     ("sideops.h", INCLUDE / "sideops.h")],
     },
     "29": {
         "definition": "029_mamba_conv1d_with_gating",
-        "name": "mamba_conv1d_tail_packed_f32x2",
-        "description": "Mamba input projection through the vendor GEMM, then one kernel for mask, depthwise causal "
-                       "conv1d, SiLU, mask and the [L, C] -> [C, L] transposition with packed f32x2 arithmetic.",
+        "name": "mamba_in_proj_tcgen05_conv1d_tail_packed_f32x2",
+        "description": "Mamba input projection as a persistent tcgen05 bf16 GEMM on CTA pairs with the bias in its "
+                       "epilogue, then one kernel for mask, depthwise causal conv1d, SiLU, mask and the "
+                       "[L, C] -> [C, L] transposition with packed f32x2 arithmetic.",
         "destination_passing_style": False,
         "sources": [("binding.cpp", BINDINGS / "binding_029.cpp"), ("sideops.cu", CSRC / "sideops.cu"),
+                    ("proj_gemm.cuh", CSRC / "proj_gemm.cuh"), ("ptx_sm100.cuh", CSRC / "ptx_sm100.cuh"),
                     ("sideops.h", INCLUDE / "sideops.h")],
     },
 }

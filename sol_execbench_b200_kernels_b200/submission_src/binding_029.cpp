@@ -1,10 +1,8 @@
 // SOL-ExecBench problem 029 as a "cuda_cpp" submission.  Six bf16 inputs in, (output_hidden_states, gate) out, as
-// the reference's entry point has it (kernels/029_mamba_conv1d_with_gating/binding.cpp:31-104).  The input
-// projection is a plain GEMM + bias and is left to the vendor library (at::linear); `gate` is a transposed view of
-// the projection's upper half, never copied; everything after the projection is one call into the C ABI of
-// sideops.h on torch's current stream.
+// the reference's entry point has it (kernels/029_mamba_conv1d_with_gating/binding.cpp:31-104).  Two calls into the
+// C ABI of sideops.h on torch's current stream: the input projection (bf16 GEMM with the bias in its epilogue) and
+// everything after it; `gate` is a transposed view of the projection's upper half, never copied.
 #include <ATen/cuda/CUDAContext.h>
-#include <ATen/ops/linear.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
 
@@ -55,7 +53,14 @@ std::tuple<torch::Tensor, torch::Tensor> run(const torch::Tensor& hidden_states,
               "conv1d_weight: expected [", C, ", 1, 4]");
   TORCH_CHECK(conv1d_bias.dim() == 1 && conv1d_bias.size(0) == C, "conv1d_bias: expected [", C, "]");
 
-  torch::Tensor projection = at::linear(hidden_states, in_proj_weight, in_proj_bias);  // [B, L, 2 C]
+  TORCH_CHECK(H % 8 == 0 && H >= 8, "hidden_states: H must be a multiple of 8, got ", H);
+  torch::Tensor projection = torch::empty({B, L, two_c}, hidden_states.options());
+  if (B > 0 && L > 0) {
+    const int status = so_mamba_in_proj(hidden_states.data_ptr(), in_proj_weight.data_ptr(), in_proj_bias.data_ptr(),
+                                        projection.data_ptr(), B * L, H, two_c,
+                                        at::cuda::getCurrentCUDAStream(device).stream());
+    TORCH_CHECK(status == SO_OK, "so_mamba_in_proj failed: ", so_error_string(status));
+  }
   torch::Tensor gate = projection.narrow(/*dim=*/2, /*start=*/C, /*length=*/C).transpose(1, 2);
   torch::Tensor mixed = torch::empty({B, C, L}, hidden_states.options());
   if (B > 0 && L > 0) {

@@ -181,3 +181,101 @@ def test_mamba_with_gating_matches_reference_op_when_built():
     assert got_gate.stride() == want_gate.stride()
     rel = float(torch.linalg.vector_norm(got_out.float() - want_out.float()) / torch.linalg.vector_norm(want_out.float()))
     assert rel <= 1e-2
+
+
+# ------------------------------------------------------------------------------------------------------------
+# Input projection of problem 029: bf16 GEMM + bias.  The exact (float64) result is rounded once to bf16 by an ideal
+# implementation; fp32 accumulation over K in another order moves a value by far less than a rounding step, but can
+# move it across a rounding boundary, so the bound is one bf16 step (2^-8 relative to the value) plus the
+# accumulation error (a small multiple of 2^-24 of the sum of the products' magnitudes; 2^-16 of it is allowed).
+# ------------------------------------------------------------------------------------------------------------
+PROJ_SHAPES = [(1, 64, 8), (5, 8, 16), (127, 72, 264), (128, 256, 512), (129, 512, 256), (256, 64, 256),
+               (300, 1024, 776), (257, 200, 1000), (1000, 520, 2048), (512, 8192, 1024), (2048, 1024, 4096)]
+
+
+def _proj_inputs(m, k, n, seed):
+    g = torch.Generator().manual_seed(seed)
+    hidden = (torch.randn(m, k, generator=g) * 0.5).to(torch.bfloat16).to(_dev())
+    weight = (torch.randn(n, k, generator=g) * 0.04).to(torch.bfloat16).to(_dev())
+    bias = (torch.randn(n, generator=g) * 0.2).to(torch.bfloat16).to(_dev())
+    return hidden, weight, bias
+
+
+def _assert_proj_close(got, hidden, weight, bias, label):
+    exact = O.mamba_in_proj(hidden, weight, bias, exact=True)              # float64, on the GPU
+    mags = hidden.double().abs() @ weight.double().abs().t() + bias.double().abs()
+    bound = exact.abs() * 2.0 ** -8 + mags * 2.0 ** -16 + 1e-30
+    err = (got.double() - exact).abs()
+    worst = float((err / bound).max())
+    assert worst <= 1.0, f"{label}: error / bound = {worst}"
+    # and the typical value is correctly rounded: most outputs equal the rounding of the exact result
+    same = float((got == exact.to(torch.bfloat16)).double().mean())
+    assert same >= 0.98, f"{label}: only {same:.4f} of the outputs equal the rounded exact result"
+
+
+@pytest.mark.parametrize("shape", PROJ_SHAPES)
+def test_mamba_in_proj_matches_exact_product(shape):
+    from sol_execbench_b200_kernels_b200 import side_ops
+    m, k, n = shape
+    hidden, weight, bias = _proj_inputs(m, k, n, seed=m + k + n)
+    got = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=_dev())
+    side_ops.mamba_in_proj(hidden, weight, bias, got)
+    torch.cuda.synchronize()
+    assert side_ops.last_status() == (0, 0)
+    assert torch.isfinite(got.float()).all()
+    _assert_proj_close(got, hidden, weight, bias, str(shape))
+    # the CPU restatement (fp32 accumulation in the library's order) agrees within the same bound
+    if m * k * n <= 300 * 1024 * 776:
+        want = O.mamba_in_proj(hidden.cpu(), weight.cpu(), bias.cpu())
+        _assert_proj_close(want.to(_dev()), hidden, weight, bias, f"oracle {shape}")
+        assert float((got.cpu() == want).double().mean()) >= 0.98
+
+
+def test_mamba_in_proj_is_deterministic_and_leaves_neighbours_alone():
+    from sol_execbench_b200_kernels_b200 import side_ops
+    m, k, n = 333, 512, 520
+    hidden, weight, bias = _proj_inputs(m, k, n, seed=4)
+    # the destination sits inside a larger allocation: rows before and after it must keep their contents
+    buf = torch.full((m + 2, n), 7.0, dtype=torch.bfloat16, device=_dev())
+    out = buf[1:m + 1]
+    side_ops.mamba_in_proj(hidden, weight, bias, out)
+    first = out.clone()
+    side_ops.mamba_in_proj(hidden, weight, bias, out)
+    torch.cuda.synchronize()
+    assert torch.equal(out, first)
+    assert (buf[0] == 7.0).all() and (buf[m + 1] == 7.0).all()
+    # 3-D input as the operator passes it, and a row count of zero
+    out3 = torch.empty(3, 111, n, dtype=torch.bfloat16, device=_dev())
+    side_ops.mamba_in_proj(hidden.reshape(3, 111, k), weight, bias, out3)
+    assert torch.equal(out3.reshape(m, n), first)
+    side_ops.mamba_in_proj(hidden[:0], weight, bias, out[:0])
+
+
+def test_mamba_in_proj_pair_and_lone_kernels_agree_on_shared_rows():
+    """Rows are independent: the first 128 rows computed by the lone-CTA kernel (M = 128) equal the same rows of a
+    larger problem computed by the pair kernel, bit for bit (same K order, same epilogue)."""
+    from sol_execbench_b200_kernels_b200 import side_ops
+    k, n = 1024, 768
+    hidden, weight, bias = _proj_inputs(512, k, n, seed=6)
+    big = torch.empty(512, n, dtype=torch.bfloat16, device=_dev())
+    small = torch.empty(128, n, dtype=torch.bfloat16, device=_dev())
+    side_ops.mamba_in_proj(hidden, weight, bias, big)
+    side_ops.mamba_in_proj(hidden[:128], weight, bias, small)
+    torch.cuda.synchronize()
+    assert torch.equal(big[:128], small)
+
+
+def test_mamba_in_proj_rejects_what_the_contract_excludes():
+    from sol_execbench_b200_kernels_b200 import side_ops
+    hidden, weight, bias = _proj_inputs(16, 64, 64, seed=8)
+    out = torch.empty(16, 64, dtype=torch.bfloat16, device=_dev())
+    with pytest.raises(ValueError, match="bfloat16"):
+        side_ops.mamba_in_proj(hidden.float(), weight, bias, out)
+    with pytest.raises(ValueError, match="in_proj_bias"):
+        side_ops.mamba_in_proj(hidden, weight, bias[:32], out)
+    with pytest.raises(ValueError, match="multiples of 8"):
+        side_ops.mamba_in_proj(hidden[:, :60].contiguous(), weight[:, :60].contiguous(), bias, out)
+    with pytest.raises(ValueError, match="contiguous"):
+        side_ops.mamba_in_proj(hidden, weight.t().contiguous().t(), bias, out)
+    with pytest.raises(ValueError, match="projected"):
+        side_ops.mamba_in_proj(hidden, weight, bias, out[:8])

@@ -48,6 +48,14 @@ def test_c_abi_rejects_bad_arguments_before_any_cuda_call(so):
     assert g(8, 16, 16, 16, 16, 1, 8, 64, 64, None) == so.SO_EINVAL_ALIGN
     assert g(16, 16, 16, 16, 8, 1, 8, 64, 64, None) == so.SO_EINVAL_ALIGN
     assert g(16, 16, 16, 16, 16, 0, 8, 64, 64, None) == so.SO_OK
+    h = so.lib.so_mamba_in_proj
+    assert h(16, 16, None, 16, 4, 64, 64, None) == so.SO_EINVAL_NULL
+    assert h(16, 16, 16, 16, 4, 60, 64, None) == so.SO_EINVAL_SHAPE           # K not a multiple of 8
+    assert h(16, 16, 16, 16, 4, 64, 4, None) == so.SO_EINVAL_SHAPE            # N below 8
+    assert h(16, 16, 16, 16, -1, 64, 64, None) == so.SO_EINVAL_SHAPE
+    assert h(16, 8, 16, 16, 4, 64, 64, None) == so.SO_EINVAL_ALIGN
+    assert h(16, 16, 16, 16, 0, 64, 64, None) == so.SO_OK                     # no rows: nothing to launch
+    assert "wait" in so.error_string(so.SO_ETIMEOUT) and "10.x" in so.error_string(so.SO_EDEVICE)
     assert so.lib.so_launch_count() == 0
 
 
