@@ -136,6 +136,12 @@ int device_info(DeviceInfo** out) {
             cudaSuccess ||
         cudaFuncSetAttribute(gateup_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
         cudaFuncSetAttribute(blockwise_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
+            cudaSuccess ||
+        cudaFuncSetAttribute(gateup_pair_gather_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
+            cudaSuccess ||
+        cudaFuncSetAttribute(gateup_pair_fp8out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
+            cudaSuccess ||
+        cudaFuncSetAttribute(blockwise_gemm_pair_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
             cudaSuccess) {
       cudaGetLastError();
       return GU_ECUDA;
@@ -377,6 +383,22 @@ int launch_pair(const gu_problem* pr, const DeviceInfo& dev, cudaStream_t stream
 // The tile plan's kernel for a shape: CTA pairs once there is more than one 128-token block (a lone block would
 // leave the second CTA of every pair without rows), the lone-CTA kernel otherwise.
 bool tile_prefers_pairs(int64_t m, const DeviceInfo& dev) { return m > kTileM && dev.pair_clusters >= 1; }
+
+// Tile geometry of a pair launch: 256-token pair blocks x `col_tiles` column tiles, raster groups that keep a
+// group's activation rows (256 x K bytes per pair block) within ~24 MiB of L2.  Returns the number of clusters to
+// launch, or 0 when the schedule's 32-bit (tile, K block) count would overflow.
+int pair_geometry(TileParams& p, const DeviceInfo& dev, int64_t m, int64_t k, int col_tiles) {
+  p.num_m_blocks = static_cast<int>((m + 2 * kTileM - 1) / (2 * kTileM));
+  p.num_n_blocks = col_tiles;
+  const int64_t tiles = int64_t(p.num_m_blocks) * p.num_n_blocks;
+  if (tiles * (k / 128) >= (1ll << 31)) return 0;
+  p.num_tiles = static_cast<int>(tiles);
+  int64_t gm = (24ll << 20) / (256 * k);
+  if (gm < 1) gm = 1;
+  if (gm > p.num_m_blocks) gm = p.num_m_blocks;
+  p.group_m = static_cast<int>(gm);
+  return p.num_tiles < dev.pair_clusters ? p.num_tiles : dev.pair_clusters;
+}
 
 template <int MPAD>
 int launch_stream_t(const gu_problem* pr, const DeviceInfo& dev, cudaStream_t stream, int stages) {
@@ -681,6 +703,14 @@ int gu_run_gather(const gu_problem* pr, void* const* rank_outputs, int world, in
   p.out_rank = rank;
   p.out_col0 = static_cast<int>(int64_t(rank) * n);
 
+  if (gu::tile_prefers_pairs(m, *dev)) {
+    const int clusters = gu::pair_geometry(p, *dev, m, k, static_cast<int>(n / gu::kTileN));
+    if (clusters < 1) return GU_EINVAL_SHAPE;
+    gu::gateup_pair_gather_kernel<<<2 * clusters, gu::kPairThreads, gu::kPairSmemBytes,
+                                    static_cast<cudaStream_t>(stream_v)>>>(tm_x, tm_g, tm_u, peers, p);
+    gu::g_launches.fetch_add(1, std::memory_order_relaxed);
+    return cudaGetLastError() == cudaSuccess ? GU_OK : GU_ECUDA;
+  }
   const int grid = p.num_tiles < dev->sm_count ? p.num_tiles : dev->sm_count;
   gu::gateup_tile_gather_kernel<<<grid, gu::kTileThreads, gu::kTileSmemBytes, static_cast<cudaStream_t>(stream_v)>>>(
       tm_x, tm_g, tm_u, peers, p);
@@ -741,9 +771,17 @@ int gu_blockwise_gemm_scatter(const void* a, const float* scale_a, const void* b
   p.out_count = world;
   p.out_rank = rank;
   p.out_col0 = 0;
-  p.blocks_per_owner = p.num_m_blocks / world;
+  p.blocks_per_owner = p.num_m_blocks / world;  // in 128-token blocks, whichever kernel runs
   p.slot_rows = static_cast<int>(slot_rows);
 
+  if (gu::tile_prefers_pairs(m, *dev)) {
+    const int clusters = gu::pair_geometry(p, *dev, m, k, (p.n_blocks128 + 1) / 2);
+    if (clusters < 1) return GU_EINVAL_SHAPE;
+    gu::blockwise_gemm_pair_scatter_kernel<<<2 * clusters, gu::kPairThreads, gu::kPairSmemBytes,
+                                             static_cast<cudaStream_t>(stream_v)>>>(tm_a, tm_b, peers, p);
+    gu::g_launches.fetch_add(1, std::memory_order_relaxed);
+    return cudaGetLastError() == cudaSuccess ? GU_OK : GU_ECUDA;
+  }
   const int grid = p.num_tiles < dev->sm_count ? p.num_tiles : dev->sm_count;
   gu::blockwise_gemm_scatter_kernel<<<grid, gu::kTileThreads, gu::kTileSmemBytes, static_cast<cudaStream_t>(stream_v)>>>(
       tm_a, tm_b, peers, p);
@@ -882,7 +920,17 @@ int gu_run_fp8out(const gu_problem* pr, void* out_q, float* out_scale, void* str
   p.out_col0 = 0;
   p.n_blocks128 = static_cast<int>(n / 128);
   p.scale_out = out_scale;
+  p.blocks_per_owner = 1;
+  p.slot_rows = 0;
 
+  if (gu::tile_prefers_pairs(m, *dev)) {
+    const int clusters = gu::pair_geometry(p, *dev, m, k, static_cast<int>(n / gu::kTileN));
+    if (clusters < 1) return GU_EINVAL_SHAPE;
+    gu::gateup_pair_fp8out_kernel<<<2 * clusters, gu::kPairThreads, gu::kPairSmemBytes,
+                                    static_cast<cudaStream_t>(stream_v)>>>(tm_x, tm_g, tm_u, tm_q, p);
+    gu::g_launches.fetch_add(1, std::memory_order_relaxed);
+    return cudaGetLastError() == cudaSuccess ? GU_OK : GU_ECUDA;
+  }
   const int grid = p.num_tiles < dev->sm_count ? p.num_tiles : dev->sm_count;
   gu::gateup_tile_fp8out_kernel<<<grid, gu::kTileThreads, gu::kTileSmemBytes, static_cast<cudaStream_t>(stream_v)>>>(
       tm_x, tm_g, tm_u, tm_q, p);

@@ -163,10 +163,44 @@ __device__ __forceinline__ void mbar_wait_lane(WaitCtx& ctx, bool elected, uint3
 // GEMM the reference launches twice (kernel.py:487-488); here the MLP's down projection.  The two 128-row weight
 // tiles of a K block are then two ADJACENT 128-column blocks of one B matrix (tm_gate; scale rows 2n and 2n+1 of
 // scale_gate), a pair tile is 256 x 256 outputs, and the epilogue warps only issue the stores of the handed-over tiles.
-template <bool kSingle>
+//
+// kMode selects what the epilogue warps do with a finished tile:
+//   kPairPlain    SwiGLU (or, kSingle, nothing) and the TMA stores into outs[0]
+//   kPairGather   SwiGLU, then the tile is stored into every rank's buffer at this rank's column offset (own and
+//                 peers' over NVLink; plain TMA stores, no load touches peer memory): the all-gather of a
+//                 column-sharded result inside the epilogue (TileParams::out_count, out_rank, out_col0)
+//   kPairScatter  kSingle only: the tile of a row-parallel GEMM's partial result goes to the rank that owns its
+//                 token block, into the sending rank's slot (TileParams::blocks_per_owner, slot_rows)
+//   kPairFp8Out   SwiGLU, then the tile is re-quantised to e4m3 with one fp32 scale per token and 128 columns
+//                 (amax / 448; the tile is exactly one scale block wide) and stored as e4m3 + scales: the operand
+//                 format of the next block-scaled GEMM.  Bits equal quantising the bf16 result.
+enum : int { kPairPlain = 0, kPairGather = 1, kPairScatter = 2, kPairFp8Out = 3 };
+
+// |a|, |b| of a packed bf16 pair folded into a running maximum
+__device__ __forceinline__ float amax_bf16x2(float m, uint32_t pr) {
+  return fmaxf(m, fmaxf(fabsf(__uint_as_float(pr << 16)), fabsf(__uint_as_float(pr & 0xffff0000u))));
+}
+// four e4m3 from two packed bf16 pairs: v / sc correctly rounded (reciprocal, then one exact-residual step), then
+// round-to-nearest-even with saturation
+__device__ __forceinline__ uint32_t e4m3x4_from_bf16x4(uint32_t p0, uint32_t p1, float sc, float rc) {
+  uint32_t word = 0;
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    const uint32_t pr = e ? p1 : p0;
+    const float a = __uint_as_float(pr << 16), b = __uint_as_float(pr & 0xffff0000u);
+    const float qa0 = a * rc, qb0 = b * rc;
+    const float qa = fmaf(fmaf(-qa0, sc, a), rc, qa0), qb = fmaf(fmaf(-qb0, sc, b), rc, qb0);
+    word |= static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(make_float2(qa, qb), __NV_SATFINITE, __NV_E4M3)) << (16 * e);
+  }
+  return word;
+}
+
+template <bool kSingle, int kMode = kPairPlain>
 __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tm_x, const CUtensorMap& tm_gate,
-                                                 const CUtensorMap& tm_up, const CUtensorMap& tm_out,
+                                                 const CUtensorMap& tm_up, const CUtensorMap* outs,
                                                  const TileParams& p) {
+  static_assert(kMode != kPairScatter || kSingle, "scatter is a mode of the plain GEMM");
+  static_assert((kMode != kPairGather && kMode != kPairFp8Out) || !kSingle, "gather / fp8 output are modes of gate/up");
   extern __shared__ uint8_t smem_raw[];
   // operand tiles need 1024-byte alignment for the 128-byte swizzle pattern; both CTAs of a pair get the same offsets
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -211,7 +245,11 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tm_x, const 
     tma_prefetch_desc(&tm_x);
     tma_prefetch_desc(&tm_gate);
     tma_prefetch_desc(&tm_up);
-    tma_prefetch_desc(&tm_out);
+    if constexpr (kMode == kPairGather || kMode == kPairScatter) {
+      for (int r = 0; r < p.out_count; ++r) tma_prefetch_desc(&outs[r]);
+    } else {
+      tma_prefetch_desc(&outs[0]);
+    }
   }
   if (warp == 1) {
     tmem_alloc_pair(tmem_slot, kTileTmemCols);
@@ -248,6 +286,7 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tm_x, const 
           const uint32_t full = full_even + 8 * stage;
           const uint32_t dst = ring + stage * kPairStageBytes;
           const int b_row = kSingle ? (2 * nb + static_cast<int>(rank)) * kTileN : nb * kTileN;
+          (void)b_row;  // (only the range-checked build looks at it)
           if (ok && elected && GU_IN_RANGE(stage < kPairStages, kSitePairStage) &&
               GU_IN_RANGE(load_coords_ok(p.kb, j, row0, 2 * p.num_m_blocks * kTileM) &&
                               load_coords_ok(p.kb, j, b_row, (kSingle ? 2 : 1) * p.num_n_blocks * kTileN), kSitePairLoad)) {
@@ -352,21 +391,78 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tm_x, const 
             if (ok && !ctx.aborted && row0 < p.m &&
                 GU_IN_RANGE(p.out_cols == 0 || (2 * nb * kTileN + 128 <= p.out_cols && row0 >= 0 && row0 < p.out_rows),
                             kSitePairStore)) {
-              tma_store_2d(&tm_out, hand, 2 * nb * kTileN, row0);
-              tma_store_2d(&tm_out, hand + kTileOutHalfBytes, 2 * nb * kTileN + 64, row0);
+              const CUtensorMap* dst = &outs[0];
+              int y = row0;
+              if constexpr (kMode == kPairScatter) {
+                // partial result of a row-parallel GEMM: plain TMA store into the owner rank's buffer (over NVLink
+                // unless it is this rank), in the slot reserved for this rank; the owner sums the slots
+                const int mb = 2 * pm + static_cast<int>(rank);  // this CTA's 128-token block
+                const int owner = mb / p.blocks_per_owner;
+                y = p.out_rank * p.slot_rows + (mb - owner * p.blocks_per_owner) * kTileM;
+                dst = &outs[owner];
+              }
+              tma_store_2d(dst, hand, 2 * nb * kTileN, y);
+              tma_store_2d(dst, hand + kTileOutHalfBytes, 2 * nb * kTileN + 64, y);
               if (2 * nb + 1 < p.n_blocks128) {
-                tma_store_2d(&tm_out, hand + 2 * kTileOutHalfBytes, (2 * nb + 1) * kTileN, row0);
-                tma_store_2d(&tm_out, hand + 3 * kTileOutHalfBytes, (2 * nb + 1) * kTileN + 64, row0);
+                tma_store_2d(dst, hand + 2 * kTileOutHalfBytes, (2 * nb + 1) * kTileN, y);
+                tma_store_2d(dst, hand + 3 * kTileOutHalfBytes, (2 * nb + 1) * kTileN + 64, y);
               }
               tma_store_commit();
               tma_store_wait_read0();
             }
             mbar_arrive(bar_hand_empty);
           }
-          GU_TR_END(7);
-          hand_phase ^= 1u;
-          continue;
-        }
+        } else if constexpr (kMode == kPairFp8Out) {
+          // A thread owns whole rows (et, et + 64, ...): SwiGLU in place over the row's 16 chunks with the row's
+          // largest magnitude, then the row's 128 e4m3 into the bytes the row's first 64 up values occupied (this
+          // thread has read them all), in the staging layout of a 128-byte-row tile.
+#pragma unroll 1
+          for (int r = et; r < kTileM; r += kPairEpiThreads) {
+            uint8_t* grow = hand_gen + r * 128;
+            uint8_t* urow = grow + 2 * kTileOutHalfBytes;
+            float amax = 0.f;
+#pragma unroll 4
+            for (int c = 0; c < 16; ++c) {
+              const uint32_t off = (c >> 3) * kTileOutHalfBytes + (((c & 7) ^ (r & 7)) << 4);
+              const uint4 a = *reinterpret_cast<const uint4*>(grow + off);
+              const uint4 b = *reinterpret_cast<const uint4*>(urow + off);
+              uint4 o;
+              o.x = swiglu_packed_bf16x2(a.x, b.x);
+              o.y = swiglu_packed_bf16x2(a.y, b.y);
+              o.z = swiglu_packed_bf16x2(a.z, b.z);
+              o.w = swiglu_packed_bf16x2(a.w, b.w);
+              amax = amax_bf16x2(amax_bf16x2(amax_bf16x2(amax_bf16x2(amax, o.x), o.y), o.z), o.w);
+              *reinterpret_cast<uint4*>(grow + off) = o;
+            }
+            const float sc = fmaxf(amax, 1e-12f) / 448.0f;
+            const float rc = __frcp_rn(sc);
+#pragma unroll 2
+            for (int q = 0; q < 8; ++q) {  // 8 chunks of 16 e4m3, each from two chunks of 8 bf16
+              const uint32_t off0 = ((2 * q) >> 3) * kTileOutHalfBytes + ((((2 * q) & 7) ^ (r & 7)) << 4);
+              const uint32_t off1 = ((2 * q + 1) >> 3) * kTileOutHalfBytes + ((((2 * q + 1) & 7) ^ (r & 7)) << 4);
+              const uint4 o0 = *reinterpret_cast<const uint4*>(grow + off0);
+              const uint4 o1 = *reinterpret_cast<const uint4*>(grow + off1);
+              uint4 w;
+              w.x = e4m3x4_from_bf16x4(o0.x, o0.y, sc, rc);
+              w.y = e4m3x4_from_bf16x4(o0.z, o0.w, sc, rc);
+              w.z = e4m3x4_from_bf16x4(o1.x, o1.y, sc, rc);
+              w.w = e4m3x4_from_bf16x4(o1.z, o1.w, sc, rc);
+              *reinterpret_cast<uint4*>(urow + ((q ^ (r & 7)) << 4)) = w;
+            }
+            if (row0 + r < p.m && GU_IN_RANGE(nb >= 0 && nb < p.n_blocks128, kSitePairScaleOut))
+              p.scale_out[static_cast<size_t>(row0 + r) * p.n_blocks128 + nb] = sc;
+          }
+          fence_proxy_async_smem();
+          named_bar_sync(1, kPairEpiThreads);
+          if (et == 0) {
+            if (ok && !ctx.aborted && row0 < p.m) {
+              tma_store_2d(&outs[0], hand + 2 * kTileOutHalfBytes, nb * kTileN, row0);
+              tma_store_commit();
+              tma_store_wait_read0();
+            }
+            mbar_arrive(bar_hand_empty);
+          }
+        } else {
         // gate and up tiles have the same layout, so chunk q of one meets chunk q of the other whatever it holds
 #pragma unroll 4
         for (int i = 0; i < 2048 / kPairEpiThreads; ++i) {
@@ -386,12 +482,28 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tm_x, const 
           if (ok && !ctx.aborted && row0 < p.m &&
               GU_IN_RANGE(p.out_cols == 0 || (nb * kTileN + 128 <= p.out_cols && row0 >= 0 && row0 < p.out_rows),
                           kSitePairStore)) {
-            tma_store_2d(&tm_out, hand, nb * kTileN, row0);
-            tma_store_2d(&tm_out, hand + kTileOutHalfBytes, nb * kTileN + 64, row0);
+            if constexpr (kMode == kPairGather) {
+              // Destinations are visited in a rotation that differs per source rank and per cluster, so that at any
+              // moment the box's ranks are writing to different peers instead of all to the same one.
+              const int peers = p.out_count - 1;
+              const int col = p.out_col0 + nb * kTileN;
+              tma_store_2d(&outs[p.out_rank], hand, col, row0);
+              tma_store_2d(&outs[p.out_rank], hand + kTileOutHalfBytes, col + 64, row0);
+              for (int i = 0; i < peers; ++i) {
+                const int hop = 1 + (i + cluster_id + pm) % peers;
+                const CUtensorMap* dst = &outs[(p.out_rank + hop) % p.out_count];
+                tma_store_2d(dst, hand, col, row0);
+                tma_store_2d(dst, hand + kTileOutHalfBytes, col + 64, row0);
+              }
+            } else {
+              tma_store_2d(&outs[0], hand, nb * kTileN, row0);
+              tma_store_2d(&outs[0], hand + kTileOutHalfBytes, nb * kTileN + 64, row0);
+            }
             tma_store_commit();
             tma_store_wait_read0();  // the tile may be overwritten once the stores have read it
           }
           mbar_arrive(bar_hand_empty);
+        }
         }
         GU_TR_END(7);
         hand_phase ^= 1u;
@@ -568,14 +680,39 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 gateup_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_gate,
                    const __grid_constant__ CUtensorMap tm_up, const __grid_constant__ CUtensorMap tm_out,
                    const TileParams p) {
-  pair_kernel_body<false>(tm_x, tm_gate, tm_up, tm_out, p);
+  pair_kernel_body<false>(tm_x, tm_gate, tm_up, &tm_out, p);
+}
+
+// Gate/up + SwiGLU with the column all-gather fused into the epilogue (see TileParams::out_count).
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
+gateup_pair_gather_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_gate,
+                          const __grid_constant__ CUtensorMap tm_up, const __grid_constant__ PeerMaps peers,
+                          const TileParams p) {
+  pair_kernel_body<false, kPairGather>(tm_x, tm_gate, tm_up, peers.m, p);
+}
+
+// Gate/up + SwiGLU with the result re-quantised to e4m3 + 1x128 scales in the epilogue; `tm_outq` describes the
+// e4m3 [M, N] destination with 128-byte x 128-row boxes.
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
+gateup_pair_fp8out_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_gate,
+                          const __grid_constant__ CUtensorMap tm_up, const __grid_constant__ CUtensorMap tm_outq,
+                          const TileParams p) {
+  pair_kernel_body<false, kPairFp8Out>(tm_x, tm_gate, tm_up, &tm_outq, p);
 }
 
 // Plain block-scaled GEMM (single-projection mode) on CTA pairs.
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 blockwise_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                            const __grid_constant__ CUtensorMap tm_c, const TileParams p) {
-  pair_kernel_body<true>(tm_a, tm_b, tm_b, tm_c, p);
+  pair_kernel_body<true>(tm_a, tm_b, tm_b, &tm_c, p);
+}
+
+// Plain block-scaled GEMM whose output tiles are scattered to the ranks that own their token rows (see
+// TileParams::blocks_per_owner): the compute half of a fused GEMM + reduce-scatter.
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
+blockwise_gemm_pair_scatter_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                                   const __grid_constant__ PeerMaps peers, const TileParams p) {
+  pair_kernel_body<true, kPairScatter>(tm_a, tm_b, tm_b, peers.m, p);
 }
 
 }  // namespace gu

@@ -127,7 +127,7 @@ print(f"rank {rank} ok")
 
 
 @pytest.mark.parametrize("shape,world", [((128, 256, 128), 1), ((512, 512, 384), 2), ((1024, 1024, 256), 8),
-                                         ((1536, 512, 1024), 4)])
+                                         ((1536, 512, 1024), 4), ((384, 768, 640), 3), ((640, 640, 128), 5)])
 def test_scatter_and_reduce_on_one_gpu_sum_the_partial_products(shape, world):
     """All ranks of the fused GEMM + all-reduce emulated one after another on one GPU (separate buffers, no kernel
     waits on another): every rank's result must equal the fp32 sum, in rank order, of the bf16 partial products."""
@@ -167,6 +167,29 @@ def test_scatter_and_reduce_on_one_gpu_sum_the_partial_products(shape, world):
         assert torch.equal(outs[r][r * rows:(r + 1) * rows], want[r * rows:(r + 1) * rows])
         rest = torch.cat([outs[r][:r * rows], outs[r][(r + 1) * rows:]])
         assert bool(torch.isnan(rest.float()).all())
+
+
+@pytest.mark.parametrize("shape,world", [((100, 256, 256), 2), ((128, 512, 1024), 4), ((300, 512, 512), 2),
+                                         ((1000, 1024, 1024), 4), ((513, 256, 2048), 8)])
+def test_gather_epilogue_on_one_gpu_fills_every_ranks_buffer(shape, world):
+    """All ranks of the fused column all-gather emulated one after another on one GPU (one full-width buffer per
+    rank, no kernel waits on another): after every rank has run, every buffer must equal the unsharded result bit for
+    bit.  Token counts up to 128 take the lone-CTA kernel, larger ones the pair kernel; ragged counts included."""
+    import sol_execbench_b200_kernels_b200 as pkg
+
+    m, k, n = shape
+    dev = torch.device("cuda:0")
+    inp = W.make_inputs(m, k, n, seed=70 + m).to(dev)
+    ref = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+    pkg.run(*inp.args(), ref)
+    bufs = [torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=dev) for _ in range(world)]
+    for r in range(world):
+        gw, sg, uw, su = pkg.shard_weights(inp.gate_proj_weight, inp.scale_gate, inp.up_proj_weight, inp.scale_up, r, world)
+        pkg.run_gather(inp.x, inp.scale_x, gw, sg, uw, su, [b.data_ptr() for b in bufs], r, (m, n), n)
+    torch.cuda.synchronize()
+    assert pkg.last_status()[0] == 0
+    for r in range(world):
+        assert torch.equal(bufs[r], ref), f"buffer of rank {r}"
 
 
 def test_scatter_rejects_token_counts_that_do_not_split_into_whole_blocks():
