@@ -278,8 +278,9 @@ def run_sweep(args):
         inp = W.make_inputs(m, k, n, seed=0, device=dev)
         out = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
         entry = {"m": m, "auto_plan": pkg.select_plan(m, k, n), "plans": {}}
-        # "tile" is the heuristic's tile kernel (CTA pairs above 128 tokens), "tile_dp" the lone-CTA kernel forced
-        for plan in (("stream", "tile") if m <= 64 else (("tile",) if m <= 128 else ("tile", "tile_dp"))):
+        # "tile" is the heuristic's tile kernel (CTA pairs above 128 tokens, their stream-K schedule where whole tiles
+        # would idle 5 % of the device), "tile_pair" the pair kernel with whole tiles forced, "tile_dp" the lone-CTA kernel
+        for plan in (("stream", "tile") if m <= 64 else (("tile",) if m <= 128 else ("tile", "tile_pair", "tile_dp"))):
             ms, _ = time_device_steps(lambda: pkg.run_with_plan(*inp.args(), out, plan), args.steps, args.warmup, flush)
             ms /= args.steps
             roof = roofline_for(m, k, n, ms, peaks, W)

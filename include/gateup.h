@@ -46,7 +46,9 @@ extern "C" {
 #define GU_PLAN_STREAM 2  /* weight-streaming, tokens on the MMA N side, stream-K over (N-block, K-block); M <= 64 */
 #define GU_PLAN_TILE_DP 3 /* lone-CTA tile kernel, data-parallel schedule forced (whole tiles per CTA, no scratch) */
 #define GU_PLAN_TILE_SK 4 /* lone-CTA tile kernel, stream-K schedule forced (needs scratch)                  */
-#define GU_PLAN_TILE_PAIR 5      /* CTA-pair tile kernel forced (256-token tiles, cta_group::2), any M        */
+#define GU_PLAN_TILE_PAIR 5      /* CTA-pair tile kernel forced (256-token tiles, cta_group::2), any M, whole tiles per cluster */
+#define GU_PLAN_TILE_PAIR_SK 6   /* CTA-pair tile kernel, stream-K schedule forced (needs scratch; at least as many
+                                    256-token x 128-column tiles as CTA pairs on the device, else GU_EINVAL_PLAN) */
 
 /*
  * One call's operands.  Replaces the seven tensors of the reference `run`
@@ -104,10 +106,18 @@ int gu_workspace_init(void* workspace, size_t bytes, void* stream);
  * of the reference `run`: two GEMM launches and the SwiGLU launch
  * (kernel.py:487-503), or `launch_fp8_mlp_gate_up` (cuda_cpp_v4/kernel.cu:271-341).
  * Asynchronous; returns after the launch with 0 or a negative code.
- * With GU_PLAN_AUTO / TILE / TILE_DP / STREAM the launch keeps no host-side
- * state, so a launch recorded in a CUDA graph may be replayed (the workspace
- * must stay allocated and be used by nothing else meanwhile); GU_PLAN_TILE_SK,
- * a study option, stamps its flags from a host counter and must not be replayed.
+ * With GU_PLAN_AUTO / TILE / TILE_DP / TILE_PAIR / TILE_PAIR_SK / STREAM the
+ * launch keeps no host-side state (the stream-K schedules of the pair and the
+ * streaming kernel count their launches in the workspace), so a launch recorded
+ * in a CUDA graph may be replayed (the workspace must stay allocated and be used
+ * by nothing else meanwhile); GU_PLAN_TILE_SK, a study option, stamps its flags
+ * from a host counter and must not be replayed.
+ * GU_PLAN_TILE above 128 tokens picks the pair kernel's stream-K schedule when a
+ * workspace of gu_workspace_bytes() is passed, there are at least two rounds of
+ * tiles and whole tiles would leave 4 % or more of the device idle in the last; the sums of a tile cut in two are
+ * joined by one extra fp32 addition, so its outputs may differ from the
+ * data-parallel schedule's in the last bf16 digit.  Without a workspace the
+ * data-parallel schedule runs.
  */
 int gu_run(const gu_problem* problem, void* stream);
 

@@ -22,9 +22,9 @@ GU_ETIMEOUT = -8
 GU_ESTATIC_LIMIT = -9
 GU_EBOUNDS = -10
 
-PLAN_AUTO, PLAN_TILE, PLAN_STREAM, PLAN_TILE_DP, PLAN_TILE_SK, PLAN_TILE_PAIR = 0, 1, 2, 3, 4, 5
+PLAN_AUTO, PLAN_TILE, PLAN_STREAM, PLAN_TILE_DP, PLAN_TILE_SK, PLAN_TILE_PAIR, PLAN_TILE_PAIR_SK = 0, 1, 2, 3, 4, 5, 6
 PLAN_NAMES = {PLAN_AUTO: "auto", PLAN_TILE: "tile", PLAN_STREAM: "stream", PLAN_TILE_DP: "tile_dp",
-              PLAN_TILE_SK: "tile_sk", PLAN_TILE_PAIR: "tile_pair"}
+              PLAN_TILE_SK: "tile_sk", PLAN_TILE_PAIR: "tile_pair", PLAN_TILE_PAIR_SK: "tile_pair_sk"}
 
 EXPORTS = (
     "gu_version", "gu_error_string", "gu_select_plan", "gu_workspace_bytes", "gu_workspace_init",

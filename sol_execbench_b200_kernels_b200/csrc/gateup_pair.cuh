@@ -79,7 +79,7 @@ constexpr int kPairRounds = kTileN / (kPairPiece * kPairInFlight);  // rounds of
 
 enum : unsigned {
   kWaitPairSlot = 11, kWaitPairFull = 12, kWaitPairStageFree = 13, kWaitPairDone = 14,
-  kWaitPairHandEmpty = 15, kWaitPairHandFull = 16,
+  kWaitPairHandEmpty = 15, kWaitPairHandFull = 16, kWaitPairFlag = 17,
 };
 
 // Study builds (never the shipped library; see build.py):
@@ -164,6 +164,72 @@ __device__ __forceinline__ void mbar_wait_lane(WaitCtx& ctx, bool elected, uint3
 // tiles of a K block are then two ADJACENT 128-column blocks of one B matrix (tm_gate; scale rows 2n and 2n+1 of
 // scale_gate), a pair tile is 256 x 256 outputs, and the epilogue warps only issue the stores of the handed-over tiles.
 //
+// kStreamK: the launch's first TileParams::tile_begin tiles (a whole number of rounds) are dealt out round-robin as
+// whole tiles, as without it; the (tile, K block) units of the remaining tiles — between one and two rounds' worth —
+// are cut into one contiguous range per cluster, all ranges equal to within one unit, so that no cluster idles
+// through a last partial round of tiles.  A range starts in the middle of a tile at most once (its first segment) and
+// ends in the middle of one at most once (its last segment).  The cluster that holds a tile's FIRST K blocks owns the
+// tile: the cluster after it, which begins with the tile's remaining K blocks, writes the running sums of that
+// remainder to its slot of a scratch array and stamps its flag with the launch's epoch; the owner, which reaches the
+// tile at the very end of its own range, finds the flag stamped, adds the remainder (ascending block order inside
+// both parts, one fp32 addition joining them) and hands the tile to its epilogue warps as usual.  Only the host picks
+// this schedule, and only when the launch has at least as many tiles as clusters (so a tile spans at most two
+// ranges).  (Cutting ALL units into contiguous ranges was measured too: the clusters then walk different weight
+// blocks at any moment and the launch loses more in L2 misses than it gains: 491 against 441 us on 4096 tokens.)
+// The epoch lives on the device (a count of launches in the scratch area, read by every CTA at its start and
+// advanced by the last CTA to have read it), so a recorded launch can be replayed.
+constexpr int kPairFlagWord0 = 512;        // words [512, 512 + CTAs) of the flag area: hand-off stamps, one per CTA
+constexpr int kPairSyncLaunches = 1020;    // finished launches on this scratch area
+constexpr int kPairSyncTickets = 1021;     // CTAs of the running launch that have left
+constexpr int kPairMaxCtas = 448;          // 1020 - 512, rounded down to a pair count with room to spare
+
+template <bool kStreamK>
+struct PairWalk {
+  long long u, u_end;  // stream-K: this cluster's unit range
+  int cur, step;       // data-parallel: next tile, clusters
+  __device__ __forceinline__ PairWalk(const TileParams& p, int cluster_id, int clusters) {
+    if constexpr (kStreamK) {
+      const long long units = static_cast<long long>(p.num_tiles - p.tile_begin) * p.kb;
+      u = units * cluster_id / clusters;
+      u_end = units * (cluster_id + 1) / clusters;
+      cur = cluster_id;
+      step = clusters;
+    } else {
+      u = u_end = 0;
+      cur = cluster_id;
+      step = clusters;
+    }
+  }
+  // next segment: K blocks [jb, je) of `tile`
+  __device__ __forceinline__ bool next(const TileParams& p, int& tile, int& jb, int& je) {
+    if constexpr (kStreamK) {
+      if (cur < p.tile_begin) {  // the whole rounds first
+        tile = cur;
+        cur += step;
+        jb = 0;
+        je = p.kb;
+        return true;
+      }
+      if (u >= u_end) return false;
+      const int rel = static_cast<int>(u / p.kb);
+      tile = p.tile_begin + rel;
+      jb = static_cast<int>(u - static_cast<long long>(rel) * p.kb);
+      const long long seg_end = min(static_cast<long long>(rel + 1) * p.kb, u_end);
+      je = jb + static_cast<int>(seg_end - u);
+      u = seg_end;
+      return true;
+    } else {
+      if (cur >= p.num_tiles) return false;
+      tile = cur;
+      cur += step;
+      jb = 0;
+      je = p.kb;
+      return true;
+    }
+  }
+};
+
+//
 // kMode selects what the epilogue warps do with a finished tile:
 //   kPairPlain    SwiGLU (or, kSingle, nothing) and the TMA stores into outs[0]
 //   kPairGather   SwiGLU, then the tile is stored into every rank's buffer at this rank's column offset (own and
@@ -195,7 +261,7 @@ __device__ __forceinline__ uint32_t e4m3x4_from_bf16x4(uint32_t p0, uint32_t p1,
   return word;
 }
 
-template <bool kSingle, int kMode = kPairPlain>
+template <bool kSingle, int kMode = kPairPlain, bool kStreamK = false>
 __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tm_x, const CUtensorMap& tm_gate,
                                                  const CUtensorMap& tm_up, const CUtensorMap* outs,
                                                  const TileParams& p) {
@@ -219,6 +285,7 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tm_x, const 
   const uint32_t abort_slot = tmem_slot + 4;
   volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + (tmem_slot - smem_base));
   volatile int* abort_gen = reinterpret_cast<volatile int*>(smem_gen + (abort_slot - smem_base));
+  volatile unsigned int* epoch_gen = reinterpret_cast<volatile unsigned int*>(smem_gen + (abort_slot + 4 - smem_base));
 
   // the warp index through a shuffle, so that the compiler knows it is the same in every lane
   const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
@@ -231,6 +298,22 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tm_x, const 
   const unsigned long long tr_cta0 = clock64();
 #endif
 
+  if constexpr (kStreamK) {
+    if (threadIdx.x == 32) {
+      // This launch's stamp: finished launches on the scratch area + 1, never 0.  The CTA takes its ticket as soon
+      // as it has read the count; the last ticket of the launch advances the count for the next launch (or a replay
+      // of this one) — by then every CTA of this launch holds its stamp, and launches that share a scratch area never
+      // overlap.
+      unsigned int e = ld_acquire_gpu(p.flags + kPairSyncLaunches) + 1u;
+      if (e == 0u) e = 1u;
+      *epoch_gen = e;
+      if (atomicAdd(p.flags + kPairSyncTickets, 1u) == gridDim.x - 1u) {
+        p.flags[kPairSyncTickets] = 0u;
+        __threadfence();
+        atomicAdd(p.flags + kPairSyncLaunches, 1u);
+      }
+    }
+  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < kPairStages; ++s) {
       mbar_init(bar_full + 8 * s, 2);
@@ -274,11 +357,13 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tm_x, const 
 #endif
       const uint32_t full_even = mapa_shared(bar_full, 0);
       uint32_t slots = 0;  // ring slots filled so far: stage = low bits, barrier phase = the next bit
-      for (int tile = cluster_id; tile < p.num_tiles; tile += clusters) {
+      PairWalk<kStreamK> walk(p, cluster_id, clusters);
+      int tile, jb, je;
+      while (walk.next(p, tile, jb, je)) {
         int pm, nb;
         tile_coords(p, tile, pm, nb);
         const int row0 = (2 * pm + static_cast<int>(rank)) * kTileM;
-        for (int j = 0; j < p.kb; ++j, ++slots) {
+        for (int j = jb; j < je; ++j, ++slots) {
           const uint32_t stage = slots % kPairStages, phase = (slots / kPairStages) & 1u;
           GU_TR_BEGIN();
           const bool ok = mbar_wait_elected(ctx, elected, bar_done + 8 * stage, phase ^ 1u, kWaitPairSlot);
@@ -322,11 +407,17 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tm_x, const 
       const uint64_t adesc0 = umma_desc_k_sw128(ring);
       const uint64_t bdesc0 = umma_desc_k_sw128(ring + kOperandTileBytes);
       uint32_t blocks = 0;  // K blocks issued so far
-      for (int tile = cluster_id; tile < p.num_tiles; tile += clusters) {
+      PairWalk<kStreamK> walk(p, cluster_id, clusters);
+      int tile, jb, je;
 #ifdef GU_TRACE
-        const bool tr_first = tile == cluster_id;
+      bool tr_first = true, tr_seen = false;
 #endif
-        for (int j = 0; j < p.kb; ++j, ++blocks) {
+      while (walk.next(p, tile, jb, je)) {
+#ifdef GU_TRACE
+        tr_first = !tr_seen;
+        tr_seen = true;
+#endif
+        for (int j = jb; j < je; ++j, ++blocks) {
           const uint32_t stage = blocks % kPairStages, phase = (blocks / kPairStages) & 1u;
           const uint32_t acc = blocks & 1u, acc_phase = (blocks >> 1) & 1u;
           const uint64_t adesc = adesc0 + stage * (kPairStageBytes >> 4);
@@ -374,7 +465,10 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tm_x, const 
       const int et = static_cast<int>(threadIdx.x) - 32 * kPairEpiWarp0;  // 0 .. kPairEpiThreads-1
       uint8_t* hand_gen = smem_gen + (hand - smem_base);
       uint32_t hand_phase = 0;
-      for (int tile = cluster_id; tile < p.num_tiles; tile += clusters) {
+      PairWalk<kStreamK> walk(p, cluster_id, clusters);
+      int tile, jb, je;
+      while (walk.next(p, tile, jb, je)) {
+        if (jb != 0) continue;  // (stream-K) the remainder of a tile another cluster owns: nothing is handed over
         int pm, nb;
         tile_coords(p, tile, pm, nb);
         const int row0 = (2 * pm + static_cast<int>(rank)) * kTileM;
@@ -524,12 +618,17 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tm_x, const 
     uint32_t blocks_done = 0;  // K blocks walked so far: accumulator stage = bit 0, ring stage = low bits, phases above
     uint32_t hand_phase = 0;
 
-    int tile = cluster_id;
+    PairWalk<kStreamK> walk(p, cluster_id, clusters);
+    int tile = 0, jb = 0, je = 0;
+    bool have = walk.next(p, tile, jb, je);
+    // stream-K: this launch's stamp (never 0) and this CTA's hand-off slot: [256 columns][128 rows] fp32
+    unsigned int epoch = 0;
+    if constexpr (kStreamK) epoch = *epoch_gen;
     // element offsets of this thread's scale rows (the host keeps M * K/128 and N/128 * K/128 below 2^31)
     uint32_t sx_off = 0, sw_off = 0;
     float sx0 = 0.f, sw0 = 0.f;
-    // first K block's scales of a tile (fetched before the previous tile is handed over)
-    auto start_tile = [&](int t) {
+    // first scales of a segment (fetched before the previous tile is handed over)
+    auto start_tile = [&](int t, int j0) {
       int pm, nb;
       tile_coords(p, t, pm, nb);
       const int m_global = min((2 * pm + static_cast<int>(rank)) * kTileM + row, p.m - 1);
@@ -539,14 +638,18 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tm_x, const 
       if (!GU_IN_RANGE(m_global >= 0 && m_global < p.m && wblock >= 0 &&
                            wblock < (kSingle ? p.n_blocks128 : p.num_n_blocks), kSitePairScale))
         return;
-      sx0 = __ldg(p.scale_x + sx_off);
-      sw0 = __ldg(scale_w + sw_off);
+      sx0 = __ldg(p.scale_x + sx_off + j0);
+      sw0 = __ldg(scale_w + sw_off + j0);
     };
-    if (tile < p.num_tiles) start_tile(tile);
-
-    while (tile < p.num_tiles) {
+    if (have) start_tile(tile, jb);
 #ifdef GU_TRACE
-      const bool tr_first = tile == cluster_id;
+    bool tr_first = true, tr_seen = false;
+#endif
+
+    while (have) {
+#ifdef GU_TRACE
+      tr_first = !tr_seen;
+      tr_seen = true;
 #endif
       float2 sums[64];       // this row's 128 running sums of one projection
       // piece buffers: one round (kPairInFlight pieces) is being added while the next round's loads are in flight
@@ -563,10 +666,10 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tm_x, const 
 #ifdef GU_TRACE
       const unsigned long long tr_loop0 = clock64();
 #endif
-      for (int j = 0; j < p.kb; ++j) {
+      for (int j = jb; j < je; ++j) {
         // the next K block's scales are fetched one block ahead of their use
         float sx1 = 0.f, sw1 = 0.f;
-        if (j + 1 < p.kb) {
+        if (j + 1 < je) {
           sx1 = __ldg(p.scale_x + sx_off + j + 1);
           sw1 = __ldg(scale_w + sw_off + j + 1);
         }
@@ -624,13 +727,75 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tm_x, const 
 #ifdef GU_TRACE
       if (tr_me) {
         atomicAdd(&g_trace[blockIdx.x & 1][5], (unsigned long long)(clock64() - tr_loop0));
-        atomicAdd(&g_trace[blockIdx.x & 1][10], (unsigned long long)p.kb);
+        atomicAdd(&g_trace[blockIdx.x & 1][10], (unsigned long long)(je - jb));
       }
 #endif
 
-      // next tile's coordinates and first scales, so their latency hides under the hand-over
-      const int next = tile + clusters;
-      if (next < p.num_tiles) start_tile(next);
+      // next segment's coordinates and first scales, so their latency hides under the hand-over
+      int next_tile = 0, next_jb = 0, next_je = 0;
+      const bool have_next = walk.next(p, next_tile, next_jb, next_je);
+      if (have_next) start_tile(next_tile, next_jb);
+
+      if constexpr (kStreamK) {
+        static_assert(kPairPiece == 16 && kPairInFlight == 2, "the fix-up reads through the four 16-column buffers");
+        const int ct = static_cast<int>(threadIdx.x) - 128;  // 0 .. 255 over the consumer warps
+        if (jb != 0) {
+          // -------- the remainder of a tile the cluster before this one owns: publish the running sums --------
+          float* slot = p.partials + static_cast<size_t>(blockIdx.x) * kTilePartialFloats + proj * (kTileN * kTileM) + row;
+          if (GU_IN_RANGE(blockIdx.x < static_cast<unsigned>(kPairMaxCtas), kSitePairHandOff)) {
+#pragma unroll
+            for (int i = 0; i < 64; ++i) {
+              __stcg(slot + (2 * i) * kTileM, sums[i].x);
+              __stcg(slot + (2 * i + 1) * kTileM, sums[i].y);
+            }
+          }
+          __threadfence();
+          named_bar_sync(3, 256);
+          if (ct == 0 && !ctx.aborted) st_release_gpu(p.flags + kPairFlagWord0 + blockIdx.x, epoch);
+          tile = next_tile; jb = next_jb; je = next_je; have = have_next;
+          continue;
+        }
+        if (je != p.kb) {
+          // -------- owner of a tile whose last K blocks the next cluster walked: add its sums --------
+          const unsigned int peer_cta = blockIdx.x + 2u;  // same rank, next cluster
+          if (ct == 0 && !ctx.aborted) {
+            unsigned long long t0 = 0;
+            for (uint32_t it = 1; ld_acquire_gpu(p.flags + kPairFlagWord0 + peer_cta) != epoch; ++it) {
+              spin_backoff_ns(64u);
+              if ((it & 255u) == 0u) {
+                const unsigned long long now = globaltimer_ns();
+                if (t0 == 0) {
+                  t0 = now;
+                } else if (now - t0 > g_wait_limit_ns || ctx.raised()) {
+                  ctx.fail(kWaitPairFlag, (kWaitPairFlag << 24) | (blockIdx.x & 0xffffffu));
+                  break;
+                }
+              }
+            }
+          }
+          named_bar_sync(3, 256);
+          if (!ctx.raised() && GU_IN_RANGE(peer_cta < gridDim.x, kSitePairHandOff)) {
+            const float* slot = p.partials + static_cast<size_t>(peer_cta) * kTilePartialFloats + proj * (kTileN * kTileM) + row;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {  // 64 columns at a time through the four piece buffers
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                va[i] = __ldcg(slot + (64 * half + i) * kTileM);
+                vb[i] = __ldcg(slot + (64 * half + 16 + i) * kTileM);
+                vc[i] = __ldcg(slot + (64 * half + 32 + i) * kTileM);
+                vd[i] = __ldcg(slot + (64 * half + 48 + i) * kTileM);
+              }
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                sums[32 * half + i].x += va[2 * i];       sums[32 * half + i].y += va[2 * i + 1];
+                sums[32 * half + 8 + i].x += vb[2 * i];   sums[32 * half + 8 + i].y += vb[2 * i + 1];
+                sums[32 * half + 16 + i].x += vc[2 * i];  sums[32 * half + 16 + i].y += vc[2 * i + 1];
+                sums[32 * half + 24 + i].x += vd[2 * i];  sums[32 * half + 24 + i].y += vd[2 * i + 1];
+              }
+            }
+          }
+        }
+      }
 
       // -------- hand-over: this projection's bf16 tile in the output staging layout (two 64-column half tiles of
       // 128-byte rows, 16-byte chunks swizzled by the row) --------
@@ -653,7 +818,7 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tm_x, const 
       if (lane == 0) mbar_arrive(bar_hand_full);
       GU_TR_END(6);
       hand_phase ^= 1u;
-      tile = next;
+      tile = next_tile; jb = next_jb; je = next_je; have = have_next;
     }
   }
 
@@ -681,6 +846,14 @@ gateup_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
                    const __grid_constant__ CUtensorMap tm_up, const __grid_constant__ CUtensorMap tm_out,
                    const TileParams p) {
   pair_kernel_body<false>(tm_x, tm_gate, tm_up, &tm_out, p);
+}
+
+// The same with the stream-K schedule (see PairWalk; needs TileParams::flags / partials).
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
+gateup_pair_sk_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_gate,
+                      const __grid_constant__ CUtensorMap tm_up, const __grid_constant__ CUtensorMap tm_out,
+                      const TileParams p) {
+  pair_kernel_body<false, kPairPlain, true>(tm_x, tm_gate, tm_up, &tm_out, p);
 }
 
 // Gate/up + SwiGLU with the column all-gather fused into the epilogue (see TileParams::out_count).

@@ -105,7 +105,7 @@ struct TileParams {
 // sites of the range-checked debug build (see GU_IN_RANGE)
 enum : unsigned {
   kSiteTileLoad = 1, kSiteTileScale = 2, kSiteTileStage = 3, kSiteTileStore = 4, kSiteTileHandOff = 5, kSiteTileScaleOut = 6,
-  kSitePairLoad = 17, kSitePairScale = 18, kSitePairStage = 19, kSitePairStore = 20, kSitePairScaleOut = 21,
+  kSitePairLoad = 17, kSitePairScale = 18, kSitePairStage = 19, kSitePairStore = 20, kSitePairScaleOut = 21, kSitePairHandOff = 22,
   kSiteStreamLoad = 33, kSiteStreamScale = 34, kSiteStreamStage = 35, kSiteStreamStore = 36, kSiteStreamHandOff = 37,
 };
 

@@ -4,8 +4,9 @@
 stay resident on the GPU, as model parameters do.  The token rows are cut into chunks and three
 streams are kept busy at once: host-to-device copy of chunk i+1, the fused kernel on chunk i,
 device-to-host copy of chunk i-1 (PCIe is full duplex), so the call costs about as much as the
-slowest of the three instead of their sum.  Rows are independent, so chunking changes no bit of the
-result.  PyTorch provides the streams, events and pinned memory; the arithmetic is `run`.
+slowest of the three instead of their sum.  Rows are independent and the kernel is asked for whole tiles
+(no tile cut along K, see `run_with_plan`), so chunking changes no bit of the result of the unsplit
+whole-tile call.  PyTorch provides the streams, events and pinned memory; the arithmetic is `run`.
 """
 from __future__ import annotations
 
@@ -13,7 +14,7 @@ from typing import List
 
 import torch
 
-from .kernel import run
+from .kernel import run_with_plan
 
 
 class HostPipeline:
@@ -63,7 +64,8 @@ class HostPipeline:
                 copied.record(self.s_in)
             with torch.cuda.stream(self.s_run):
                 self.s_run.wait_event(copied)
-                run(self.x[lo:hi], self.scale_x[lo:hi], gate_w, scale_gate, up_w, scale_up, self.out[lo:hi])
+                run_with_plan(self.x[lo:hi], self.scale_x[lo:hi], gate_w, scale_gate, up_w, scale_up, self.out[lo:hi],
+                              "auto", whole_tiles=True)
                 computed = torch.cuda.Event()
                 computed.record(self.s_run)
             with torch.cuda.stream(self.s_out):
@@ -150,8 +152,8 @@ class ShardedHostPipeline:
                 gathered.record(self.s_in)
             with torch.cuda.stream(self.s_run):
                 self.s_run.wait_event(gathered)
-                run(self.x_all[c].view(torch.float8_e4m3fn), self.sx_all[c], gate_shard, scale_gate_shard, up_shard,
-                    scale_up_shard, self.out[c])
+                run_with_plan(self.x_all[c].view(torch.float8_e4m3fn), self.sx_all[c], gate_shard, scale_gate_shard,
+                              up_shard, scale_up_shard, self.out[c], "auto", whole_tiles=True)
                 computed = torch.cuda.Event()
                 computed.record(self.s_run)
             with torch.cuda.stream(self.s_out):

@@ -18,11 +18,12 @@ from typing import Dict, Optional, Tuple
 import torch
 
 from . import _cabi
-from ._cabi import PLAN_AUTO, PLAN_STREAM, PLAN_TILE, PLAN_TILE_DP, PLAN_TILE_PAIR, PLAN_TILE_SK, GuProblem
+from ._cabi import (PLAN_AUTO, PLAN_STREAM, PLAN_TILE, PLAN_TILE_DP, PLAN_TILE_PAIR, PLAN_TILE_PAIR_SK, PLAN_TILE_SK,
+                    GuProblem)
 
 BLOCK = 128
 _PLANS = {"auto": PLAN_AUTO, "tile": PLAN_TILE, "stream": PLAN_STREAM, "tile_dp": PLAN_TILE_DP, "tile_sk": PLAN_TILE_SK,
-          "tile_pair": PLAN_TILE_PAIR}
+          "tile_pair": PLAN_TILE_PAIR, "tile_pair_sk": PLAN_TILE_PAIR_SK}
 
 # Scratch for the stream-K hand-off, one buffer per (device, stream): it is
 # written and consumed inside a single call and carries no result across calls.
@@ -122,12 +123,14 @@ def _workspace(device: torch.device, stream_ptr: int, nbytes: int) -> Optional[t
     return ws
 
 
-def _launch(x, scale_x, gate_w, scale_gate, up_w, scale_up, output, plan: str) -> None:
+def _launch(x, scale_x, gate_w, scale_gate, up_w, scale_up, output, plan: str, whole_tiles: bool = False) -> None:
     m, k, n = _validate(x, scale_x, gate_w, scale_gate, up_w, scale_up, output)
     plan_id = _PLANS[plan]
     with torch.cuda.device(x.device):
         stream_ptr = torch.cuda.current_stream(x.device).cuda_stream
         nbytes = _cabi.lib.gu_workspace_bytes(m, k, n, plan_id)
+        if whole_tiles and (plan_id == PLAN_TILE or (plan_id == PLAN_AUTO and _cabi.lib.gu_select_plan(m, k, n) == PLAN_TILE)):
+            nbytes = 0  # the tile plan without scratch never cuts a tile along K
         ws = _workspace(x.device, stream_ptr, nbytes)
         pr = GuProblem(
             x.data_ptr(), scale_x.data_ptr(), gate_w.data_ptr(), scale_gate.data_ptr(),
@@ -150,12 +153,17 @@ def run(x: torch.Tensor, scale_x: torch.Tensor, gate_proj_weight: torch.Tensor, 
 
 
 @torch.no_grad()
-def run_with_plan(x, scale_x, gate_proj_weight, scale_gate, up_proj_weight, scale_up, output, plan: str) -> None:
-    """`run` with the kernel forced: 'tile' (schedule by heuristic), 'tile_dp' / 'tile_sk' (data-parallel /
-    stream-K schedule), 'stream' or 'auto'; used by the M-sweep study and the tests."""
+def run_with_plan(x, scale_x, gate_proj_weight, scale_gate, up_proj_weight, scale_up, output, plan: str,
+                  whole_tiles: bool = False) -> None:
+    """`run` with the kernel forced: 'auto', 'tile' (kernel and schedule by heuristic), 'tile_pair' / 'tile_pair_sk'
+    (CTA-pair kernel, whole tiles / stream-K schedule), 'tile_dp' / 'tile_sk' (lone-CTA kernel, likewise) or 'stream'.
+
+    `whole_tiles=True` keeps the tile plan from cutting any tile along K (it is given no scratch, and then runs its
+    data-parallel schedule): the bits of an output row then do not depend on how many other rows the call has, so a
+    caller that splits M into chunks gets the result of the unsplit call bit for bit."""
     if plan not in _PLANS:
         raise ValueError(f"unknown plan {plan!r}")
-    _launch(x, scale_x, gate_proj_weight, scale_gate, up_proj_weight, scale_up, output, plan)
+    _launch(x, scale_x, gate_proj_weight, scale_gate, up_proj_weight, scale_up, output, plan, whole_tiles)
 
 
 @torch.no_grad()

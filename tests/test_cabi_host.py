@@ -61,7 +61,12 @@ def test_workspace_sizes(gateup_lib):
     assert lib.gu_workspace_bytes(4096, 4096, 14336, gateup_lib.PLAN_TILE_DP) == 0
     sk = 4096 + 256 * 128 * 256 * 4
     assert lib.gu_workspace_bytes(4096, 4096, 14336, gateup_lib.PLAN_TILE_SK) == sk
-    assert lib.gu_workspace_bytes(512, 4096, 14336, gateup_lib.PLAN_AUTO) == 0        # heuristic keeps data-parallel
+    # 224 pair tiles on 74 clusters are 3.03 rounds: the pair kernel's stream-K schedule is chosen and needs scratch
+    assert lib.gu_workspace_bytes(512, 4096, 14336, gateup_lib.PLAN_AUTO) == sk
+    assert lib.gu_workspace_bytes(512, 4096, 14336, gateup_lib.PLAN_TILE_PAIR_SK) == sk
+    assert lib.gu_workspace_bytes(512, 4096, 14336, gateup_lib.PLAN_TILE_PAIR) == 0
+    assert lib.gu_workspace_bytes(256, 4096, 14336, gateup_lib.PLAN_AUTO) == 0        # 1.51 rounds: whole tiles
+    assert lib.gu_workspace_bytes(512, 4096, 9472, gateup_lib.PLAN_AUTO) == 0         # two rounds exactly
     assert lib.gu_workspace_bytes(128, 4096, 14336, gateup_lib.PLAN_TILE_SK) == sk
     w16 = lib.gu_workspace_bytes(16, 8192, 28672, gateup_lib.PLAN_AUTO)
     w64 = lib.gu_workspace_bytes(64, 8192, 28672, gateup_lib.PLAN_STREAM)

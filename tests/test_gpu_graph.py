@@ -1,6 +1,6 @@
 """A launch recorded in a CUDA graph must stay correct when it is replayed: the tile kernel keeps no state between
-launches, and the weight-streaming kernel takes the epoch of its hand-off flags from a counter in its workspace, not
-from the host.  Each replay runs on new activations written into the captured buffers."""
+launches, and the weight-streaming kernel and the pair kernel's stream-K schedule (the last shape) take the epoch of
+their hand-off flags from a counter in the workspace, not from the host.  Each replay runs on new activations written into the captured buffers."""
 import pytest
 import torch
 
@@ -9,7 +9,8 @@ from sol_execbench_b200_kernels_b200 import workloads as W
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("shape", [(16, 4096, 8192), (8, 8192, 28672), (32, 8192, 28672), (256, 1024, 2048)])
+@pytest.mark.parametrize("shape", [(16, 4096, 8192), (8, 8192, 28672), (32, 8192, 28672), (256, 1024, 2048),
+                                   (512, 384, 4864)])
 def test_replayed_graph_equals_eager_calls(shape):
     import sol_execbench_b200_kernels_b200 as pkg
 

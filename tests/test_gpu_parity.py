@@ -104,6 +104,39 @@ def test_tile_kernel_stream_k_schedule_parity(pkg, shape):
     assert st["rel_l2"] <= 1e-4, st
 
 
+PAIR_SK_SHAPES = [(512, 256, 4736), (512, 384, 4864), (700, 512, 3840), (1024, 256, 2560), (300, 1024, 5120),
+                  (1100, 128, 2432)]
+
+
+@pytest.mark.parametrize("shape", PAIR_SK_SHAPES)
+def test_pair_kernel_stream_k_schedule_parity(pkg, shape):
+    # the pair kernel with the (tile, K block) units cut into one equal range per cluster: a tile cut in two has its
+    # two partial sums joined by one extra fp32 addition, so single bf16 roundings may differ from the whole-tile
+    # schedule; the heuristic plan picks this schedule for these shapes when it is given scratch
+    inp = W.make_inputs(*shape, seed=1)
+    out = _run(pkg, inp, "tile_pair_sk")
+    _check(out, inp, f"tile_pair_sk {shape}")
+    whole = _run(pkg, inp, "tile_pair")
+    st = O.error_stats(out, whole)
+    assert st["rel_l2"] <= 1e-4, st
+    assert float((out != whole).float().mean()) <= 2e-3
+    assert torch.equal(_run(pkg, inp, "tile_pair_sk"), out)
+    auto = _run(pkg, inp, "tile")
+    assert torch.equal(auto, out) or torch.equal(auto, whole)
+    # asked for whole tiles, the heuristic plan gives the whole-tile bits whatever it would have picked
+    g = inp.to("cuda:0")
+    kept = torch.empty_like(whole)
+    pkg.run_with_plan(*g.args(), kept, "auto", whole_tiles=True)
+    torch.cuda.synchronize()
+    assert torch.equal(kept, whole)
+
+
+def test_pair_kernel_stream_k_needs_a_tile_per_cluster(pkg):
+    inp = W.make_inputs(256, 128, 128, seed=1)
+    with pytest.raises(ValueError, match="plan"):
+        _run(pkg, inp, "tile_pair_sk")
+
+
 @pytest.mark.parametrize("shape", STREAM_SHAPES)
 def test_stream_kernel_parity(pkg, shape):
     inp = W.make_inputs(*shape, seed=2)
@@ -137,6 +170,7 @@ def test_small_config_through_public_run(pkg):
 def test_deterministic(pkg):
     for shape, plan in (((300, 512, 384), "tile_dp"), ((300, 512, 384), "tile_pair"), ((1024, 1024, 1024), "tile"),
                         ((300, 512, 384), "tile_sk"), ((128, 4096, 2048), "tile_sk"),
+                        ((512, 384, 4864), "tile_pair_sk"), ((700, 512, 3840), "tile"),
                         ((16, 8192, 2048), "stream"), ((7, 2048, 5632), "stream")):
         inp = W.make_inputs(*shape, seed=4)
         a = _run(pkg, inp, plan).clone()
