@@ -114,7 +114,7 @@ int gu_workspace_init(void* workspace, size_t bytes, void* stream);
  * from a host counter and must not be replayed.
  * GU_PLAN_TILE above 128 tokens picks the pair kernel's stream-K schedule when a
  * workspace of gu_workspace_bytes() is passed, there are at least two rounds of
- * tiles and whole tiles would leave 4 % or more of the device idle in the last; the sums of a tile cut in two are
+ * tiles and whole tiles would leave 10 % or more of the device idle in the last; the sums of a tile cut in two are
  * joined by one extra fp32 addition, so its outputs may differ from the
  * data-parallel schedule's in the last bf16 digit.  Without a workspace the
  * data-parallel schedule runs.

@@ -344,16 +344,16 @@ int launch_tile(const gu_problem* pr, const DeviceInfo& dev, cudaStream_t stream
 // CTA-pair kernel: 256-token x 128-column tiles, one per two-CTA cluster.
 // Stream-K schedule of the pair kernel (whole rounds as whole tiles, the last whole round plus the remainder cut into
 // equal unit ranges).  Possible when no tile spans more than two ranges (at least as many tiles as clusters).  Its
-// hand-off (one 128 KiB publish and one 128 KiB fix-up per CTA) costs 5 - 8 us per launch, measured on B200 at
-// K=4096, N=14336 against whole tiles: 512 tokens (3.03 rounds) 74.8 against 81.8 us, 1024 (6.05) 124.8 against 133.2,
-// 2048 (12.1) 230.3 against 235.6, 4096 (24.2) 439.7 against 445.9; 256 tokens (1.51 rounds, no whole round before
-// the cut) 53.4 against 49.3, and 2 us lost where the tiles divide evenly.  So the heuristic wants two rounds or more
-// and at least 4 % of the device idle in the last round of whole tiles.
+// hand-off (one 128 KiB publish and one 128 KiB fix-up per CTA, and a K block more on the critical path) costs about
+// 6 us per launch, measured on B200 at K=4096, N=14336 against whole tiles: 512 tokens (3.03 rounds) 72.4 against
+// 79.7 us, 1024 (6.05) 122.8 against 129.1, 2048 (12.1) 229.6 against 231.7, 4096 (24.2) 443.9 against 440.3; 256
+// tokens (1.51 rounds, no whole round before the cut) 52.1 against 49.8, and 1 us lost where the tiles divide evenly.
+// So the heuristic wants two rounds or more and at least 10 % of the device idle in the last round of whole tiles.
 bool pair_can_stream_k(int tiles, int clusters) { return clusters >= 2 && tiles >= clusters && 2 * clusters <= kPairMaxCtas; }
 bool pair_prefers_stream_k(int tiles, int clusters) {
   if (!pair_can_stream_k(tiles, clusters) || tiles < 2 * clusters || tiles % clusters == 0) return false;
   const int rounds = (tiles + clusters - 1) / clusters;
-  return double(tiles) / (double(rounds) * clusters) < 0.96;
+  return double(tiles) / (double(rounds) * clusters) < 0.90;
 }
 
 int launch_pair(const gu_problem* pr, const DeviceInfo& dev, cudaStream_t stream, int stream_k /* 0 no, 1 yes, -1 by the heuristic */) {

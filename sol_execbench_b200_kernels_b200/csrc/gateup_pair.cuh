@@ -298,22 +298,6 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tm_x, const 
   const unsigned long long tr_cta0 = clock64();
 #endif
 
-  if constexpr (kStreamK) {
-    if (threadIdx.x == 32) {
-      // This launch's stamp: finished launches on the scratch area + 1, never 0.  The CTA takes its ticket as soon
-      // as it has read the count; the last ticket of the launch advances the count for the next launch (or a replay
-      // of this one) — by then every CTA of this launch holds its stamp, and launches that share a scratch area never
-      // overlap.
-      unsigned int e = ld_acquire_gpu(p.flags + kPairSyncLaunches) + 1u;
-      if (e == 0u) e = 1u;
-      *epoch_gen = e;
-      if (atomicAdd(p.flags + kPairSyncTickets, 1u) == gridDim.x - 1u) {
-        p.flags[kPairSyncTickets] = 0u;
-        __threadfence();
-        atomicAdd(p.flags + kPairSyncLaunches, 1u);
-      }
-    }
-  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < kPairStages; ++s) {
       mbar_init(bar_full + 8 * s, 2);
@@ -323,6 +307,7 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tm_x, const 
     mbar_init(bar_hand_full, 8);
     mbar_init(bar_hand_empty, 1);
     *abort_gen = 0;
+    *epoch_gen = 0u;
     fence_mbar_init();
     fence_proxy_async_smem();
     tma_prefetch_desc(&tm_x);
@@ -465,6 +450,23 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tm_x, const 
       const int et = static_cast<int>(threadIdx.x) - 32 * kPairEpiWarp0;  // 0 .. kPairEpiThreads-1
       uint8_t* hand_gen = smem_gen + (hand - smem_base);
       uint32_t hand_phase = 0;
+      if constexpr (kStreamK) {
+        if (et == 0) {
+          // This launch's stamp: launches counted on the scratch area + 1, never 0 (done here, off the other roles'
+          // way: they need it a tile part later at the earliest).  The CTA takes its ticket as soon as it has read
+          // the count; the last ticket of the launch advances the count for the next launch (or a replay of this
+          // one) — by then every CTA of this launch holds its stamp, and launches that share a scratch area never
+          // overlap.
+          unsigned int e = ld_acquire_gpu(p.flags + kPairSyncLaunches) + 1u;
+          if (e == 0u) e = 1u;
+          *epoch_gen = e;
+          if (atomicAdd(p.flags + kPairSyncTickets, 1u) == gridDim.x - 1u) {
+            p.flags[kPairSyncTickets] = 0u;
+            __threadfence();
+            atomicAdd(p.flags + kPairSyncLaunches, 1u);
+          }
+        }
+      }
       PairWalk<kStreamK> walk(p, cluster_id, clusters);
       int tile, jb, je;
       while (walk.next(p, tile, jb, je)) {
@@ -623,7 +625,17 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tm_x, const 
     bool have = walk.next(p, tile, jb, je);
     // stream-K: this launch's stamp (never 0) and this CTA's hand-off slot: [256 columns][128 rows] fp32
     unsigned int epoch = 0;
-    if constexpr (kStreamK) epoch = *epoch_gen;
+    // (stream-K) consumer thread 0 fetches the stamp the first epilogue thread left in shared memory
+    auto fetch_epoch = [&]() {
+      const unsigned long long t0 = globaltimer_ns();
+      while ((epoch = *epoch_gen) == 0u) {
+        spin_backoff_ns(64u);
+        if (globaltimer_ns() - t0 > g_wait_limit_ns) {
+          ctx.fail(kWaitPairFlag, (kWaitPairFlag << 24) | (blockIdx.x & 0xffffffu));
+          break;
+        }
+      }
+    };
     // element offsets of this thread's scale rows (the host keeps M * K/128 and N/128 * K/128 below 2^31)
     uint32_t sx_off = 0, sw_off = 0;
     float sx0 = 0.f, sw0 = 0.f;
@@ -737,27 +749,29 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tm_x, const 
       if (have_next) start_tile(next_tile, next_jb);
 
       if constexpr (kStreamK) {
-        static_assert(kPairPiece == 16 && kPairInFlight == 2, "the fix-up reads through the four 16-column buffers");
         const int ct = static_cast<int>(threadIdx.x) - 128;  // 0 .. 255 over the consumer warps
         if (jb != 0) {
           // -------- the remainder of a tile the cluster before this one owns: publish the running sums --------
-          float* slot = p.partials + static_cast<size_t>(blockIdx.x) * kTilePartialFloats + proj * (kTileN * kTileM) + row;
+          // slot of this CTA: [32][256 consumer threads] float4, values 4i .. 4i+3 of thread t at [i * 256 + t]
+          float4* slot = reinterpret_cast<float4*>(p.partials + static_cast<size_t>(blockIdx.x) * kTilePartialFloats) + ct;
           if (GU_IN_RANGE(blockIdx.x < static_cast<unsigned>(kPairMaxCtas), kSitePairHandOff)) {
 #pragma unroll
-            for (int i = 0; i < 64; ++i) {
-              __stcg(slot + (2 * i) * kTileM, sums[i].x);
-              __stcg(slot + (2 * i + 1) * kTileM, sums[i].y);
-            }
+            for (int i = 0; i < 32; ++i)
+              __stcg(slot + i * 256, make_float4(sums[2 * i].x, sums[2 * i].y, sums[2 * i + 1].x, sums[2 * i + 1].y));
           }
           __threadfence();
           named_bar_sync(3, 256);
-          if (ct == 0 && !ctx.aborted) st_release_gpu(p.flags + kPairFlagWord0 + blockIdx.x, epoch);
+          if (ct == 0) {
+            if (epoch == 0u) fetch_epoch();
+            if (!ctx.aborted) st_release_gpu(p.flags + kPairFlagWord0 + blockIdx.x, epoch);
+          }
           tile = next_tile; jb = next_jb; je = next_je; have = have_next;
           continue;
         }
         if (je != p.kb) {
           // -------- owner of a tile whose last K blocks the next cluster walked: add its sums --------
           const unsigned int peer_cta = blockIdx.x + 2u;  // same rank, next cluster
+          if (ct == 0 && epoch == 0u) fetch_epoch();
           if (ct == 0 && !ctx.aborted) {
             unsigned long long t0 = 0;
             for (uint32_t it = 1; ld_acquire_gpu(p.flags + kPairFlagWord0 + peer_cta) != epoch; ++it) {
@@ -775,22 +789,20 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tm_x, const 
           }
           named_bar_sync(3, 256);
           if (!ctx.raised() && GU_IN_RANGE(peer_cta < gridDim.x, kSitePairHandOff)) {
-            const float* slot = p.partials + static_cast<size_t>(peer_cta) * kTilePartialFloats + proj * (kTileN * kTileM) + row;
+            const float4* slot =
+                reinterpret_cast<const float4*>(p.partials + static_cast<size_t>(peer_cta) * kTilePartialFloats) + ct;
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {  // 64 columns at a time through the four piece buffers
+            for (int half = 0; half < 2; ++half) {  // 16 loads of 16 bytes in flight (the piece buffers are free here)
+              float4 buf[16];
+#pragma unroll
+              for (int i = 0; i < 16; ++i) buf[i] = __ldcg(slot + (16 * half + i) * 256);
 #pragma unroll
               for (int i = 0; i < 16; ++i) {
-                va[i] = __ldcg(slot + (64 * half + i) * kTileM);
-                vb[i] = __ldcg(slot + (64 * half + 16 + i) * kTileM);
-                vc[i] = __ldcg(slot + (64 * half + 32 + i) * kTileM);
-                vd[i] = __ldcg(slot + (64 * half + 48 + i) * kTileM);
-              }
-#pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                sums[32 * half + i].x += va[2 * i];       sums[32 * half + i].y += va[2 * i + 1];
-                sums[32 * half + 8 + i].x += vb[2 * i];   sums[32 * half + 8 + i].y += vb[2 * i + 1];
-                sums[32 * half + 16 + i].x += vc[2 * i];  sums[32 * half + 16 + i].y += vc[2 * i + 1];
-                sums[32 * half + 24 + i].x += vd[2 * i];  sums[32 * half + 24 + i].y += vd[2 * i + 1];
+                const float4 v = buf[i];
+                sums[2 * (16 * half + i)].x += v.x;
+                sums[2 * (16 * half + i)].y += v.y;
+                sums[2 * (16 * half + i) + 1].x += v.z;
+                sums[2 * (16 * half + i) + 1].y += v.w;
               }
             }
           }
