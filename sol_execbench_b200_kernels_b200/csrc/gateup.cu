@@ -344,11 +344,12 @@ int launch_tile(const gu_problem* pr, const DeviceInfo& dev, cudaStream_t stream
 // CTA-pair kernel: 256-token x 128-column tiles, one per two-CTA cluster.
 // Stream-K schedule of the pair kernel (whole rounds as whole tiles, the last whole round plus the remainder cut into
 // equal unit ranges).  Possible when no tile spans more than two ranges (at least as many tiles as clusters).  Its
-// hand-off (one 128 KiB publish and one 128 KiB fix-up per CTA, and a K block more on the critical path) costs about
-// 6 us per launch, measured on B200 at K=4096, N=14336 against whole tiles: 512 tokens (3.03 rounds) 72.4 against
-// 79.7 us, 1024 (6.05) 122.8 against 129.1, 2048 (12.1) 229.6 against 231.7, 4096 (24.2) 443.9 against 440.3; 256
-// tokens (1.51 rounds, no whole round before the cut) 52.1 against 49.8, and 1 us lost where the tiles divide evenly.
-// So the heuristic wants two rounds or more and at least 10 % of the device idle in the last round of whole tiles.
+// hand-off (one 128 KiB publish and one 128 KiB fix-up per CTA, a K block more on the critical path, and the last
+// tile's SwiGLU on two warps only) costs about 8 us per launch, measured on B200 at K=4096, N=14336 against whole
+// tiles: 512 tokens (3.03 rounds) 73.8 against 77.8 us, 1024 (6.05) 123.7 against 127.3, 2048 (12.1) 229.4 against
+// 231.5, 4096 (24.2) within the noise; 256 tokens (1.51 rounds, no whole round before the cut) 55.2 against 47.1, and
+// 2 - 4 us lost where the tiles divide evenly.  So the heuristic wants two rounds or more and at least 10 % of the
+// device idle in the last round of whole tiles.
 bool pair_can_stream_k(int tiles, int clusters) { return clusters >= 2 && tiles >= clusters && 2 * clusters <= kPairMaxCtas; }
 bool pair_prefers_stream_k(int tiles, int clusters) {
   if (!pair_can_stream_k(tiles, clusters) || tiles < 2 * clusters || tiles % clusters == 0) return false;

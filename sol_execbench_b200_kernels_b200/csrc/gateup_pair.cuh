@@ -200,6 +200,11 @@ struct PairWalk {
       step = clusters;
     }
   }
+  // no segment is left
+  __device__ __forceinline__ bool done(const TileParams& p) const {
+    if constexpr (kStreamK) return cur >= p.tile_begin && u >= u_end;
+    else return cur >= p.num_tiles;
+  }
   // next segment: K blocks [jb, je) of `tile`
   __device__ __forceinline__ bool next(const TileParams& p, int& tile, int& jb, int& je) {
     if constexpr (kStreamK) {
@@ -261,10 +266,37 @@ __device__ __forceinline__ uint32_t e4m3x4_from_bf16x4(uint32_t p0, uint32_t p1,
   return word;
 }
 
+// SiLU(gate) * up with the three roundings, in place over the handed-over tiles: 16-byte chunk q of the gate tile
+// meets chunk q of the up tile (same layout); chunks first, first + stride, ... of the 2048 belong to this thread
+__device__ __forceinline__ void pair_swiglu_chunks(uint8_t* hand_gen, int first, int stride) {
+#pragma unroll 4
+  for (int q = first; q < 2048; q += stride) {
+    uint4* gq = reinterpret_cast<uint4*>(hand_gen + q * 16);
+    const uint4 a = *gq;
+    const uint4 b = *reinterpret_cast<const uint4*>(hand_gen + 2 * kTileOutHalfBytes + q * 16);
+    uint4 o;
+    o.x = swiglu_packed_bf16x2(a.x, b.x);
+    o.y = swiglu_packed_bf16x2(a.y, b.y);
+    o.z = swiglu_packed_bf16x2(a.z, b.z);
+    o.w = swiglu_packed_bf16x2(a.w, b.w);
+    *gq = o;
+  }
+}
+// The SwiGLU of a cluster's LAST tile has nothing to hide behind (4 - 5 us on two warps: two special-function
+// operations per output), so the eight consumer warps, idle by then, share it with the epilogue warps: 2 us per
+// launch.  (Not in the stream-K kernel: with this code in it the same K loop measured 165 cycles per block slower,
+// 78.0 against 75.8 us at 512 x 4096 x 14336, for a reason that -Xptxas -v does not show.)
+constexpr int kPairAllHands = kPairEpiThreads + 256;
+
 template <bool kSingle, int kMode = kPairPlain, bool kStreamK = false>
 __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tm_x, const CUtensorMap& tm_gate,
                                                  const CUtensorMap& tm_up, const CUtensorMap* outs,
                                                  const TileParams& p) {
+#ifdef GU_NO_SHARED_EPILOGUE  // study build: the last tile's SwiGLU stays on the epilogue warps
+  constexpr bool kShareLast = false;
+#else
+  constexpr bool kShareLast = !kSingle && kMode != kPairFp8Out && !kStreamK;
+#endif
   static_assert(kMode != kPairScatter || kSingle, "scatter is a mode of the plain GEMM");
   static_assert((kMode != kPairGather && kMode != kPairFp8Out) || !kSingle, "gather / fp8 output are modes of gate/up");
   extern __shared__ uint8_t smem_raw[];
@@ -471,6 +503,8 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tm_x, const 
       int tile, jb, je;
       while (walk.next(p, tile, jb, je)) {
         if (jb != 0) continue;  // (stream-K) the remainder of a tile another cluster owns: nothing is handed over
+        // (a cluster's last segment is always the head or the whole of a tile it owns)
+        const bool last_tile = kShareLast && walk.done(p);
         int pm, nb;
         tile_coords(p, tile, pm, nb);
         const int row0 = (2 * pm + static_cast<int>(rank)) * kTileM;
@@ -559,21 +593,15 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tm_x, const 
             mbar_arrive(bar_hand_empty);
           }
         } else {
-        // gate and up tiles have the same layout, so chunk q of one meets chunk q of the other whatever it holds
-#pragma unroll 4
-        for (int i = 0; i < 2048 / kPairEpiThreads; ++i) {
-          uint4* gq = reinterpret_cast<uint4*>(hand_gen + (et + kPairEpiThreads * i) * 16);
-          const uint4 a = *gq;
-          const uint4 b = *reinterpret_cast<const uint4*>(hand_gen + 2 * kTileOutHalfBytes + (et + kPairEpiThreads * i) * 16);
-          uint4 o;
-          o.x = swiglu_packed_bf16x2(a.x, b.x);
-          o.y = swiglu_packed_bf16x2(a.y, b.y);
-          o.z = swiglu_packed_bf16x2(a.z, b.z);
-          o.w = swiglu_packed_bf16x2(a.w, b.w);
-          *gq = o;
+        if (last_tile) {
+          pair_swiglu_chunks(hand_gen, et, kPairAllHands);  // shared with the consumer warps
+          fence_proxy_async_smem();
+          named_bar_sync(4, kPairAllHands);
+        } else {
+          pair_swiglu_chunks(hand_gen, et, kPairEpiThreads);
+          fence_proxy_async_smem();
+          named_bar_sync(1, kPairEpiThreads);
         }
-        fence_proxy_async_smem();
-        named_bar_sync(1, kPairEpiThreads);
         if (et == 0) {
           if (ok && !ctx.aborted && row0 < p.m &&
               GU_IN_RANGE(p.out_cols == 0 || (nb * kTileN + 128 <= p.out_cols && row0 >= 0 && row0 < p.out_rows),
@@ -829,6 +857,22 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tm_x, const 
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_hand_full);
       GU_TR_END(6);
+      if constexpr (kShareLast) {
+        if (!have_next) {
+          // this cluster's last tile: once all eight warps' halves are in, share its SwiGLU with the epilogue warps
+          GU_TR_BEGIN();
+          mbar_wait_lane(ctx, lane == 0, bar_hand_full, hand_phase, kWaitPairHandFull);
+          GU_TR_END(11);
+          GU_TR_BEGIN();
+          pair_swiglu_chunks(smem_gen + (hand - smem_base), kPairEpiThreads + static_cast<int>(threadIdx.x) - 128,
+                             kPairAllHands);
+          fence_proxy_async_smem();
+          GU_TR_END(12);
+          GU_TR_BEGIN();
+          named_bar_sync(4, kPairAllHands);
+          GU_TR_END(13);
+        }
+      }
       hand_phase ^= 1u;
       tile = next_tile; jb = next_jb; je = next_je; have = have_next;
     }
