@@ -379,7 +379,7 @@ def run_ours(args):
         # every rank holds only its row block of the activations in host memory; the blocks are exchanged over NVLink
         from sol_execbench_b200_kernels_b200.host_pipeline import ShardedHostPipeline
 
-        pipe = ShardedHostPipeline(m, k, n_local, dev, chunks=max(1, args.e2e_chunks // 2))
+        pipe = ShardedHostPipeline(m, k, n_local, dev, chunks=max(1, args.e2e_chunks))
         lo, hi = rank * pipe.block_rows, (rank + 1) * pipe.block_rows
         x_host = local.x[lo:hi].cpu().view(torch.uint8).pin_memory().view(torch.float8_e4m3fn)
         sx_host = local.scale_x[lo:hi].cpu().pin_memory()
@@ -419,11 +419,11 @@ def run_ours(args):
                     "note": "ceiling = the metric if a step took only the slower of its host copies (or the kernel)"},
            "note": ("HostPipeline.run: weights resident in HBM; x and scale_x copied from pinned host memory and the "
                     f"bf16 output copied back to pinned host memory every step, in {len(pipe.bounds)} row chunks on three "
-                    "streams; wall clock") if n_gpus == 1 else
+                    "streams, consecutive steps overlapping chunk by chunk; wall clock over all steps") if n_gpus == 1 else
                    ("ShardedHostPipeline.run: every rank copies its M/R row block of x and scale_x from pinned host "
                     "memory, the blocks are exchanged over NVLink (NCCL all-gather), every rank copies its [M, N/R] slice "
-                    f"of the bf16 output back to pinned host memory, in {len(pipe.bounds)} row chunks on three streams; "
-                    "bytes are per rank; wall clock, max over ranks")}
+                    f"of the bf16 output back to pinned host memory, in {len(pipe.bounds)} row chunks on three streams, "
+                    "consecutive steps overlapping chunk by chunk; bytes are per rank; wall clock over all steps, max over ranks")}
     if n_gpus > 1:
         e2e["nvlink_bytes_in_per_step"] = pipe.bytes_nvlink_in
 
@@ -939,7 +939,9 @@ def main():
     ap.add_argument("--gather", action="store_true", help="N>1: also all-gather the contiguous [M, N] output")
     ap.add_argument("--fused-gather", action="store_true",
                     help="N>1: contiguous [M, N] output on every rank through peer stores in the kernel epilogue")
-    ap.add_argument("--e2e-chunks", type=int, default=8, help="row chunks of the host-memory pipeline in the e2e leg")
+    ap.add_argument("--e2e-chunks", type=int, default=4,
+                    help="row chunks of the host-memory pipeline in the e2e leg (measured on prefill_8b: 2 chunks 2.31 ms, "
+                         "4 2.13, 8 2.21, 16 2.22 per step)")
     ap.add_argument("--mlp", action="store_true",
                     help="N>1: tensor-parallel MLP block, NCCL all-reduce against the fused peer-store reduction")
     ap.add_argument("--graph", action="store_true",

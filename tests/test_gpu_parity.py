@@ -390,6 +390,18 @@ def test_host_pipeline_matches_device_run(pkg):
         pipe.run(x_host, sx_host, g.gate_proj_weight, g.scale_gate, g.up_proj_weight, g.scale_up, out_host)
         pipe.synchronize()
         assert torch.equal(out_host, ref)
+    # calls in a row overlap on the device; each must still see its own input and deliver its own result
+    inp2 = W.make_inputs(m, k, n, seed=15)
+    ref2 = _run(pkg, W.GateUpInputs(inp2.x, inp2.scale_x, inp.gate_proj_weight, inp.scale_gate, inp.up_proj_weight,
+                                    inp.scale_up), "auto").cpu()
+    x2_host = inp2.x.view(torch.uint8).pin_memory().view(torch.float8_e4m3fn)
+    sx2_host = inp2.scale_x.pin_memory()
+    out2_host = torch.zeros(m, n, dtype=torch.bfloat16).pin_memory()
+    for _ in range(3):
+        pipe.run(x_host, sx_host, g.gate_proj_weight, g.scale_gate, g.up_proj_weight, g.scale_up, out_host)
+        pipe.run(x2_host, sx2_host, g.gate_proj_weight, g.scale_gate, g.up_proj_weight, g.scale_up, out2_host)
+    pipe.synchronize()
+    assert torch.equal(out_host, ref) and torch.equal(out2_host, ref2)
     with pytest.raises(ValueError, match="pinned"):
         pipe.run(inp.x, sx_host, g.gate_proj_weight, g.scale_gate, g.up_proj_weight, g.scale_up, out_host)
 
