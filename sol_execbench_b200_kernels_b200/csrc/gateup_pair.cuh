@@ -91,6 +91,8 @@ enum : unsigned {
 //                4 as 2, and the issuer never waits for the consumers: MMA + TMA + issuer alone
 //                5 as 3 and 4 together: one K block in flight on an otherwise idle SM
 //                6 consumers do the promotion arithmetic on stale registers but never read TMEM
+//                7 consumers read only 64 of their 128 columns (two rounds of loads) before the stage goes back, all
+//                  the arithmetic still done; 8 as 7 with the arithmetic of those 64 columns only
 //   -DGU_PAIR_THREADS=512, -DGU_PIECE=32, -DGU_INFLIGHT=1, -DGU_PAIR_STAGES=5   layout variants that were measured
 #ifdef GU_TRACE
 // Cycle counters of cluster 0 (both CTAs), summed over the launch: [rank][slot]
@@ -730,6 +732,29 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tm_x, const 
         tc_fence_after();
         pair_ld(t, va);
         if constexpr (kPairInFlight == 2) pair_ld(t + kPairPiece, vb);
+#if defined(GU_EXP) && (GU_EXP == 7 || GU_EXP == 8)
+        // experiments: only 64 of the 128 columns are read (two rounds of loads instead of four) before the stage goes
+        // back; 7 still does the arithmetic of all 128 columns (on stale registers), 8 only that of the 64
+        tmem_ld_wait_pin<kPairPiece>(va);
+        tmem_ld_wait_pin<kPairPiece>(vb);
+        pair_ld(t + 2 * kPairPiece, vc);
+        pair_ld(t + 3 * kPairPiece, vd);
+        pair_fma(sums, va, scv);
+        pair_fma(sums + 8, vb, scv);
+        tmem_ld_wait_pin<kPairPiece>(vc);
+        tmem_ld_wait_pin<kPairPiece>(vd);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(stage_free_even + 8 * acc);
+        pair_fma(sums + 16, vc, scv);
+        pair_fma(sums + 24, vd, scv);
+#if GU_EXP == 7
+        pair_fma(sums + 32, va, scv);
+        pair_fma(sums + 40, vb, scv);
+        pair_fma(sums + 48, vc, scv);
+        pair_fma(sums + 56, vd, scv);
+#endif
+#else
 #pragma unroll
         for (int q = 0; q < kPairRounds; ++q) {
           // buffers of this round and of the next (one or two pieces each)
@@ -759,6 +784,7 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tm_x, const 
             if constexpr (kPairInFlight == 2) pair_fma(sums + ((q - 1) * 2 + 1) * (kPairPiece / 2), n1, scv);
           }
         }
+#endif
 
         ++blocks_done;
         sx0 = sx1;
