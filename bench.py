@@ -547,6 +547,52 @@ def run_ours(args):
             "tflops": round(bfl / (bms / gsteps * 1e-3) / 1e12, 2)})
         del blk, dq, dsc, mid_q, mid_s, yout, xb
         torch.cuda.empty_cache()
+        # an awkward tile count: 512 tokens are 3.03 rounds of tiles (the tile plan's stream-K schedule runs here)
+        wm, wk, wn = 512, W.SWEEP_KN[0], W.SWEEP_KN[1]
+        wav = W.make_inputs(wm, wk, wn, seed=0, device=dev)
+        wout = torch.empty(wm, wn, dtype=torch.bfloat16, device=dev)
+        wsteps = 20
+        wrow = {}
+        for plan in ("tile", "tile_pair"):
+            wms, _ = time_device_steps(lambda: pkg.run_with_plan(*wav.args(), wout, plan), wsteps, 3, flush)
+            wrow[plan] = wms / wsteps
+        result["also"].append({
+            "workload": f"sweep row M={wm} K={wk} N={wn}", "plan": "tile (heuristic schedule)",
+            "ms_per_step": round(wrow["tile"], 5), "steps": wsteps, "whole_tiles_ms_per_step": round(wrow["tile_pair"], 5),
+            "tflops": round(W.algorithmic_flops(wm, wk, wn) / (wrow["tile"] * 1e-3) / 1e12, 2),
+            "roofline": roofline_for(wm, wk, wn, wrow["tile"], peaks, W)})
+        del wav, wout
+        # the repository's other operators (problems 038 and 029) behind the second C ABI, one shape each
+        from sol_execbench_b200_kernels_b200 import side_ops
+        side = {}
+        q_, k_, wq_, wk_, eps_ = W.make_rmsnorm_inputs(*W.RMSNORM_SHAPES["flux_4608"], 0, dev)
+        qn_, kn_ = torch.empty_like(q_), torch.empty_like(k_)
+        sms, _ = time_device_steps(lambda: side_ops.rmsnorm_qk(q_, k_, wq_, wk_, eps_, qn_, kn_), 10, 3, flush)
+        nb_ = 4 * q_.numel() * 4
+        side["rmsnorm_qk flux_4608"] = {"us": round(sms / 10 * 1e3, 2), "bound": "hbm",
+                                        "frac": round(nb_ / (sms / 10) / 1e6 / peaks["hbm_gbs"], 4)}
+        del q_, k_, qn_, kn_
+        pb, pl, pc, pw = W.MAMBA_TAIL_SHAPES["mamba_b1_l2048"]
+        pp, pmask, pcw, pcb = W.make_mamba_tail_inputs(pb, pl, pc, pw, 0, dev)
+        pout = torch.empty(pb, pc, pl, dtype=torch.bfloat16, device=dev)
+        sms, _ = time_device_steps(lambda: side_ops.mamba_conv1d_tail(pp, pmask, pcw, pcb, pout), 10, 3, flush)
+        side["mamba_conv1d_tail b1_l2048"] = {"us": round(sms / 10 * 1e3, 2), "bound": "hbm",
+                                              "frac": round(2 * pb * pl * pc * 2 / (sms / 10) / 1e6 / peaks["hbm_gbs"], 4)}
+        gen_ = torch.Generator().manual_seed(0)
+        ph = (torch.randn(pb * pl, 8192, generator=gen_) * 0.5).to(torch.bfloat16).to(dev)
+        pwt = (torch.randn(pw, 512, generator=gen_) * 0.02).to(torch.bfloat16).to(dev).repeat(1, 16)
+        pbias = (torch.randn(pw, generator=gen_) * 0.1).to(torch.bfloat16).to(dev)
+        sms, _ = time_device_steps(lambda: side_ops.mamba_in_proj(ph, pwt, pbias, pp.view(pb * pl, pw)), 5, 3, flush)
+        side["mamba_in_proj M=2048 K=8192 N=32768"] = {
+            "us": round(sms / 5 * 1e3, 2), "bound": "tensor (bf16)",
+            "frac": round(2.0 * pb * pl * 8192 * pw / (sms / 5) / 1e9 / peaks["bf16_tflops"], 4)}
+        scode, sdetail = side_ops.last_status()
+        if scode != 0:
+            raise SystemExit(f"bench.py: side-ops device status {scode} detail {sdetail:#x}")
+        result["also"].append({"workload": "side operators (problems 038, 029)", "rows": side,
+                               "peaks": {"hbm_gbs": peaks["hbm_gbs"], "bf16_tflops": peaks["bf16_tflops"]}})
+        del pp, pmask, pcw, pcb, pout, ph, pwt, pbias
+        torch.cuda.empty_cache()
         # last, because seconds under the power cap leave the part hot and slow for whatever is timed next
         sout = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
         result["also"].append({"workload": f"{workload} back to back (sustained)",
