@@ -350,7 +350,10 @@ int launch_tile(const gu_problem* pr, const DeviceInfo& dev, cudaStream_t stream
 // 231.5, 4096 (24.2) within the noise; 256 tokens (1.51 rounds, no whole round before the cut) 55.2 against 47.1, and
 // 2 - 4 us lost where the tiles divide evenly.  So the heuristic wants two rounds or more and at least 10 % of the
 // device idle in the last round of whole tiles.
-bool pair_can_stream_k(int tiles, int clusters) { return clusters >= 2 && tiles >= clusters && 2 * clusters <= kPairMaxCtas; }
+bool pair_can_stream_k(int tiles, int clusters) {
+  // one flag word and one 128 KiB slot of the scratch per CTA
+  return clusters >= 2 && tiles >= clusters && 2 * clusters <= kPairMaxCtas && 2 * clusters <= kTileMaxGrid;
+}
 bool pair_prefers_stream_k(int tiles, int clusters) {
   if (!pair_can_stream_k(tiles, clusters) || tiles < 2 * clusters || tiles % clusters == 0) return false;
   const int rounds = (tiles + clusters - 1) / clusters;
