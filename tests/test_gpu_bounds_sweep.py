@@ -4,9 +4,10 @@
 built with -DGU_BOUNDS=1 (libgateup_bounds.so) every kernel tests each computed TMA coordinate, global index and
 ring / accumulator stage index against its extent before using it, records the first violation in the status word
 (`gu_last_status` -> GU_EBOUNDS) and skips the access.  This test runs every token count M = 1 ... 129 at
-K, N in {128, 256} through every plan that takes the shape — the lone-CTA tile kernel, the CTA-pair kernel (forced
-also where the second CTA of a pair has no rows), its stream-K schedule and the weight-streaming kernel — inside
-that build, with canary rows and columns around the destination, against the CPU oracle.  A process binds one build
+K, N in {128, 256} through every plan that takes the shape — the lone-CTA tile kernel and its stream-K schedule, the
+CTA-pair kernel (forced also where the second CTA of a pair has no rows) and the weight-streaming kernel — inside
+that build, with canary rows and columns around the destination, against the CPU oracle; then a few larger shapes
+through the pair kernel's stream-K schedule, its FP8-output epilogue and its plain-GEMM mode.  A process binds one build
 of the library, so the sweep runs in a child process.
 """
 import os
@@ -57,6 +58,44 @@ for k in (128, 256):
                 mask = torch.ones_like(wide, dtype=torch.bool)
                 mask[1:m + 1, 128:128 + n] = False
                 assert bool((wide[mask] == 7.0).all()), f"M={m} K={k} N={n} {plan}: wrote outside the destination"
+# larger shapes for what needs many tiles or other epilogues: the pair kernel's stream-K schedule (a tile per cluster
+# at least), its FP8-output epilogue and its plain-GEMM mode
+for shape in ((512, 128, 4864), (300, 256, 5120), (1100, 128, 2432)):
+    inp = W.make_inputs(*shape, seed=sum(shape))
+    ref = O.gateup_blockwise(*inp.args())
+    g = inp.to(dev)
+    m, k, n = shape
+    wide = torch.full((m + 2, n + 256), 7.0, dtype=torch.bfloat16, device=dev)
+    view = wide[1:m + 1, 128:128 + n]
+    pkg.run_with_plan(*g.args(), view, "tile_pair_sk")
+    launches += 1
+    torch.cuda.synchronize()
+    code, detail = pkg.last_status()
+    assert code == 0, f"{shape} tile_pair_sk: device status {code}, detail {detail:#x}"
+    st = O.error_stats(view.float().cpu(), ref)
+    assert st["finite"] and st["rel_l2"] <= 1e-3, (shape, st)
+    mask = torch.ones_like(wide, dtype=torch.bool)
+    mask[1:m + 1, 128:128 + n] = False
+    assert bool((wide[mask] == 7.0).all()), f"{shape} tile_pair_sk: wrote outside the destination"
+for shape in ((300, 256, 256), (129, 128, 384)):
+    m, k, n = shape
+    g = W.make_inputs(*shape, seed=7 + m).to(dev)
+    q = torch.zeros(m, n, dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn)
+    sc = torch.zeros(m, n // 128, dtype=torch.float32, device=dev)
+    pkg.run_fp8_output(*g.args(), q, sc)
+    ref = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+    pkg.run_with_plan(*g.args(), ref, "tile_dp")
+    c = torch.empty(m, k, dtype=torch.bfloat16, device=dev)
+    wq, ws = W.quantize_weight_128x128(torch.randn(k, n, device=dev) * 0.05)
+    pkg.blockwise_gemm(q, sc, wq, ws, c)
+    launches += 3
+    torch.cuda.synchronize()
+    code, detail = pkg.last_status()
+    assert code == 0, f"{shape} fp8 output / plain GEMM: device status {code}, detail {detail:#x}"
+    q_ref, s_ref = W.quantize_activation_1x128(ref.cpu().float())
+    assert torch.equal(sc.cpu(), s_ref) and torch.equal(q.cpu().view(torch.uint8), q_ref.view(torch.uint8))
+    want = O.gemm_blockwise(q.cpu(), sc.cpu(), wq.cpu(), ws.cpu())
+    assert O.error_stats(c, want)["rel_l2"] <= 1e-3
 print(f"swept {launches} launches under the range-checked build: status 0 throughout")
 """
 
