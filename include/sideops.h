@@ -23,6 +23,7 @@ extern "C" {
 #define SO_ECUDA -4        /* the launch failed */
 #define SO_EDEVICE -5      /* the current device is not a compute capability 10.x GPU */
 #define SO_ETIMEOUT -6     /* so_last_status: a bounded device-side wait of an earlier launch ran out */
+#define SO_EBOUNDS -7      /* so_last_status, range-checked debug build only: an index or coordinate was out of range */
 
 int so_version(void);
 const char* so_error_string(int code);
@@ -71,9 +72,17 @@ int so_mamba_in_proj(const void* hidden, const void* weight, const void* bias, v
 
 /*
  * Synchronises the device and returns SO_OK, or SO_ETIMEOUT if a bounded wait inside so_mamba_in_proj ran out since
- * the status was last cleared (`detail`: wait id << 24 | block); `clear` != 0 resets it.
+ * the status was last cleared (`detail`: wait id << 24 | block), or SO_EBOUNDS (range-checked build); `clear` != 0
+ * resets it.
  */
 int so_last_status(int* detail, int clear);
+
+/*
+ * 1 in the range-checked debug build (-DGU_BOUNDS=1: the projection kernel tests every computed TMA coordinate, bias
+ * index and ring stage against its extent, records the first violation — so_last_status then returns SO_EBOUNDS with
+ * detail = site << 16 | block — and skips the access), 0 in the regular library.
+ */
+int so_is_range_checked_build(void);
 
 /* Time limit of the device-side waits in nanoseconds (0 restores the default of 2 s).  Synchronises the device. */
 int so_set_wait_limit_ns(uint64_t ns);

@@ -4,14 +4,13 @@ from __future__ import annotations
 
 import ctypes
 from ctypes import POINTER, c_char_p, c_float, c_int, c_int64, c_uint64, c_void_p
-from pathlib import Path
+from . import build as _build
 
-LIB_PATH = Path(__file__).resolve().parent / "libsideops.so"
-
-SO_OK, SO_EINVAL_NULL, SO_EINVAL_SHAPE, SO_EINVAL_ALIGN, SO_ECUDA, SO_EDEVICE, SO_ETIMEOUT = 0, -1, -2, -3, -4, -5, -6
+SO_OK, SO_EINVAL_NULL, SO_EINVAL_SHAPE, SO_EINVAL_ALIGN, SO_ECUDA, SO_EDEVICE, SO_ETIMEOUT, SO_EBOUNDS = (
+    0, -1, -2, -3, -4, -5, -6, -7)
 
 EXPORTS = ("so_version", "so_error_string", "so_rmsnorm_qk", "so_mamba_conv1d_tail", "so_mamba_in_proj", "so_last_status",
-           "so_set_wait_limit_ns", "so_launch_count")
+           "so_is_range_checked_build", "so_set_wait_limit_ns", "so_launch_count")
 
 
 class SideOpsError(RuntimeError):
@@ -21,6 +20,7 @@ class SideOpsError(RuntimeError):
 
 
 def _load() -> ctypes.CDLL:
+    LIB_PATH = _build.SIDE_LIB_PATH  # (a study or debug build can be bound by setting this before the first import)
     if not LIB_PATH.exists():
         raise ImportError(
             f"{LIB_PATH} is missing. Build it with `python -m sol_execbench_b200_kernels_b200.build` "
@@ -39,6 +39,7 @@ def _load() -> ctypes.CDLL:
     lib.so_mamba_in_proj.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p]
     lib.so_last_status.restype = c_int
     lib.so_last_status.argtypes = [POINTER(c_int), c_int]
+    lib.so_is_range_checked_build.restype = c_int
     lib.so_set_wait_limit_ns.restype = c_int
     lib.so_set_wait_limit_ns.argtypes = [c_uint64]
     lib.so_launch_count.restype = c_int64

@@ -82,9 +82,14 @@ def build_trace(force: bool = False, verbose: bool = False) -> Path:
 BOUNDS_LIB_PATH = PKG_DIR / "libgateup_bounds.so"
 
 
+SIDE_BOUNDS_LIB_PATH = PKG_DIR / "libsideops_bounds.so"
+
+
 def build_bounds(force: bool = False, verbose: bool = False) -> Path:
     if force or _stale(BOUNDS_LIB_PATH, SOURCES + HEADERS):
         _compile(BOUNDS_LIB_PATH, SOURCES, verbose, defines=("GU_BOUNDS=1",))
+    if force or _stale(SIDE_BOUNDS_LIB_PATH, SIDE_SOURCES + SIDE_HEADERS):
+        _compile(SIDE_BOUNDS_LIB_PATH, SIDE_SOURCES, verbose, defines=("GU_BOUNDS=1",))
     return BOUNDS_LIB_PATH
 
 

@@ -49,6 +49,8 @@ struct PjCfg {
 };
 
 enum : unsigned { kWaitPjSlot = 40, kWaitPjFull = 41, kWaitPjAccFree = 42, kWaitPjAccFull = 43 };
+// sites of the range-checked debug build (-DGU_BOUNDS=1, see GU_IN_RANGE)
+enum : unsigned { kSitePjLoad = 49, kSitePjStage = 50, kSitePjStore = 51, kSitePjBias = 52, kSitePjTile = 53 };
 
 struct ProjParams {
   const __nv_bfloat16* bias;  // [N]
@@ -177,7 +179,13 @@ __device__ __forceinline__ void proj_gemm_body(const CUtensorMap& tm_a, const CU
         const bool ok = pj_wait_elected(ctx, elected, bar_empty + 8 * stage, phase ^ 1u, kWaitPjSlot);
         const uint32_t full = full_base + 8 * stage;
         const uint32_t dst = ring + stage * Cfg::stage_bytes;
-        if (ok && elected) {
+        // (loads may start past the last row of a ragged tile, where they read zeros, but never before row 0, past the
+        // padded row range, or at a K offset that is not 16-byte aligned)
+        if (ok && elected && GU_IN_RANGE(stage < static_cast<uint32_t>(Cfg::stages), kSitePjStage) &&
+            GU_IN_RANGE(tm >= 0 && tm < p.m_tiles && tn >= 0 && tn < p.n_tiles, kSitePjTile) &&
+            GU_IN_RANGE(j >= 0 && j < p.kb && ((j * kPjBlockK * 2) & 15) == 0 && row0 >= 0 &&
+                            row0 < p.m_tiles * Cfg::rows_per_tile && wrow0 >= 0 && wrow0 < p.n_tiles * kPjTileN,
+                        kSitePjLoad)) {
           // rows past M / N and columns past K read as zero
           if constexpr (kPair) {
             mbar_arrive_expect_tx_cluster(full, Cfg::stage_bytes);
@@ -265,7 +273,9 @@ __device__ __forceinline__ void proj_gemm_body(const CUtensorMap& tm_a, const CU
         uint4 bq[8];  // this chunk's 64 bias values (the same for every row: broadcast loads)
 #pragma unroll
         for (int q = 0; q < 8; ++q)
-          bq[q] = (colc + 8 * q < p.n) ? __ldg(reinterpret_cast<const uint4*>(p.bias + colc + 8 * q)) : make_uint4(0, 0, 0, 0);
+          bq[q] = (colc + 8 * q < p.n && GU_IN_RANGE(colc + 8 * q >= 0 && colc + 8 * q + 8 <= p.n, kSitePjBias))
+                      ? __ldg(reinterpret_cast<const uint4*>(p.bias + colc + 8 * q))
+                      : make_uint4(0, 0, 0, 0);
         tmem_ld_wait_pin<64>(v);
         if (c + 1 == kPjTileN / 64) {
           // the whole accumulator is in registers or stored: hand it back to the issuer
@@ -293,7 +303,9 @@ __device__ __forceinline__ void proj_gemm_body(const CUtensorMap& tm_a, const CU
         }
         fence_proxy_async_smem();
         named_bar_sync(2, 128);
-        if (et == 0 && ok && !ctx.aborted && row0 < p.m && colc < p.n) {
+        // (a store may reach past the last row or column, where it is clipped, but starts inside the tensor)
+        if (et == 0 && ok && !ctx.aborted && row0 < p.m && colc < p.n &&
+            GU_IN_RANGE(row0 >= 0 && colc >= 0 && ((colc * 2) & 15) == 0, kSitePjStore)) {
           tma_store_2d(&tm_out, stag + (c & 1) * kPjOutChunkBytes, colc, row0);  // rows past M, columns past N are clipped
           tma_store_commit();
         }

@@ -494,6 +494,7 @@ const char* so_error_string(int code) {
     case SO_ECUDA: return "the CUDA launch failed";
     case SO_EDEVICE: return "the current device is not a compute capability 10.x GPU";
     case SO_ETIMEOUT: return "a device-side wait of an earlier launch ran out; its output is not valid";
+    case SO_EBOUNDS: return "the range-checked debug build found an index or coordinate outside its extent";
     default: return "unknown error code";
   }
 }
@@ -564,7 +565,16 @@ int so_last_status(int* detail, int clear) {
     const unsigned int zero[4] = {0, 0, 0, 0};
     if (cudaMemcpyToSymbol(gu::g_status, zero, sizeof(zero)) != cudaSuccess) return SO_ECUDA;
   }
-  return host[0] == 0 ? SO_OK : SO_ETIMEOUT;
+  if (host[0] == 0) return SO_OK;
+  return host[0] == gu::kStatusBounds ? SO_EBOUNDS : SO_ETIMEOUT;
+}
+
+int so_is_range_checked_build(void) {
+#ifdef GU_BOUNDS
+  return 1;
+#else
+  return 0;
+#endif
 }
 
 int so_set_wait_limit_ns(uint64_t ns) {

@@ -109,7 +109,55 @@ def test_every_small_shape_through_every_plan_under_the_range_checked_build():
     assert "status 0 throughout" in proc.stdout
 
 
+_PROJ_SWEEP = r"""
+import os, sys
+sys.path.insert(0, os.environ["GU_ROOT"])
+import sol_execbench_b200_kernels_b200.build as B
+B.SIDE_LIB_PATH = B.SIDE_BOUNDS_LIB_PATH
+import torch
+from sol_execbench_b200_kernels_b200 import _sideops_cabi, side_ops
+
+assert _sideops_cabi.lib.so_is_range_checked_build() == 1
+dev = torch.device("cuda:0")
+side_ops.last_status()
+launches = 0
+g = torch.Generator().manual_seed(3)
+for k in (8, 64, 72, 200):
+    for n in (8, 248, 264, 520):
+        weight = (torch.randn(n, k, generator=g) * 0.1).to(torch.bfloat16).to(dev)
+        bias = (torch.randn(n, generator=g) * 0.2).to(torch.bfloat16).to(dev)
+        for m in list(range(1, 131)) + [255, 256, 257, 300, 383, 384, 385, 511, 513]:
+            hidden = (torch.randn(m, k, generator=g) * 0.5).to(torch.bfloat16).to(dev)
+            buf = torch.full((m + 2, n), 7.0, dtype=torch.bfloat16, device=dev)     # canary rows around the result
+            out = buf[1:m + 1]
+            side_ops.mamba_in_proj(hidden, weight, bias, out)
+            launches += 1
+            torch.cuda.synchronize()
+            code, detail = side_ops.last_status()
+            assert code == 0, f"M={m} K={k} N={n}: device status {code}, detail {detail:#x}"
+            exact = hidden.double() @ weight.double().t() + bias.double()
+            mags = hidden.double().abs() @ weight.double().abs().t() + bias.double().abs()
+            err = (out.double() - exact).abs()
+            assert bool((err <= exact.abs() * 2.0 ** -8 + mags * 2.0 ** -16 + 1e-30).all()), (m, k, n, float(err.max()))
+            assert bool((buf[0] == 7.0).all()) and bool((buf[m + 1] == 7.0).all()), f"M={m} K={k} N={n}: wrote outside"
+print(f"swept {launches} projection launches under the range-checked build: status 0 throughout")
+"""
+
+
+def test_projection_small_shapes_under_the_range_checked_build():
+    """The bf16 projection GEMM relies on TMA's out-of-range behaviour for ragged M, K and N (reads give zero, stores
+    are clipped): every M = 1 ... 130 and a few around the 256-row pair tile, at K and N that are and are not whole
+    tiles, inside the range-checked build of libsideops, with canary rows around the destination."""
+    lib = os.path.join(ROOT, "sol_execbench_b200_kernels_b200", "libsideops_bounds.so")
+    assert os.path.exists(lib), "libsideops_bounds.so is missing: python -m sol_execbench_b200_kernels_b200.build --bounds"
+    proc = subprocess.run([sys.executable, "-c", _PROJ_SWEEP], env=dict(os.environ, GU_ROOT=ROOT), capture_output=True,
+                          text=True, timeout=1500)
+    assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-4000:]
+    assert "status 0 throughout" in proc.stdout
+
+
 def test_the_regular_library_is_not_the_range_checked_build():
-    from sol_execbench_b200_kernels_b200 import _cabi
+    from sol_execbench_b200_kernels_b200 import _cabi, _sideops_cabi
 
     assert _cabi.lib.gu_is_range_checked_build() == 0
+    assert _sideops_cabi.lib.so_is_range_checked_build() == 0
