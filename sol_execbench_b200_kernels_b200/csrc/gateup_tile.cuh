@@ -322,6 +322,7 @@ __device__ __forceinline__ void tile_kernel_body(const CUtensorMap& tm_x, const 
           su_row = p.scale_up + static_cast<size_t>(nb) * p.kb;
         }
         const int w_blocks = kSingle ? p.n_blocks128 : p.num_n_blocks;
+        (void)w_blocks;  // (only the range-checked build looks at it)
         if (!GU_IN_RANGE(m_global >= 0 && m_global < p.m && (sg_row - p.scale_gate) / p.kb < w_blocks &&
                              (su_row - (kSingle ? p.scale_gate : p.scale_up)) / p.kb < w_blocks, kSiteTileScale))
           return;

@@ -73,7 +73,6 @@ __global__ void __launch_bounds__(32) peer_barrier_kernel(const PeerBarrierParam
   unsigned int* mine = p.flags[p.rank];
   const unsigned int epoch = *reinterpret_cast<volatile unsigned int*>(mine + 16) + 1u;
   __syncwarp();
-  unsigned int missing = 0;
   if (t < p.world) {
     // everything this rank's earlier kernels on the stream wrote (to any rank) is visible before the stamp is
     asm volatile("fence.acq_rel.sys;" ::: "memory");
@@ -88,7 +87,6 @@ __global__ void __launch_bounds__(32) peer_barrier_kernel(const PeerBarrierParam
         if (t0 == 0) {
           t0 = now;
         } else if (now - t0 > p.limit_ns) {
-          missing = 1;
           if (atomicCAS(&g_status[0], 0u, kWaitPeerBarrier) == 0u)
             g_status[1] = (kWaitPeerBarrier << 24) | static_cast<unsigned int>(t);
           break;
@@ -97,7 +95,6 @@ __global__ void __launch_bounds__(32) peer_barrier_kernel(const PeerBarrierParam
       }
     }
   }
-  (void)missing;
   __syncwarp();
   if (t == 0) *reinterpret_cast<volatile unsigned int*>(mine + 16) = epoch;
 }
