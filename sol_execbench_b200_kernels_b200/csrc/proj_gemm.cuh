@@ -304,9 +304,12 @@ __device__ __forceinline__ void proj_gemm_body(const CUtensorMap& tm_a, const CU
         fence_proxy_async_smem();
         named_bar_sync(2, 128);
         // (a store may reach past the last row or column, where it is clipped, but starts inside the tensor)
-        if (et == 0 && ok && !ctx.aborted && row0 < p.m && colc < p.n &&
-            GU_IN_RANGE(row0 >= 0 && colc >= 0 && ((colc * 2) & 15) == 0, kSitePjStore)) {
-          tma_store_2d(&tm_out, stag + (c & 1) * kPjOutChunkBytes, colc, row0);  // rows past M, columns past N are clipped
+        if (et == 0) {
+          if (ok && !ctx.aborted && row0 < p.m && colc < p.n &&
+              GU_IN_RANGE(row0 >= 0 && colc >= 0 && ((colc * 2) & 15) == 0, kSitePjStore))
+            tma_store_2d(&tm_out, stag + (c & 1) * kPjOutChunkBytes, colc, row0);  // rows past M, columns past N are clipped
+          // one group per chunk, also when the chunk lies outside the tensor and nothing is stored (an empty group):
+          // "all groups but the newest have been read" above then always means "the store two chunks back has"
           tma_store_commit();
         }
       }
