@@ -93,6 +93,8 @@ enum : unsigned {
 //                6 consumers do the promotion arithmetic on stale registers but never read TMEM
 //                7 consumers read only 64 of their 128 columns (two rounds of loads) before the stage goes back, all
 //                  the arithmetic still done; 8 as 7 with the arithmetic of those 64 columns only
+//                9 the epilogue warps skip the SwiGLU arithmetic (what their instruction stream costs the consumer
+//                  warps that share their schedulers)
 //   -DGU_PAIR_THREADS=512, -DGU_PIECE=32, -DGU_INFLIGHT=1, -DGU_PAIR_STAGES=5   layout variants that were measured
 #ifdef GU_TRACE
 // Cycle counters of cluster 0 (both CTAs), summed over the launch: [rank][slot]
@@ -600,7 +602,9 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tm_x, const 
           fence_proxy_async_smem();
           named_bar_sync(4, kPairAllHands);
         } else {
+#if !(defined(GU_EXP) && GU_EXP == 9)  // (experiment 9: the epilogue warps store the gate tile without the SwiGLU arithmetic)
           pair_swiglu_chunks(hand_gen, et, kPairEpiThreads);
+#endif
           fence_proxy_async_smem();
           named_bar_sync(1, kPairEpiThreads);
         }
