@@ -274,7 +274,9 @@ int gu_run_decode_static(const gu_problem* problem, void* stream);
  * (2^126, 2^128)) that division returns 0 where g * sigmoid(g) would be a normal number of magnitude ~1e-36 — a
  * deviation of that size and nothing more.  gu_quantize_activation takes the block maximum with a maximum that
  * ignores NaN: a NaN input does not poison its block's scale (torch's amax would propagate it); the NaN element
- * itself goes through the hardware's saturating e4m3 conversion.  Inputs are expected to be finite.
+ * itself goes through the hardware's saturating e4m3 conversion.  Inputs are expected to be finite.  A zero keeps
+ * its sign through both quantisers (the activation quantiser and the FP8-output epilogue): -0.0, and a negative
+ * whose quotient rounds to zero, become e4m3 0x80 as in the torch quantiser.
  */
 
 /* Kernel launches issued by this library in this process so far. */

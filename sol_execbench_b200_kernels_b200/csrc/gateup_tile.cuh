@@ -412,7 +412,9 @@ __device__ __forceinline__ void tile_kernel_body(const CUtensorMap& tm_x, const 
                 const float a = __uint_as_float(pr << 16), b = __uint_as_float(pr & 0xffff0000u);
                 const float qa0 = a * rc, qb0 = b * rc;  // correctly rounded a / sc, b / sc (exact-residual step)
                 const float qa = fmaf(fmaf(-qa0, sc, a), rc, qa0), qb = fmaf(fmaf(-qb0, sc, b), rc, qb0);
-                word |= static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(make_float2(qa, qb), __NV_SATFINITE, __NV_E4M3))
+                // (the residual step turns a quotient of -0 into +0; the source's sign bits put the sign of such a zero back)
+                const uint32_t signs = ((pr >> 8) & 0x80u) | ((pr >> 16) & 0x8000u);
+                word |= (static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(make_float2(qa, qb), __NV_SATFINITE, __NV_E4M3)) | signs)
                         << (16 * e);
               }
               w[k4] = word;

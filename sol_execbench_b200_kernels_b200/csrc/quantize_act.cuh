@@ -144,7 +144,10 @@ quantize_act_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, float* __r
             // |x| <= amax, so |x / s| <= 448 up to one rounding; the saturating conversion does the clamp
             const float2 ac = quot2(v[4 * w + 2 * i], v[4 * w + 2 * i + 1]);
             const __nv_fp8x2_storage_t pair = __nv_cvt_float2_to_fp8x2(ac, __NV_SATFINITE, __NV_E4M3);
-            word |= static_cast<uint32_t>(pair) << (16 * i);
+            // (the residual step turns a quotient of -0 into +0; the source's sign bits put the sign of such a zero back)
+            const uint32_t signs = ((__float_as_uint(v[4 * w + 2 * i]) >> 24) & 0x80u) |
+                                   ((__float_as_uint(v[4 * w + 2 * i + 1]) >> 16) & 0x8000u);
+            word |= (static_cast<uint32_t>(pair) | signs) << (16 * i);
           }
           packed[w] = word;
         }

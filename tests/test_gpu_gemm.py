@@ -71,7 +71,7 @@ def test_blockwise_gemm_pitched_output_and_errors():
 
 
 @pytest.mark.parametrize("shape", [(128, 256, 128), (129, 128, 128), (256, 256, 256), (300, 512, 384), (1000, 1024, 640),
-                                   (2048, 512, 1792)])
+                                   (2048, 512, 1792), (256, 128, 14336), (100, 128, 14336)])  # (the last two have -0.0 outputs)
 def test_fp8_output_epilogue_equals_quantising_the_bf16_result(shape):
     """Fused re-quantisation: e4m3 bytes and scales identical to quantising `run`'s bf16 output afterwards."""
     import sol_execbench_b200_kernels_b200 as pkg

@@ -42,6 +42,20 @@ def test_quantizer_edge_values():
     _compare(x.to(torch.bfloat16))
 
 
+def test_quantizer_keeps_the_sign_of_zero():
+    # -0.0 in, and negatives so small that their quotient rounds to zero: e4m3 0x80, as the torch quantiser gives
+    x = torch.randn(8, 256, generator=torch.Generator().manual_seed(5))
+    x[0, 3] = -0.0
+    x[1, 100:140] = -0.0
+    x[2, 7] = -1e-12
+    x[3, :128] = -0.0                # a whole block of negative zeros (amax 0: the clamp floor sets the scale)
+    x[4, 130] = -1e-30
+    for dtype in (torch.float32, torch.bfloat16):
+        _compare(x.to(dtype))
+    q, _ = W.quantize_activation_1x128(x)
+    assert int(q.view(torch.uint8)[0, 3]) == 0x80    # (the reference quantiser itself keeps the sign)
+
+
 def test_quantizer_pitched_rows_and_outputs_feed_run():
     import sol_execbench_b200_kernels_b200 as pkg
 
