@@ -1,0 +1,129 @@
+"""Seeded random shapes through every entry point: what hand-picked parametrisations miss (this sweep found the
+quantisers dropping the sign of a zero).  Each case compares two routes to the same result — the CTA-pair kernel and
+its schedules against the lone-CTA kernel, the weight-streaming kernel against the tile kernel, the fused e4m3 epilogue
+against quantising the bf16 result, the plain GEMM on pairs against lone-CTA row blocks, the projection against the
+exact product, the side operators against their CPU restatement — with canary rows and columns around the destination
+and the device status word checked after every launch."""
+import random
+
+import pytest
+import torch
+
+from oracle import sideops_oracle as SO
+from sol_execbench_b200_kernels_b200 import workloads as W
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _status_ok(pkg):
+    torch.cuda.synchronize()
+    code, detail = pkg.last_status()
+    assert code == 0, f"device status {code}, detail {detail:#x}"
+
+
+def test_tile_plans_on_random_shapes():
+    import sol_execbench_b200_kernels_b200 as pkg
+
+    rng = random.Random(1234)
+    for it in range(40):
+        m = rng.choice([129, 130, 200, 255, 256, 257, 300, 383, 384, 385, 400, 511, 512, 513, 640, 700, 768, 1000, 1024,
+                        1100, 1500, 2047, 2048, 2050])
+        k = 128 * rng.choice([1, 2, 3, 4, 5, 8, 16])
+        n = 128 * rng.choice([1, 2, 3, 5, 8, 19, 20, 37, 38, 40, 56, 74, 75, 100, 112, 148])
+        inp = W.make_inputs(m, k, n, seed=it, device=DEV)
+        wide = torch.empty(m + 2, n + 256, dtype=torch.bfloat16, device=DEV)
+        ref = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+        pkg.run_with_plan(*inp.args(), ref, "tile_dp")
+        tiles = ((m + 255) // 256) * (n // 128)
+        for plan in ["tile_pair", "tile", "auto"] + (["tile_pair_sk"] if tiles >= 74 else []):
+            wide.fill_(7.0)
+            view = wide[1:m + 1, 128:128 + n]
+            pkg.run_with_plan(*inp.args(), view, plan)
+            _status_ok(pkg)
+            mask = torch.ones_like(wide, dtype=torch.bool)
+            mask[1:m + 1, 128:128 + n] = False
+            assert bool((wide[mask] == 7.0).all()), (m, k, n, plan, "wrote outside the destination")
+            if plan == "tile_pair":
+                assert torch.equal(view, ref), (m, k, n, plan)      # whole tiles: the lone-CTA kernel's bits
+            else:                                                    # a tile cut along K: single roundings may differ
+                rel = float(torch.linalg.vector_norm(view.float() - ref.float()) / torch.linalg.vector_norm(ref.float()))
+                assert rel <= 1e-4 and float((view != ref).float().mean()) <= 5e-3, (m, k, n, plan, rel)
+        q = torch.zeros(m, n, dtype=torch.uint8, device=DEV).view(torch.float8_e4m3fn)
+        sc = torch.zeros(m, n // 128, dtype=torch.float32, device=DEV)
+        pkg.run_fp8_output(*inp.args(), q, sc)
+        _status_ok(pkg)
+        q_ref, s_ref = W.quantize_activation_1x128(ref.cpu().float())
+        assert torch.equal(sc.cpu(), s_ref) and torch.equal(q.cpu().view(torch.uint8), q_ref.view(torch.uint8)), (m, k, n)
+
+
+def test_streaming_kernel_and_plain_gemm_on_random_shapes():
+    import sol_execbench_b200_kernels_b200 as pkg
+
+    rng = random.Random(99)
+    for it in range(30):
+        m, k = rng.randint(1, 64), 128 * rng.choice([1, 2, 4, 7, 16, 32])
+        n = 128 * rng.choice([1, 2, 3, 8, 37, 74, 100, 148, 150])
+        inp = W.make_inputs(m, k, n, seed=it, device=DEV)
+        a = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+        b = torch.empty_like(a)
+        pkg.run_with_plan(*inp.args(), a, "tile_dp")
+        pkg.run_with_plan(*inp.args(), b, "stream")
+        _status_ok(pkg)
+        rel = float(torch.linalg.vector_norm(a.float() - b.float()) / torch.linalg.vector_norm(a.float()).clamp_min(1e-30))
+        assert rel <= 1e-3, (m, k, n, rel)
+    for it in range(20):
+        m = rng.choice([129, 200, 256, 300, 384, 500, 513, 777, 1024, 1100])
+        k, n = 128 * rng.choice([1, 2, 3, 8, 20]), 128 * rng.choice([1, 2, 3, 5, 9, 16, 33])
+        a, sa = W.quantize_activation_1x128(torch.randn(m, k, device=DEV))
+        b, sb = W.quantize_weight_128x128(torch.randn(n, k, device=DEV) * 0.05)
+        c = torch.full((m + 1, n + 128), 3.0, dtype=torch.bfloat16, device=DEV)
+        pkg.blockwise_gemm(a, sa, b, sb, c[:m, :n])
+        ref = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+        for lo in range(0, m, 128):      # (at most 128 rows at a time take the lone-CTA kernel)
+            hi = min(m, lo + 128)
+            pkg.blockwise_gemm(a.view(torch.uint8)[lo:hi].contiguous().view(a.dtype), sa[lo:hi].contiguous(), b, sb, ref[lo:hi])
+        _status_ok(pkg)
+        assert torch.equal(c[:m, :n], ref), (m, k, n)
+        assert bool((c[m] == 3.0).all()) and bool((c[:, n:] == 3.0).all()), (m, k, n, "wrote outside the destination")
+
+
+def test_side_operators_on_random_shapes():
+    from sol_execbench_b200_kernels_b200 import side_ops
+
+    rng = random.Random(7)
+    for it in range(30):
+        m = rng.choice([1, 5, 64, 127, 128, 129, 255, 256, 257, 300, 512, 640, 1000])
+        k, n = 8 * rng.randint(1, 130), 8 * rng.randint(1, 140)
+        g = torch.Generator().manual_seed(it)
+        h = (torch.randn(m, k, generator=g) * 0.5).to(torch.bfloat16).to(DEV)
+        w = (torch.randn(n, k, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+        bias = (torch.randn(n, generator=g) * 0.2).to(torch.bfloat16).to(DEV)
+        buf = torch.full((m + 2, n), 7.0, dtype=torch.bfloat16, device=DEV)
+        out = buf[1:m + 1]
+        side_ops.mamba_in_proj(h, w, bias, out)
+        torch.cuda.synchronize()
+        assert side_ops.last_status() == (0, 0)
+        exact = h.double() @ w.double().t() + bias.double()
+        mags = h.double().abs() @ w.double().abs().t() + bias.double().abs()
+        err = (out.double() - exact).abs()
+        # one bf16 rounding step of the exact product plus the fp32 accumulation's share (see test_gpu_sideops.py)
+        assert bool((err <= exact.abs() * 2.0 ** -8 + mags * 2.0 ** -16 + 1e-30).all()), (m, k, n, float(err.max()))
+        assert bool((buf[0] == 7.0).all()) and bool((buf[m + 1] == 7.0).all()), (m, k, n, "wrote outside the destination")
+    for it in range(15):
+        b, l = rng.randint(1, 3), rng.choice([1, 2, 3, 4, 5, 31, 127, 128, 129, 200, 333, 1000])
+        c = 64 * rng.randint(1, 6)
+        width = c + 8 * rng.randint(0, 20)
+        p, mask, cw, cb = W.make_mamba_tail_inputs(b, l, c, width, seed=it)
+        want = SO.mamba_conv1d_tail(p, mask, cw, cb)
+        got = torch.empty(b, c, l, dtype=torch.bfloat16, device=DEV)
+        side_ops.mamba_conv1d_tail(p.to(DEV), mask.to(DEV), cw.to(DEV), cb.to(DEV), got)
+        differ = int((got.cpu() != want).sum())
+        assert differ <= max(2, 1e-3 * want.numel()), (b, l, c, width, differ)       # (tolerance of test_gpu_sideops.py)
+        tokens, heads = rng.randint(1, 700), rng.choice([1, 3, 24, 48])
+        q, kk, wq, wk, eps = W.make_rmsnorm_inputs(tokens, heads, seed=it)
+        qn, kn = torch.empty_like(q, device=DEV), torch.empty_like(kk, device=DEV)
+        side_ops.rmsnorm_qk(q.to(DEV), kk.to(DEV), wq.to(DEV), wk.to(DEV), eps, qn, kn)
+        aq, ak = SO.rmsnorm_qk(q, kk, wq, wk, eps)
+        torch.testing.assert_close(qn.cpu(), aq, rtol=4e-6, atol=4e-6)
+        torch.testing.assert_close(kn.cpu(), ak, rtol=4e-6, atol=4e-6)
