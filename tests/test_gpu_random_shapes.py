@@ -127,3 +127,49 @@ def test_side_operators_on_random_shapes():
         aq, ak = SO.rmsnorm_qk(q, kk, wq, wk, eps)
         torch.testing.assert_close(qn.cpu(), aq, rtol=4e-6, atol=4e-6)
         torch.testing.assert_close(kn.cpu(), ak, rtol=4e-6, atol=4e-6)
+
+
+def test_fused_gather_and_reduce_emulated_on_one_gpu_on_random_shapes():
+    """All ranks of the fused column gather and of the fused GEMM + all-reduce run one after another on one GPU (one
+    buffer per rank, no kernel waits on another), over random token counts and rank counts."""
+    import sol_execbench_b200_kernels_b200 as pkg
+
+    rng = random.Random(5)
+    for it in range(20):
+        world = rng.choice([1, 2, 3, 4, 8])
+        m = rng.choice([1, 17, 100, 128, 129, 300, 512, 513, 1000])
+        k, n = 128 * rng.choice([1, 2, 4, 8]), 128 * world * rng.choice([1, 2, 3, 5])
+        inp = W.make_inputs(m, k, n, seed=it).to(DEV)
+        ref = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+        pkg.run_with_plan(*inp.args(), ref, "tile", whole_tiles=True)
+        bufs = [torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=DEV) for _ in range(world)]
+        for r in range(world):
+            gw, sg, uw, su = pkg.shard_weights(inp.gate_proj_weight, inp.scale_gate, inp.up_proj_weight, inp.scale_up, r, world)
+            pkg.run_gather(inp.x, inp.scale_x, gw, sg, uw, su, [b.data_ptr() for b in bufs], r, (m, n), n)
+        _status_ok(pkg)
+        for r in range(world):
+            assert torch.equal(bufs[r], ref), (m, k, n, world, r)
+    for it in range(20):
+        world = rng.choice([1, 2, 3, 4, 5, 8])
+        m, k = 128 * world * rng.choice([1, 2, 3]), 128 * world * rng.choice([1, 2, 4])
+        h = 128 * rng.choice([1, 2, 3, 5, 8])
+        a, sa = W.quantize_activation_1x128(torch.randn(m, k, device=DEV))
+        b, sb = W.quantize_weight_128x128(torch.randn(h, k, device=DEV) * 0.05)
+        slots = [torch.full((world, m // world, h), float("nan"), dtype=torch.bfloat16, device=DEV) for _ in range(world)]
+        outs = [torch.full((m, h), float("nan"), dtype=torch.bfloat16, device=DEV) for _ in range(world)]
+        want = torch.zeros(m, h, dtype=torch.float32, device=DEV)
+        for r in range(world):
+            lo, hi = pkg.shard_bounds(k, r, world)
+            a_r = a.view(torch.uint8)[:, lo:hi].contiguous().view(a.dtype)
+            sa_r = sa[:, lo // 128:hi // 128].contiguous()
+            b_r, sb_r = pkg.shard_down_weights(b, sb, r, world)
+            part = torch.empty(m, h, dtype=torch.bfloat16, device=DEV)
+            pkg.blockwise_gemm(a_r, sa_r, b_r, sb_r, part)
+            want += part.float()
+            pkg.blockwise_gemm_scatter(a_r, sa_r, b_r, sb_r, [s.data_ptr() for s in slots], r)
+        for r in range(world):
+            pkg.reduce_gather(slots[r], [o.data_ptr() for o in outs], r, m, h)
+        _status_ok(pkg)
+        want = want.to(torch.bfloat16)
+        for r in range(world):
+            assert torch.equal(outs[r], want), (m, k, h, world, r)
