@@ -460,7 +460,8 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tm_x, const 
             ok = (hit_free || mbar_wait(ctx, stage_free, acc_phase ^ 1u, kWaitPairStageFree)) && ok;
 #endif
           }
-          ok = __all_sync(0xffffffffu, ok);
+          // (only the elected lane looks at `ok`; the others walk the loop whatever it is, so no vote is needed between
+          // the wake-up and the first MMA)
           GU_TR_END(1);
           GU_EV(0, j, 0);
           if (ok && elected) {
