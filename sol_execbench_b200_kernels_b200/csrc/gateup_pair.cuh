@@ -265,11 +265,11 @@ __device__ __forceinline__ uint32_t e4m3x4_from_bf16x4(uint32_t p0, uint32_t p1,
     const float a = __uint_as_float(pr << 16), b = __uint_as_float(pr & 0xffff0000u);
     const float qa0 = a * rc, qb0 = b * rc;
     const float qa = fmaf(fmaf(-qa0, sc, a), rc, qa0), qb = fmaf(fmaf(-qb0, sc, b), rc, qb0);
-    // (the residual step turns a quotient of -0 into +0; the source's sign bits put the sign of such a zero back)
-    const uint32_t signs = ((pr >> 8) & 0x80u) | ((pr >> 16) & 0x8000u);
-    word |= (static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(make_float2(qa, qb), __NV_SATFINITE, __NV_E4M3)) | signs) << (16 * e);
+    word |= static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(make_float2(qa, qb), __NV_SATFINITE, __NV_E4M3)) << (16 * e);
   }
-  return word;
+  // (the residual step turns a quotient of -0 into +0; the sources' sign bits — the high byte of each bf16, gathered by
+  // one byte permute — put the sign of such a zero back; a quotient never has the other sign)
+  return word | (__byte_perm(p0, p1, 0x7531) & 0x80808080u);
 }
 
 // SiLU(gate) * up with the three roundings, in place over the handed-over tiles: 16-byte chunk q of the gate tile

@@ -412,12 +412,12 @@ __device__ __forceinline__ void tile_kernel_body(const CUtensorMap& tm_x, const 
                 const float a = __uint_as_float(pr << 16), b = __uint_as_float(pr & 0xffff0000u);
                 const float qa0 = a * rc, qb0 = b * rc;  // correctly rounded a / sc, b / sc (exact-residual step)
                 const float qa = fmaf(fmaf(-qa0, sc, a), rc, qa0), qb = fmaf(fmaf(-qb0, sc, b), rc, qb0);
-                // (the residual step turns a quotient of -0 into +0; the source's sign bits put the sign of such a zero back)
-                const uint32_t signs = ((pr >> 8) & 0x80u) | ((pr >> 16) & 0x8000u);
-                word |= (static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(make_float2(qa, qb), __NV_SATFINITE, __NV_E4M3)) | signs)
+                word |= static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(make_float2(qa, qb), __NV_SATFINITE, __NV_E4M3))
                         << (16 * e);
               }
-              w[k4] = word;
+              // (the residual step turns a quotient of -0 into +0; the sources' sign bits — the high byte of each
+              // bf16, gathered by one byte permute — put the sign of such a zero back)
+              w[k4] = word | (__byte_perm(o2[8 * c + 2 * k4], o2[8 * c + 2 * k4 + 1], 0x7531) & 0x80808080u);
             }
             const int chunk = half * 4 + c;
             *reinterpret_cast<uint4*>(out_row + ((chunk ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);

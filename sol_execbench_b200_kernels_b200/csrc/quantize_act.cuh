@@ -45,6 +45,11 @@ struct Raw8<__nv_bfloat16> {
     const float2 mf = __bfloat1622float2(m2);
     return fmaxf(mf.x, mf.y);
   }
+  // the sign bits of elements 4w .. 4w+3 at bits 7, 15, 23, 31 (the high byte of each bf16, one byte permute)
+  __device__ __forceinline__ uint32_t signs(int word) const {
+    const uint32_t* p = reinterpret_cast<const uint32_t*>(&w);
+    return __byte_perm(p[2 * word], p[2 * word + 1], 0x7531) & 0x80808080u;
+  }
 };
 template <>
 struct Raw8<float> {
@@ -61,6 +66,13 @@ struct Raw8<float> {
 #pragma unroll
     for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(v[i]));
     return m;
+  }
+  // the sign bits of elements 4w .. 4w+3 at bits 7, 15, 23, 31 (the top byte of each float)
+  __device__ __forceinline__ uint32_t signs(int word) const {
+    const float4& f = word ? b : a;
+    const uint32_t lo = __byte_perm(__float_as_uint(f.x), __float_as_uint(f.y), 0x0073);  // bytes: x.b3, y.b3, -, -
+    const uint32_t hi = __byte_perm(__float_as_uint(f.z), __float_as_uint(f.w), 0x0073);
+    return __byte_perm(lo, hi, 0x5410) & 0x80808080u;
   }
 };
 
@@ -144,11 +156,11 @@ quantize_act_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, float* __r
             // |x| <= amax, so |x / s| <= 448 up to one rounding; the saturating conversion does the clamp
             const float2 ac = quot2(v[4 * w + 2 * i], v[4 * w + 2 * i + 1]);
             const __nv_fp8x2_storage_t pair = __nv_cvt_float2_to_fp8x2(ac, __NV_SATFINITE, __NV_E4M3);
-            // (the residual step turns a quotient of -0 into +0; the source's sign bits put the sign of such a zero back)
-            const uint32_t signs = ((__float_as_uint(v[4 * w + 2 * i]) >> 24) & 0x80u) |
-                                   ((__float_as_uint(v[4 * w + 2 * i + 1]) >> 16) & 0x8000u);
-            word |= (static_cast<uint32_t>(pair) | signs) << (16 * i);
+            word |= static_cast<uint32_t>(pair) << (16 * i);
           }
+          // (the residual step turns a quotient of -0 into +0; the source's sign bits put the sign of such a zero back:
+          // a quotient never has the other sign, so the OR changes nothing else)
+          word |= raw[u].signs(w);
           packed[w] = word;
         }
         __stcs(reinterpret_cast<uint2*>(q + static_cast<long long>(bb) * 128 + sub * 8), make_uint2(packed[0], packed[1]));
