@@ -95,7 +95,7 @@ enum : unsigned {
 //                  the arithmetic still done; 8 as 7 with the arithmetic of those 64 columns only
 //                9 the epilogue warps skip the SwiGLU arithmetic (what their instruction stream costs the consumer
 //                  warps that share their schedulers)
-//   -DGU_PAIR_THREADS=512, -DGU_PIECE=32, -DGU_INFLIGHT=1, -DGU_PAIR_STAGES=5   layout variants that were measured
+//   -DGU_PAIR_THREADS=512, -DGU_PIECE=32, -DGU_INFLIGHT=1, -DGU_PAIR_STAGES=5, -DGU_CONSUMER_ROUNDS   layout variants that were measured
 #ifdef GU_TRACE
 // Cycle counters of cluster 0 (both CTAs), summed over the launch: [rank][slot]
 //  0 producer: waiting for a free ring slot     1 issuer: waiting for operands   2 issuer: waiting for a free unit
@@ -728,10 +728,9 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tm_x, const 
         const uint32_t stage = blocks_done % kPairStages, phase = (blocks_done / kPairStages) & 1u;
         const uint32_t t = lane_addr + acc * (2 * kTileN);
 
-        // This half's 128 columns come in rounds of kPairInFlight pieces of kPairPiece columns through two alternating
-        // sets of buffers: the loads of a round are in flight while the round before it is added; the stage goes back
-        // to the issuer as soon as the last round is in registers.  (Two loads of 16 columns instead of one of 32:
-        // same registers, but the allocator places four 16-register blocks without spilling, two 32-register ones not.)
+        // This half's 128 columns come in pieces of kPairPiece columns through four buffers; the stage goes back to the
+        // issuer as soon as the last piece is in registers.  (Loads of 16 columns instead of 32: same registers, but
+        // the allocator places four 16-register blocks without spilling, two 32-register ones not.)
         GU_TR_BEGIN();
         mbar_wait_lane(ctx, lane == 0, bar_done + 8 * stage, phase, kWaitPairDone);
         GU_TR_END(3);
@@ -761,7 +760,43 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tm_x, const 
         pair_fma(sums + 48, vc, scv);
         pair_fma(sums + 56, vd, scv);
 #endif
+#elif GU_PIECE == 16 && GU_INFLIGHT == 2 && !defined(GU_CONSUMER_ROUNDS)
+        // The shipped schedule: all four buffers are filled at once (64 columns in flight), each pair is refilled as
+        // soon as it has been added, and the stage goes back when the second 64 columns are in registers — two load
+        // latencies and 32 packed FMAs on the way to the release.  (The round-by-round loop below, four latencies:
+        // 0.433 against 0.4255 ms on prefill_8b.)
+        pair_ld(t + 2 * kPairPiece, vc);
+        pair_ld(t + 3 * kPairPiece, vd);
+        tmem_ld_wait();
+        pin_regs<kPairPiece>(va);
+        pin_regs<kPairPiece>(vb);
+        pin_regs<kPairPiece>(vc);
+        pin_regs<kPairPiece>(vd);
+        pair_fma(sums, va, scv);
+        pair_fma(sums + 8, vb, scv);
+        pair_ld(t + 4 * kPairPiece, va);
+        pair_ld(t + 5 * kPairPiece, vb);
+        pair_fma(sums + 16, vc, scv);
+        pair_fma(sums + 24, vd, scv);
+        pair_ld(t + 6 * kPairPiece, vc);
+        pair_ld(t + 7 * kPairPiece, vd);
+        tmem_ld_wait();
+        pin_regs<kPairPiece>(va);
+        pin_regs<kPairPiece>(vb);
+        pin_regs<kPairPiece>(vc);
+        pin_regs<kPairPiece>(vd);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(stage_free_even + 8 * acc);  // the half is in registers: hand it back
+        GU_EV(1, j, 3);
+        pair_fma(sums + 32, va, scv);
+        pair_fma(sums + 40, vb, scv);
+        pair_fma(sums + 48, vc, scv);
+        pair_fma(sums + 56, vd, scv);
 #else
+        // Round by round (the other piece sizes, one load in flight, and -DGU_CONSUMER_ROUNDS): kPairInFlight pieces
+        // per round through two alternating sets of buffers, the loads of a round in flight while the round before
+        // it is added.
 #pragma unroll
         for (int q = 0; q < kPairRounds; ++q) {
           // buffers of this round and of the next (one or two pieces each)

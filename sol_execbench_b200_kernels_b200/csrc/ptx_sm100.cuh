@@ -265,12 +265,17 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
 // Waits for this thread's outstanding tcgen05.ld.  The loaded registers are
 // threaded through as in/out operands so no use of them can be scheduled above it.
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// (no instruction: makes the registers of an earlier tcgen05.ld look written here, after the wait)
 template <int N>
-__device__ __forceinline__ void tmem_ld_wait_pin(float* v) {
-  tmem_ld_wait();
+__device__ __forceinline__ void pin_regs(float* v) {
   uint32_t* r = reinterpret_cast<uint32_t*>(v);
 #pragma unroll
   for (int i = 0; i < N; ++i) asm volatile("" : "+r"(r[i]));
+}
+template <int N>
+__device__ __forceinline__ void tmem_ld_wait_pin(float* v) {
+  tmem_ld_wait();
+  pin_regs<N>(v);
 }
 
 // ---------------------------------------------------------------------------
