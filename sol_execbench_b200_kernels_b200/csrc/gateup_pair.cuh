@@ -93,6 +93,7 @@ enum : unsigned {
 //                6 consumers do the promotion arithmetic on stale registers but never read TMEM
 //                7 consumers read only 64 of their 128 columns (two rounds of loads) before the stage goes back, all
 //                  the arithmetic still done; 8 as 7 with the arithmetic of those 64 columns only
+//               10 consumers read 64 columns in one batch, hand the stage back at once, then do all the arithmetic
 //                9 the epilogue warps skip the SwiGLU arithmetic (what their instruction stream costs the consumer
 //                  warps that share their schedulers)
 //   -DGU_PAIR_THREADS=512, -DGU_PIECE=32, -DGU_INFLIGHT=1, -DGU_PAIR_STAGES=5, -DGU_CONSUMER_ROUNDS   layout variants that were measured
@@ -760,6 +761,28 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tm_x, const 
         pair_fma(sums + 48, vc, scv);
         pair_fma(sums + 56, vd, scv);
 #endif
+#elif defined(GU_EXP) && GU_EXP == 10
+        // experiment: 64 of the 128 columns are read in one batch, the stage goes back at once, all the arithmetic of
+        // 128 columns follows (on stale registers for the second half): what consumers with half the columns each
+        // and twice the warps could reach at most
+        pair_ld(t + 2 * kPairPiece, vc);
+        pair_ld(t + 3 * kPairPiece, vd);
+        tmem_ld_wait();
+        pin_regs<kPairPiece>(va);
+        pin_regs<kPairPiece>(vb);
+        pin_regs<kPairPiece>(vc);
+        pin_regs<kPairPiece>(vd);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(stage_free_even + 8 * acc);
+        pair_fma(sums, va, scv);
+        pair_fma(sums + 8, vb, scv);
+        pair_fma(sums + 16, vc, scv);
+        pair_fma(sums + 24, vd, scv);
+        pair_fma(sums + 32, va, scv);
+        pair_fma(sums + 40, vb, scv);
+        pair_fma(sums + 48, vc, scv);
+        pair_fma(sums + 56, vd, scv);
 #elif GU_PIECE == 16 && GU_INFLIGHT == 2 && !defined(GU_CONSUMER_ROUNDS)
         // The shipped schedule: all four buffers are filled at once (64 columns in flight), each pair is refilled as
         // soon as it has been added, and the stage goes back when the second 64 columns are in registers — two load
