@@ -48,8 +48,9 @@ struct StreamParams {
 
 // The epoch of a launch is kept on the device, so that a launch recorded once (a CUDA graph) can be replayed: word
 // kStreamSyncLaunches of the flag area counts completed launches on this workspace, every CTA reads it when it starts
-// and stamps with that count + 1; at its end every CTA takes a ticket (word kStreamSyncTickets) and the last one
-// advances the count.  All CTAs have read the count before the last ticket is taken.
+// and stamps with that count + 1 and takes a ticket (word kStreamSyncTickets) right after reading; the CTA that drew
+// the last ticket advances the count when its work is done.  All CTAs have read the count before the last ticket is
+// taken.
 constexpr int kStreamSyncLaunches = 1022;
 constexpr int kStreamSyncTickets = 1023;
 static_assert(kStreamMaxGrid <= kStreamSyncLaunches, "hand-off flags and the launch counters share the flag area");
@@ -188,9 +189,11 @@ gateup_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_cons
     const int row = quarter * 32 + lane;  // weight row inside the tile = output column inside the block
     const int ctid = threadIdx.x - 64;    // 0..127
     unsigned int epoch = 0;               // this launch's stamp, never 0; only thread ctid == 0 uses it
+    unsigned int ticket = 0;              // taken as soon as the count has been read; looked at when the work is done
     if (ctid == 0) {
       epoch = ld_acquire_gpu(p.flags + kStreamSyncLaunches) + 1u;
       if (epoch == 0u) epoch = 1u;
+      ticket = atomicAdd(p.flags + kStreamSyncTickets, 1u);
     }
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
 
@@ -326,6 +329,13 @@ gateup_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_cons
       }
       if (++j == p.kb) { j = 0; ++nbk; }
     }
+    // Whoever drew the launch's last ticket — every CTA had read the count by then — advances the count: the next
+    // launch (or a replay of this one) stamps with a new epoch.
+    if (ctid == 0 && ticket == gridDim.x - 1u) {
+      p.flags[kStreamSyncTickets] = 0u;
+      __threadfence();
+      atomicAdd(p.flags + kStreamSyncLaunches, 1u);
+    }
   }
 
   // ------------------------------- teardown --------------------------------
@@ -337,15 +347,6 @@ gateup_stream_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_cons
     while (globaltimer_ns() - t0 < 200000ull) spin_backoff_ns(1000u);
   }
   if (warp == 1) tmem_dealloc(tmem_base, Cfg::kTmemCols);
-  if (threadIdx.x == 0) {
-    // the last CTA to get here closes the launch: the next one (or a replay of this one) stamps with a new epoch
-    __threadfence();
-    if (atomicAdd(p.flags + kStreamSyncTickets, 1u) == gridDim.x - 1u) {
-      p.flags[kStreamSyncTickets] = 0u;
-      __threadfence();
-      atomicAdd(p.flags + kStreamSyncLaunches, 1u);
-    }
-  }
 }
 
 }  // namespace gu
