@@ -97,6 +97,8 @@ enum : unsigned {
 //                9 the epilogue warps skip the SwiGLU arithmetic (what their instruction stream costs the consumer
 //                  warps that share their schedulers)
 //   -DGU_PAIR_THREADS=512, -DGU_PIECE=32, -DGU_INFLIGHT=1, -DGU_PAIR_STAGES=5, -DGU_CONSUMER_ROUNDS   layout variants that were measured
+//   -DGU_ISSUER2 two issuing threads in the even CTA (warps 0 and 1 each fill the ring slots and issue the K blocks of
+//                one parity); results are right, 3.6 % slower than one issuer (0.437 against 0.422 ms at 4096 tokens)
 #ifdef GU_TRACE
 // Cycle counters of cluster 0 (both CTAs), summed over the launch: [rank][slot]
 //  0 producer: waiting for a free ring slot     1 issuer: waiting for operands   2 issuer: waiting for a free unit
@@ -294,6 +296,12 @@ __device__ __forceinline__ void pair_swiglu_chunks(uint8_t* hand_gen, int first,
 // launch.  (Not in the stream-K kernel: with this code in it the same K loop measured 165 cycles per block slower,
 // 78.0 against 75.8 us at 512 x 4096 x 14336, for a reason that -Xptxas -v does not show.)
 constexpr int kPairAllHands = kPairEpiThreads + 256;
+#ifdef GU_ISSUER2
+// study: in the even CTA warps 0 and 1 each fill the ring slots of one parity and issue the K blocks of that parity
+constexpr bool kPairTwoIssuers = true;
+#else
+constexpr bool kPairTwoIssuers = false;
+#endif
 
 template <bool kSingle, int kMode = kPairPlain, bool kStreamK = false>
 __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tm_x, const CUtensorMap& tm_gate,
@@ -373,9 +381,38 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tm_x, const 
 
   if (!is_consumer) {
     reg_dealloc<40>();
-    if (warp == 0) {
+    if (warp == 0 || (kPairTwoIssuers && warp == 1 && rank == 0)) {
       // ---------------- TMA producer: the whole warp walks the loop, one elected lane waits and issues ----------------
       const bool elected = elect_one() != 0u;
+      // (two issuers) parity of the slots and K blocks this warp owns; -1: every slot, no block
+      const int own = (kPairTwoIssuers && rank == 0) ? (warp == 0 ? 1 : 0) : -1;
+      uint32_t next_issue = own < 0 ? 0u : static_cast<uint32_t>(own);
+      const uint32_t tmem_u2 = kPairTwoIssuers ? __shfl_sync(0xffffffffu, tmem_base, 0) : 0u;
+      const uint32_t done_odd2 = kPairTwoIssuers ? mapa_shared(bar_done, 1) : 0u;
+      auto issue_own = [&](uint32_t b) {
+        constexpr uint32_t idesc = umma_idesc_e4m3_f32(2 * kTileM, 2 * kTileN);
+        const uint32_t stage = b % kPairStages, phase = (b / kPairStages) & 1u;
+        const uint32_t acc = b & 1u, acc_phase = (b >> 1) & 1u;
+        const uint64_t adesc = umma_desc_k_sw128(ring) + stage * (kPairStageBytes >> 4);
+        const uint64_t bdesc = umma_desc_k_sw128(ring + kOperandTileBytes) + stage * (kPairStageBytes >> 4);
+        const uint32_t d = tmem_u2 + acc * (2 * kTileN);
+        bool ok = true;
+        if (elected) {
+          const uint32_t hit_full = mbar_try_wait(bar_full + 8 * stage, phase);
+          const uint32_t hit_free = mbar_try_wait(bar_stage_free + 8 * acc, acc_phase ^ 1u);
+          ok = hit_full || mbar_wait(ctx, bar_full + 8 * stage, phase, kWaitPairFull);
+          ok = (hit_free || mbar_wait(ctx, bar_stage_free + 8 * acc, acc_phase ^ 1u, kWaitPairStageFree)) && ok;
+        }
+        if (ok && elected) {
+          tc_fence_after();
+#pragma unroll
+          for (int kk = 0; kk < kBlockK / 32; ++kk)
+            umma_f8_pair(d, adesc + 2 * kk, bdesc + 2 * kk, idesc, kk > 0 ? 1u : 0u);
+          umma_commit_pair(bar_done + 8 * stage);
+          umma_commit_pair(done_odd2 + 8 * stage);
+        }
+        __syncwarp();
+      };
 #ifdef GU_TRACE
       tr_me = blockIdx.x < 2 && elected;
 #endif
@@ -389,6 +426,7 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tm_x, const 
         const int row0 = (2 * pm + static_cast<int>(rank)) * kTileM;
         for (int j = jb; j < je; ++j, ++slots) {
           const uint32_t stage = slots % kPairStages, phase = (slots / kPairStages) & 1u;
+          if (kPairTwoIssuers && own >= 0 && static_cast<int>(slots & 1u) != own) continue;
           GU_TR_BEGIN();
           const bool ok = mbar_wait_elected(ctx, elected, bar_done + 8 * stage, phase ^ 1u, kWaitPairSlot);
           GU_TR_END(0);
@@ -412,13 +450,26 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tm_x, const 
             }
           }
           __syncwarp();
+          if constexpr (kPairTwoIssuers) {
+            if (own >= 0) {
+              for (; next_issue + 2 <= slots; next_issue += 2) issue_own(next_issue);
+            }
+          }
+        }
+      }
+      if constexpr (kPairTwoIssuers) {
+        if (own >= 0) {
+          for (; next_issue < slots; next_issue += 2) issue_own(next_issue);
+          // the odd CTA's last hand-backs must have landed here before this CTA may go away
+          for (uint32_t b = slots; b < slots + 2; ++b)
+            mbar_wait_elected(ctx, elected, bar_stage_free + 8 * (b & 1u), ((b >> 1) & 1u) ^ 1u, kWaitPairStageFree);
         }
       }
       // the last commits into this CTA's ring barriers must have landed before the CTA may go away
       for (int s = 0; s < kPairStages; ++s, ++slots)
         mbar_wait_elected(ctx, elected, bar_done + 8 * (slots % kPairStages), ((slots / kPairStages) & 1u) ^ 1u,
                           kWaitPairSlot);
-    } else if (warp == 1 && rank == 0) {
+    } else if (!kPairTwoIssuers && warp == 1 && rank == 0) {
       // ---------------- MMA issuer of the pair: the whole warp walks the loop, one elected lane waits and issues ------
       const bool elected = elect_one() != 0u;
 #ifdef GU_TRACE
