@@ -42,7 +42,8 @@ extern "C" {
 
 /* plans */
 #define GU_PLAN_AUTO 0    /* shape heuristic (gu_select_plan)                                      */
-#define GU_PLAN_TILE 1    /* persistent tiles of both projections; any M; CTA pairs above 128 tokens    */
+#define GU_PLAN_TILE 1    /* persistent tiles of both projections; any M; above 128 tokens CTA pairs or lone CTAs,
+                             whichever the tile counts favour (same bits for whole tiles) */
 #define GU_PLAN_STREAM 2  /* weight-streaming, tokens on the MMA N side, stream-K over (N-block, K-block); M <= 64 */
 #define GU_PLAN_TILE_DP 3 /* lone-CTA tile kernel, data-parallel schedule forced (whole tiles per CTA, no scratch) */
 #define GU_PLAN_TILE_SK 4 /* lone-CTA tile kernel, stream-K schedule forced (needs scratch)                  */

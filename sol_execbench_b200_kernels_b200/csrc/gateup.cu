@@ -348,8 +348,8 @@ int launch_tile(const gu_problem* pr, const DeviceInfo& dev, cudaStream_t stream
 // tile's SwiGLU on two warps only) costs about 8 us per launch, measured on B200 at K=4096, N=14336 against whole
 // tiles: 512 tokens (3.03 rounds) 73.8 against 77.8 us, 1024 (6.05) 123.7 against 127.3, 2048 (12.1) 229.4 against
 // 231.5, 4096 (24.2) within the noise; 256 tokens (1.51 rounds, no whole round before the cut) 55.2 against 47.1, and
-// 2 - 4 us lost where the tiles divide evenly.  So the heuristic wants two rounds or more and at least 10 % of the
-// device idle in the last round of whole tiles.
+// 2 - 4 us lost where the tiles divide evenly.  So the heuristic wants two rounds or more, at least 10 % of the
+// device idle in the last round of whole tiles, and a last round less than 0.3 full.
 bool pair_can_stream_k(int tiles, int clusters) {
   // one flag word and one 128 KiB slot of the scratch per CTA
   return clusters >= 2 && tiles >= clusters && 2 * clusters <= kPairMaxCtas && 2 * clusters <= kTileMaxGrid;
@@ -357,7 +357,8 @@ bool pair_can_stream_k(int tiles, int clusters) {
 bool pair_prefers_stream_k(int tiles, int clusters) {
   if (!pair_can_stream_k(tiles, clusters) || tiles < 2 * clusters || tiles % clusters == 0) return false;
   const int rounds = (tiles + clusters - 1) / clusters;
-  return double(tiles) / (double(rounds) * clusters) < 0.90;
+  // (the hand-off is worth about 0.7 of a round: 3.57 rounds at K=2048 ran 55.8 us cut against 53.2 us whole)
+  return double(tiles) / (double(rounds) * clusters) < 0.90 && double(tiles) / clusters + 0.7 < double(rounds);
 }
 
 int launch_pair(const gu_problem* pr, const DeviceInfo& dev, cudaStream_t stream, int stream_k /* 0 no, 1 yes, -1 by the heuristic */) {
@@ -422,6 +423,31 @@ int launch_pair(const gu_problem* pr, const DeviceInfo& dev, cudaStream_t stream
 // The tile plan's kernel for a shape: CTA pairs once there is more than one 128-token block (a lone block would
 // leave the second CTA of every pair without rows), the lone-CTA kernel otherwise.
 bool tile_prefers_pairs(int64_t m, const DeviceInfo& dev) { return m > kTileM && dev.pair_clusters >= 1; }
+
+// gu_run's choice between the two tile kernels for more than one 128-token block.  The lone-CTA kernel needs about
+// 1.21 times as long for the same work (its MMAs read every weight row from the CTA's own shared memory) but it
+// schedules 128-token blocks on single SMs and starts and ends a few microseconds sooner, so it wins where the pair
+// kernel's rounds come out badly: an odd number of 128-token blocks (a third block costs the pair kernel a whole
+// 256-token block), or few K blocks per tile.  Costs are counted in rounds of the pair kernel; its stream-K
+// schedule costs the fraction of rounds it runs plus 0.7 of a round.  Measured on B200 over 129 ... 3072 tokens at
+// (K, N) = (4096, 14336), (8192, 28672), (7168, 2304), (2048, 5632): the kernel picked this way is within 7 % of
+// the fastest of the three everywhere; before (pairs for every M > 128) it was up to 66 % behind (384 tokens at
+// (2048, 5632): 30.7 us against 18.4 us) and 9 - 14 % behind at 320 - 384 tokens on the large shapes.  Both kernels
+// give the same bits when no tile is cut along K.
+bool tile_prefers_lone(int64_t m, int64_t k, int64_t n, int sm_count, int pair_clusters, bool scratch) {
+  if (m <= kTileM || pair_clusters < 1) return true;
+  const int64_t col = n / kTileN, kb = k / 128;
+  const int64_t lone_tiles = ((m + kTileM - 1) / kTileM) * col, pair_tiles = ((m + 2 * kTileM - 1) / (2 * kTileM)) * col;
+  if (pair_tiles >= (1ll << 31) || sm_count < 1) return false;
+  const double lone_rounds = double((lone_tiles + sm_count - 1) / sm_count);
+  const int clusters = pair_tiles < pair_clusters ? static_cast<int>(pair_tiles) : pair_clusters;
+  double pair_rounds = double((pair_tiles + clusters - 1) / clusters);
+  if (scratch && pair_prefers_stream_k(static_cast<int>(pair_tiles), clusters)) {
+    const double cut = double(pair_tiles) / clusters + 0.7;
+    if (cut < pair_rounds) pair_rounds = cut;
+  }
+  return 1.21 * lone_rounds <= pair_rounds + 16.0 / double(kb) - 0.1;
+}
 
 // Tile geometry of a pair launch: 256-token pair blocks x `col_tiles` column tiles, raster groups that keep a
 // group's activation rows (256 x K bytes per pair block) within ~24 MiB of L2.  Returns the number of clusters to
@@ -573,7 +599,8 @@ size_t gu_workspace_bytes(int64_t m, int64_t k, int64_t n, int plan) {
     // what the tile plan would launch on a B200 (one cluster per two SMs): scratch only where stream-K is chosen
     const int clusters = gu::sm_count_or_default() / 2;
     const int64_t tiles = ((m + 255) / 256) * (n / 128);
-    if (m > gu::kTileM && tiles < (1ll << 31) && gu::pair_prefers_stream_k(static_cast<int>(tiles), clusters))
+    if (m > gu::kTileM && tiles < (1ll << 31) && gu::pair_prefers_stream_k(static_cast<int>(tiles), clusters) &&
+        !gu::tile_prefers_lone(m, k, n, gu::sm_count_or_default(), clusters, true))
       return gu::tile_stream_k_bytes();
     if (m <= gu::kTileM && gu::tile_prefers_stream_k(m, k, n, gu::sm_count_or_default())) return gu::tile_stream_k_bytes();
   }
@@ -599,9 +626,13 @@ int gu_run(const gu_problem* pr, void* stream_v) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   if (plan == GU_PLAN_TILE_PAIR) return gu::launch_pair(pr, *dev, stream, 0);
   if (plan == GU_PLAN_TILE_PAIR_SK) return gu::launch_pair(pr, *dev, stream, 1);
-  if (plan == GU_PLAN_TILE && gu::tile_prefers_pairs(pr->m, *dev)) return gu::launch_pair(pr, *dev, stream, -1);
+  const bool have_ws = pr->workspace && pr->workspace_bytes >= gu::tile_stream_k_bytes() && gu::aligned16(pr->workspace);
+  if (plan == GU_PLAN_TILE && pr->m > gu::kTileM) {
+    if (!gu::tile_prefers_lone(pr->m, pr->k, pr->n, dev->sm_count, dev->pair_clusters, have_ws))
+      return gu::launch_pair(pr, *dev, stream, -1);
+    plan = GU_PLAN_TILE_DP;  // whole 128-token tiles on single SMs
+  }
   if (plan != GU_PLAN_STREAM) {
-    const bool have_ws = pr->workspace && pr->workspace_bytes >= gu::tile_stream_k_bytes() && gu::aligned16(pr->workspace);
     bool sk = false;
     if (plan == GU_PLAN_TILE_SK) {
       if (!have_ws) return GU_EWORKSPACE;

@@ -68,6 +68,10 @@ def test_workspace_sizes(gateup_lib):
     assert lib.gu_workspace_bytes(256, 4096, 14336, gateup_lib.PLAN_AUTO) == 0        # 1.51 rounds: whole tiles
     assert lib.gu_workspace_bytes(512, 4096, 9472, gateup_lib.PLAN_AUTO) == 0         # two rounds exactly
     assert lib.gu_workspace_bytes(128, 4096, 14336, gateup_lib.PLAN_TILE_SK) == sk
+    # three 128-token blocks: the lone-CTA kernel with whole tiles (3 rounds) beats two 256-token pair blocks
+    assert lib.gu_workspace_bytes(384, 4096, 14336, gateup_lib.PLAN_AUTO) == 0
+    assert lib.gu_workspace_bytes(384, 2048, 5632, gateup_lib.PLAN_AUTO) == 0
+    assert lib.gu_workspace_bytes(1024, 4096, 14336, gateup_lib.PLAN_AUTO) == sk       # 6.05 rounds of pairs
     w16 = lib.gu_workspace_bytes(16, 8192, 28672, gateup_lib.PLAN_AUTO)
     w64 = lib.gu_workspace_bytes(64, 8192, 28672, gateup_lib.PLAN_STREAM)
     assert w16 == 4096 + 256 * 2 * 16 * 128 * 4

@@ -131,6 +131,17 @@ def test_pair_kernel_stream_k_schedule_parity(pkg, shape):
     assert torch.equal(kept, whole)
 
 
+@pytest.mark.parametrize("shape", [(384, 2048, 5632), (320, 512, 2048), (640, 256, 14336), (300, 128, 1024)])
+def test_heuristic_plan_with_an_odd_number_of_token_blocks(pkg, shape):
+    # an odd number of 128-token blocks, or few K blocks per tile: the heuristic plan runs whole 128-token tiles on
+    # single SMs instead of 256-token pair tiles; either way the bits are those of the whole-tile schedule
+    inp = W.make_inputs(*shape, seed=2)
+    out = _run(pkg, inp, "tile")
+    _check(out, inp, f"tile {shape}")
+    assert torch.equal(out, _run(pkg, inp, "tile_dp"))
+    assert torch.equal(out, _run(pkg, inp, "tile_pair"))
+
+
 def test_pair_kernel_stream_k_needs_a_tile_per_cluster(pkg):
     inp = W.make_inputs(256, 128, 128, seed=1)
     with pytest.raises(ValueError, match="plan"):
