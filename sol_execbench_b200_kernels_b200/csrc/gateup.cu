@@ -424,29 +424,43 @@ int launch_pair(const gu_problem* pr, const DeviceInfo& dev, cudaStream_t stream
 // leave the second CTA of every pair without rows), the lone-CTA kernel otherwise.
 bool tile_prefers_pairs(int64_t m, const DeviceInfo& dev) { return m > kTileM && dev.pair_clusters >= 1; }
 
-// gu_run's choice between the two tile kernels for more than one 128-token block.  The lone-CTA kernel needs about
-// 1.21 times as long for the same work (its MMAs read every weight row from the CTA's own shared memory) but it
-// schedules 128-token blocks on single SMs and starts and ends a few microseconds sooner, so it wins where the pair
-// kernel's rounds come out badly: an odd number of 128-token blocks (a third block costs the pair kernel a whole
-// 256-token block), or few K blocks per tile.  Costs are counted in rounds of the pair kernel; its stream-K
-// schedule costs the fraction of rounds it runs plus 0.7 of a round.  Measured on B200 over 129 ... 3072 tokens at
-// (K, N) = (4096, 14336), (8192, 28672), (7168, 2304), (2048, 5632): the kernel picked this way is within 7 % of
-// the fastest of the three everywhere; before (pairs for every M > 128) it was up to 66 % behind (384 tokens at
-// (2048, 5632): 30.7 us against 18.4 us) and 9 - 14 % behind at 320 - 384 tokens on the large shapes.  Both kernels
-// give the same bits when no tile is cut along K.
-bool tile_prefers_lone(int64_t m, int64_t k, int64_t n, int sm_count, int pair_clusters, bool scratch) {
+// The choice between the two tile kernels for more than one 128-token block.  The lone-CTA kernel needs about 1.21
+// times as long for the same work (its MMAs read every weight row from the CTA's own shared memory) but it schedules
+// 128-token blocks on single SMs, starts and ends a few microseconds sooner (worth about 16 K blocks) and has four
+// epilogue warps per 128 x 128 outputs where the pair kernel has two, so it wins where the pair kernel's rounds come
+// out badly — an odd number of 128-token blocks (a third block costs the pair kernel a whole 256-token block) — or
+// where a tile has so few K blocks that the pair kernel's epilogue takes longer than its K loop.  Costs are counted
+// in K blocks of the pair kernel: rounds x max(K blocks per tile, the epilogue's length in K blocks); the pair
+// kernel's stream-K schedule costs the fraction of rounds it runs plus 0.7 of a round.  Measured on B200 over 129 ...
+// 4096 tokens.  Gate/up, bf16 output, (K, N) = (4096, 14336), (8192, 28672), (7168, 2304), (2048, 5632), (3584,
+// 18944), (5120, 13824), (1024, 4096), (4096, 4736): the kernel picked this way is within 7 % of the fastest
+// everywhere; with pairs for every M > 128 it was up to 66 % behind (384 tokens at (2048, 5632): 30.7 us against
+// 18.4 us) and 9 - 14 % behind at 320 - 384 tokens on the large shapes.  Gate/up with e4m3 output: the pair kernel's
+// two epilogue warps need about 29 K blocks' time per tile, so at K = 2048 the lone kernel is 21 - 105 % faster at
+// every M (4096 tokens: 118.8 against 144.3 us), at K = 4096 only on odd block counts (384 tokens: 68.1 against
+// 79.9 us).  Single GEMM, (K, N) = (14336, 4096), (5632, 2048), (4096, 4096): pairs except where the lone kernel
+// saves a round (1152 tokens: 71.8 against 105.5 us).  Both kernels give the same bits when no tile is cut along K.
+enum TileOp { kOpGateUp = 0, kOpGateUpFp8 = 1, kOpGemm = 2 };
+bool tile_prefers_lone(int op, int64_t m, int64_t kb, int64_t col_tiles, int sm_count, int pair_clusters, bool scratch) {
   if (m <= kTileM || pair_clusters < 1) return true;
-  const int64_t col = n / kTileN, kb = k / 128;
-  const int64_t lone_tiles = ((m + kTileM - 1) / kTileM) * col, pair_tiles = ((m + 2 * kTileM - 1) / (2 * kTileM)) * col;
+  const int64_t lone_tiles = ((m + kTileM - 1) / kTileM) * col_tiles;
+  const int64_t pair_tiles = ((m + 2 * kTileM - 1) / (2 * kTileM)) * col_tiles;
   if (pair_tiles >= (1ll << 31) || sm_count < 1) return false;
   const double lone_rounds = double((lone_tiles + sm_count - 1) / sm_count);
   const int clusters = pair_tiles < pair_clusters ? static_cast<int>(pair_tiles) : pair_clusters;
   double pair_rounds = double((pair_tiles + clusters - 1) / clusters);
-  if (scratch && pair_prefers_stream_k(static_cast<int>(pair_tiles), clusters)) {
+  if (op == kOpGateUp && scratch && pair_prefers_stream_k(static_cast<int>(pair_tiles), clusters)) {
     const double cut = double(pair_tiles) / clusters + 0.7;
     if (cut < pair_rounds) pair_rounds = cut;
   }
-  return 1.21 * lone_rounds <= pair_rounds + 16.0 / double(kb) - 0.1;
+  // epilogue lengths in K blocks (pair, lone) and the lone kernel's head start
+  const double pair_epi = op == kOpGateUp ? 18.0 : op == kOpGateUpFp8 ? 29.0 : 0.0;
+  const double lone_epi = op == kOpGateUpFp8 ? 20.0 : 0.0;
+  const double head_start = op == kOpGemm ? 0.0 : 16.0;
+  const double kbd = double(kb);
+  const double pair_cost = pair_rounds * (kbd > pair_epi ? kbd : pair_epi);
+  const double lone_cost = 1.21 * lone_rounds * (kbd > lone_epi ? kbd : lone_epi);
+  return lone_cost <= pair_cost + head_start - 0.1 * kbd;
 }
 
 // Tile geometry of a pair launch: 256-token pair blocks x `col_tiles` column tiles, raster groups that keep a
@@ -600,7 +614,7 @@ size_t gu_workspace_bytes(int64_t m, int64_t k, int64_t n, int plan) {
     const int clusters = gu::sm_count_or_default() / 2;
     const int64_t tiles = ((m + 255) / 256) * (n / 128);
     if (m > gu::kTileM && tiles < (1ll << 31) && gu::pair_prefers_stream_k(static_cast<int>(tiles), clusters) &&
-        !gu::tile_prefers_lone(m, k, n, gu::sm_count_or_default(), clusters, true))
+        !gu::tile_prefers_lone(gu::kOpGateUp, m, k / 128, n / gu::kTileN, gu::sm_count_or_default(), clusters, true))
       return gu::tile_stream_k_bytes();
     if (m <= gu::kTileM && gu::tile_prefers_stream_k(m, k, n, gu::sm_count_or_default())) return gu::tile_stream_k_bytes();
   }
@@ -628,7 +642,8 @@ int gu_run(const gu_problem* pr, void* stream_v) {
   if (plan == GU_PLAN_TILE_PAIR_SK) return gu::launch_pair(pr, *dev, stream, 1);
   const bool have_ws = pr->workspace && pr->workspace_bytes >= gu::tile_stream_k_bytes() && gu::aligned16(pr->workspace);
   if (plan == GU_PLAN_TILE && pr->m > gu::kTileM) {
-    if (!gu::tile_prefers_lone(pr->m, pr->k, pr->n, dev->sm_count, dev->pair_clusters, have_ws))
+    if (!gu::tile_prefers_lone(gu::kOpGateUp, pr->m, pr->k / 128, pr->n / gu::kTileN, dev->sm_count, dev->pair_clusters,
+                               have_ws))
       return gu::launch_pair(pr, *dev, stream, -1);
     plan = GU_PLAN_TILE_DP;  // whole 128-token tiles on single SMs
   }
@@ -1001,7 +1016,7 @@ int gu_run_fp8out(const gu_problem* pr, void* out_q, float* out_scale, void* str
   p.blocks_per_owner = 1;
   p.slot_rows = 0;
 
-  if (gu::tile_prefers_pairs(m, *dev)) {
+  if (!gu::tile_prefers_lone(gu::kOpGateUpFp8, m, k / 128, n / gu::kTileN, dev->sm_count, dev->pair_clusters, false)) {
     const int clusters = gu::pair_geometry(p, *dev, m, k, static_cast<int>(n / gu::kTileN));
     if (clusters < 1) return GU_EINVAL_SHAPE;
     gu::gateup_pair_fp8out_kernel<<<2 * clusters, gu::kPairThreads, gu::kPairSmemBytes,
@@ -1044,7 +1059,7 @@ int gu_blockwise_gemm(const void* a, const float* scale_a, const void* b, const 
   p.slot_rows = 0;
   p.out_rows = static_cast<int>(m);
   p.out_cols = static_cast<int>(n);
-  if (gu::tile_prefers_pairs(m, *dev)) {
+  if (!gu::tile_prefers_lone(gu::kOpGemm, m, k / 128, (n / 128 + 1) / 2, dev->sm_count, dev->pair_clusters, false)) {
     // CTA pairs: 256-token x 256-column tiles, one per two-CTA cluster
     p.num_m_blocks = static_cast<int>((m + 2 * gu::kTileM - 1) / (2 * gu::kTileM));
     p.num_n_blocks = (p.n_blocks128 + 1) / 2;
