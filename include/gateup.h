@@ -88,6 +88,24 @@ const char* gu_error_string(int code);
 int gu_select_plan(int64_t m, int64_t k, int64_t n);
 
 /*
+ * Which tile kernel and schedule the tile plan runs for `op` on this shape on
+ * the current device (148 SMs assumed when there is none): GU_PLAN_TILE_DP
+ * (lone CTAs, whole tiles), GU_PLAN_TILE_SK, GU_PLAN_TILE_PAIR or
+ * GU_PLAN_TILE_PAIR_SK; `with_workspace` says whether the call will pass
+ * scratch (the stream-K schedules need it; only GU_OP_GATEUP has them).  The
+ * reference's counterpart is the parity test on M / 128 in
+ * `launch_fp8_mlp_gate_up` (variants/cuda_cpp_v4/kernel.cu:297-311), which
+ * picks its 2-CTA or 1-CTA configuration; here the choice follows measured
+ * costs (rounds of tiles x max(K blocks per tile, epilogue length)).  Whole
+ * tiles give the same bits on either kernel.  Returns a negative code for a
+ * shape or `op` that is not supported.
+ */
+#define GU_OP_GATEUP 0     /* gu_run / gu_run_concat */
+#define GU_OP_GATEUP_FP8 1 /* gu_run_fp8out */
+#define GU_OP_GEMM 2       /* gu_blockwise_gemm */
+int gu_select_tile_kernel(int op, int64_t m, int64_t k, int64_t n, int with_workspace);
+
+/*
  * Scratch bytes a plan needs for this shape (0 when it needs none).  The
  * reference allocates its scratch inside the call (kernel.py:226-229,
  * cuda_cpp_v4/kernel.cu:221-230, 290-296); here the caller owns it.

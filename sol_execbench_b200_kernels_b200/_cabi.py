@@ -23,11 +23,12 @@ GU_ESTATIC_LIMIT = -9
 GU_EBOUNDS = -10
 
 PLAN_AUTO, PLAN_TILE, PLAN_STREAM, PLAN_TILE_DP, PLAN_TILE_SK, PLAN_TILE_PAIR, PLAN_TILE_PAIR_SK = 0, 1, 2, 3, 4, 5, 6
+OP_GATEUP, OP_GATEUP_FP8, OP_GEMM = 0, 1, 2
 PLAN_NAMES = {PLAN_AUTO: "auto", PLAN_TILE: "tile", PLAN_STREAM: "stream", PLAN_TILE_DP: "tile_dp",
               PLAN_TILE_SK: "tile_sk", PLAN_TILE_PAIR: "tile_pair", PLAN_TILE_PAIR_SK: "tile_pair_sk"}
 
 EXPORTS = (
-    "gu_version", "gu_error_string", "gu_select_plan", "gu_workspace_bytes", "gu_workspace_init",
+    "gu_version", "gu_error_string", "gu_select_plan", "gu_select_tile_kernel", "gu_workspace_bytes", "gu_workspace_init",
     "gu_run", "gu_run_concat", "gu_last_status", "gu_launch_count", "gu_run_decode_static", "gu_run_gather", "gu_quantize_activation", "gu_blockwise_gemm", "gu_run_fp8out",
     "gu_blockwise_gemm_scatter", "gu_reduce_gather", "gu_set_wait_limit_ns", "gu_trace_read", "gu_wait_probe", "gu_peer_barrier", "gu_is_range_checked_build",
 )
@@ -63,6 +64,8 @@ def _load() -> ctypes.CDLL:
     lib.gu_error_string.argtypes = [c_int]
     lib.gu_select_plan.restype = c_int
     lib.gu_select_plan.argtypes = [c_int64, c_int64, c_int64]
+    lib.gu_select_tile_kernel.restype = c_int
+    lib.gu_select_tile_kernel.argtypes = [c_int, c_int64, c_int64, c_int64, c_int]
     lib.gu_workspace_bytes.restype = c_size_t
     lib.gu_workspace_bytes.argtypes = [c_int64, c_int64, c_int64, c_int]
     lib.gu_workspace_init.restype = c_int

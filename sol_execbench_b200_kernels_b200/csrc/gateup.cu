@@ -440,7 +440,7 @@ bool tile_prefers_pairs(int64_t m, const DeviceInfo& dev) { return m > kTileM &&
 // every M (4096 tokens: 118.8 against 144.3 us), at K = 4096 only on odd block counts (384 tokens: 68.1 against
 // 79.9 us).  Single GEMM, (K, N) = (14336, 4096), (5632, 2048), (4096, 4096): pairs except where the lone kernel
 // saves a round (1152 tokens: 71.8 against 105.5 us).  Both kernels give the same bits when no tile is cut along K.
-enum TileOp { kOpGateUp = 0, kOpGateUpFp8 = 1, kOpGemm = 2 };
+enum TileOp { kOpGateUp = GU_OP_GATEUP, kOpGateUpFp8 = GU_OP_GATEUP_FP8, kOpGemm = GU_OP_GEMM };
 bool tile_prefers_lone(int op, int64_t m, int64_t kb, int64_t col_tiles, int sm_count, int pair_clusters, bool scratch) {
   if (m <= kTileM || pair_clusters < 1) return true;
   const int64_t lone_tiles = ((m + kTileM - 1) / kTileM) * col_tiles;
@@ -601,6 +601,22 @@ int gu_select_plan(int64_t m, int64_t k, int64_t n) {
   if (can_stream && ((m <= 16 && weight_bytes >= (64ll << 20)) || (m <= 32 && weight_bytes >= (256ll << 20))))
     return GU_PLAN_STREAM;
   return GU_PLAN_TILE;
+}
+
+int gu_select_tile_kernel(int op, int64_t m, int64_t k, int64_t n, int with_workspace) {
+  if (!gu::shape_ok(m, k, n)) return GU_EINVAL_SHAPE;
+  if (op != GU_OP_GATEUP && op != GU_OP_GATEUP_FP8 && op != GU_OP_GEMM) return GU_EINVAL_PLAN;
+  const int sms = gu::sm_count_or_default(), clusters = sms / 2;
+  const int64_t col_tiles = op == GU_OP_GEMM ? (n / 128 + 1) / 2 : n / gu::kTileN;
+  if (gu::tile_prefers_lone(op, m, k / 128, col_tiles, sms, clusters, with_workspace != 0)) {
+    const bool cut = op == GU_OP_GATEUP && with_workspace && m <= gu::kTileM && gu::tile_prefers_stream_k(m, k, n, sms);
+    return cut ? GU_PLAN_TILE_SK : GU_PLAN_TILE_DP;
+  }
+  const int64_t tiles = ((m + 2 * gu::kTileM - 1) / (2 * gu::kTileM)) * col_tiles;
+  const int used = tiles < clusters ? static_cast<int>(tiles) : clusters;
+  return op == GU_OP_GATEUP && with_workspace && gu::pair_prefers_stream_k(static_cast<int>(tiles), used)
+             ? GU_PLAN_TILE_PAIR_SK
+             : GU_PLAN_TILE_PAIR;
 }
 
 size_t gu_workspace_bytes(int64_t m, int64_t k, int64_t n, int plan) {

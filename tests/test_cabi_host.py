@@ -78,6 +78,58 @@ def test_workspace_sizes(gateup_lib):
     assert w64 == 4096 + 256 * 2 * 64 * 128 * 4
 
 
+# (op, (M, K, N), kernel) rows of the B200 measurements the choice was fitted on: the fastest of the three kernels there
+_MEASURED_CHOICES = [
+    ("gateup", (256, 4096, 14336), "tile_pair"),        # 44.4 us against 47.2 lone
+    ("gateup", (384, 4096, 14336), "tile_dp"),          # three 128-token blocks: 65.4 lone against 71.6 / 73.7
+    ("gateup", (512, 4096, 14336), "tile_pair_sk"),     # 3.03 rounds: 71.7 cut, 73.8 whole, 83.9 lone
+    ("gateup", (640, 4096, 14336), "tile_dp"),          # 86.0 lone against 90.1
+    ("gateup", (768, 4096, 14336), "tile_pair"),        # 90.2 against 104.4 lone
+    ("gateup", (1024, 4096, 14336), "tile_pair_sk"),
+    ("gateup", (4096, 4096, 14336), "tile_pair"),       # the headline shape: whole tiles on pairs
+    ("gateup", (16384, 7168, 18432), "tile_pair"),
+    ("gateup", (16384, 7168, 2304), "tile_pair"),       # the 8-GPU shard of it
+    ("gateup", (384, 8192, 28672), "tile_dp"),          # 197.6 lone against 221 - 233
+    ("gateup", (512, 8192, 28672), "tile_pair_sk"),
+    ("gateup", (384, 2048, 5632), "tile_dp"),           # 18.4 lone against 30.7
+    ("gateup", (1024, 2048, 5632), "tile_dp"),          # 38.9 lone against 43.0
+    ("gateup", (1536, 2048, 5632), "tile_dp"),          # 49.1 lone against 53.2 whole, 55.8 cut
+    ("gateup", (1024, 7168, 2304), "tile_pair"),
+    ("gateup", (128, 4096, 14336), "tile_dp"),
+    ("gateup_fp8", (4096, 4096, 14336), "tile_pair"),
+    ("gateup_fp8", (384, 4096, 14336), "tile_dp"),      # 68.1 lone against 79.9
+    ("gateup_fp8", (512, 4096, 14336), "tile_pair"),    # 80.8 against 86.0 lone
+    ("gateup_fp8", (4096, 2048, 5632), "tile_dp"),      # short K: the pair epilogue outlasts the K loop, 118.8 against 144.3
+    ("gateup_fp8", (256, 2048, 5632), "tile_dp"),
+    ("gemm", (4096, 14336, 4096), "tile_pair"),         # the down projection
+    ("gemm", (1024, 14336, 4096), "tile_pair"),         # 60.4 against 69.7 lone
+    ("gemm", (1152, 14336, 4096), "tile_dp"),           # nine blocks fit one round of lone CTAs: 71.8 against 105.5
+    ("gemm", (1152, 4096, 4096), "tile_dp"),            # 28.5 against 38.9
+    ("gemm", (768, 4096, 4096), "tile_pair"),           # 24.6 against 27.0 lone
+    ("gemm", (1152, 5632, 2048), "tile_pair"),          # 29.6 against 32.8 lone
+]
+
+
+@pytest.mark.parametrize("op,shape,kernel", _MEASURED_CHOICES)
+def test_tile_kernel_choice_matches_the_measurements(gateup_lib, op, shape, kernel):
+    ops = {"gateup": gateup_lib.OP_GATEUP, "gateup_fp8": gateup_lib.OP_GATEUP_FP8, "gemm": gateup_lib.OP_GEMM}
+    code = gateup_lib.lib.gu_select_tile_kernel(ops[op], *shape, 1)
+    assert gateup_lib.PLAN_NAMES[code] == kernel
+    # without scratch nothing is cut along K
+    bare = gateup_lib.PLAN_NAMES[gateup_lib.lib.gu_select_tile_kernel(ops[op], *shape, 0)]
+    assert bare in ("tile_dp", "tile_pair")
+
+
+def test_tile_kernel_choice_rejects_bad_arguments(gateup_lib):
+    lib = gateup_lib.lib
+    assert lib.gu_select_tile_kernel(gateup_lib.OP_GATEUP, 4, 100, 128, 1) == gateup_lib.GU_EINVAL_SHAPE
+    assert lib.gu_select_tile_kernel(3, 256, 128, 128, 1) == gateup_lib.GU_EINVAL_PLAN
+    # scratch is asked for exactly where a stream-K schedule would run
+    for shape in [(512, 4096, 14336), (384, 4096, 14336), (4096, 4096, 14336), (1024, 8192, 28672)]:
+        cut = gateup_lib.PLAN_NAMES[lib.gu_select_tile_kernel(gateup_lib.OP_GATEUP, *shape, 1)].endswith("_sk")
+        assert (lib.gu_workspace_bytes(*shape, gateup_lib.PLAN_TILE) > 0) == cut, shape
+
+
 def _problem(gateup_lib, **over):
     base = dict(x=0x1000, scale_x=0x2000, gate_w=0x3000, scale_gate=0x4000, up_w=0x5000, scale_up=0x6000,
                 output=0x7000, m=128, k=128, n=128, ld_output=128, workspace=None, workspace_bytes=0,
