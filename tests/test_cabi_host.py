@@ -96,6 +96,10 @@ _MEASURED_CHOICES = [
     ("gateup", (1536, 2048, 5632), "tile_dp"),          # 49.1 lone against 53.2 whole, 55.8 cut
     ("gateup", (1024, 7168, 2304), "tile_pair"),
     ("gateup", (128, 4096, 14336), "tile_dp"),
+    ("gateup", (4096, 1024, 4096), "tile_dp"),          # 8 K blocks per tile: 51.1 lone against 73.7
+    ("gateup", (256, 2560, 6912), "tile_dp"),           # 20.9 lone against 22.5
+    ("gateup", (2048, 2560, 6912), "tile_pair"),        # 75.8 against 81.9 lone
+    ("gateup", (4096, 3072, 8192), "tile_pair"),        # 180.2 against 206.8 lone
     ("gateup_fp8", (4096, 4096, 14336), "tile_pair"),
     ("gateup_fp8", (384, 4096, 14336), "tile_dp"),      # 68.1 lone against 79.9
     ("gateup_fp8", (512, 4096, 14336), "tile_pair"),    # 80.8 against 86.0 lone
